@@ -1,0 +1,113 @@
+/*
+ * magi_swiglu.h — C ABI of the B200 (sm_100a) fused GEMM-SwiGLU library.
+ *
+ *     Y[M,N] = silu(X[M,K] · Wg[N,K]^T) * (X[M,K] · Wu[N,K]^T)
+ *
+ * with one packed weight W[2N,K] = [Wg ; Wu] (gate rows first), bf16 inputs and
+ * output, fp32 accumulation, fp32 epilogue and a single rounding to bf16.
+ *
+ * Reference interface replaced by this ABI (paths inside MagiCompiler):
+ *   - the body of a custom op registered through
+ *     magi_compiler/_magi_register_custom_op.py:168-204 (the decorated Python
+ *     function is what the dispatcher finally calls; here that body is one call
+ *     of magi_swiglu_forward_bf16);
+ *   - the arithmetic of TransformerMLP.forward's gate/up part,
+ *     tests/model_definition.py:336-339, and FeedForward.forward,
+ *     example/training/llama3.py:172-173;
+ *   - the calling style follows magi_compiler/cuda/cudart.py:24-62 (a ctypes
+ *     call into a shared library with plain pointers and sizes).
+ *
+ * All pointers are raw device pointers owned by the caller.  No entry point
+ * allocates device memory, synchronises the device or reads device memory on
+ * the host, except where stated (magi_swiglu_device_status).
+ *
+ * Return convention: 0 = ok; negative = argument rejected on the host, nothing
+ * was launched; positive = a CUDA runtime/driver error code.  The text of the
+ * last error of the calling thread is available from magi_swiglu_last_error().
+ */
+#ifndef MAGI_SWIGLU_H_
+#define MAGI_SWIGLU_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MAGI_SWIGLU_ABI_VERSION 1
+
+/* variant selector of magi_swiglu_forward_bf16 */
+#define MAGI_SWIGLU_VARIANT_AUTO   0  /* M <= 128 -> STREAM, else MMA            */
+#define MAGI_SWIGLU_VARIANT_MMA    1  /* persistent tcgen05 tile kernel          */
+#define MAGI_SWIGLU_VARIANT_STREAM 2  /* weight-streaming schedule for small M   */
+#define MAGI_SWIGLU_VARIANT_SIMT   3  /* plain CUDA-core kernel, validation only */
+
+/* host-side argument errors (negative return values) */
+#define MAGI_SWIGLU_ERR_NULL       -1  /* null pointer                                */
+#define MAGI_SWIGLU_ERR_SHAPE      -2  /* M/N/K/ld out of range or inconsistent       */
+#define MAGI_SWIGLU_ERR_ALIGN      -3  /* pointer or stride not 16-byte aligned       */
+#define MAGI_SWIGLU_ERR_VARIANT    -4  /* unknown variant, or variant cannot run shape */
+#define MAGI_SWIGLU_ERR_DEVICE     -5  /* device is not compute capability 10.0       */
+#define MAGI_SWIGLU_ERR_DRIVER     -6  /* tensor-map encoder unavailable / failed     */
+
+/* ABI version of the loaded library (== MAGI_SWIGLU_ABI_VERSION).
+ * Replaces: nothing in the reference; lets the Python host refuse a stale build. */
+int magi_swiglu_version(void);
+
+/* 1 iff `device` exists and is compute capability 10.0 (B200, sm_100a), else 0.
+ * Replaces: the implicit "is CUDA available" assumption of the reference's
+ * custom-op bodies (tests/api_tests/test_register_custom_op.py run on any device). */
+int magi_swiglu_supported(int device);
+
+/* The fused op.  x is [M,K] with row stride ldx, w_gate_up is [2N,K] with row
+ * stride ldw (rows 0..N-1 = gate, N..2N-1 = up), y is [M,N] with row stride ldy;
+ * strides are in elements.  Requirements: K % 8 == 0, N % 8 == 0,
+ * ldx/ldw/ldy % 8 == 0, all three base pointers 16-byte aligned, M >= 0.
+ * M == 0 is a successful no-op.  The kernel is enqueued on `cuda_stream`
+ * (a cudaStream_t; NULL = legacy default stream) of `device` and the call
+ * returns without waiting for it.
+ * Replaces: gate = F.silu(gate_proj(x)); up = up_proj(x); gate * up
+ * (tests/model_definition.py:337-339) on the packed weight. */
+int magi_swiglu_forward_bf16(const void* x, const void* w_gate_up, void* y,
+                             int64_t M, int64_t N, int64_t K,
+                             int64_t ldx, int64_t ldw, int64_t ldy,
+                             int device, void* cuda_stream, int variant);
+
+/* Same as magi_swiglu_forward_bf16 with explicit schedule knobs, for tuning
+ * sweeps and tests: block_n = output columns per tile (multiple of 16, 16..256;
+ * 0 = heuristic), stages = shared-memory pipeline depth (0 = as many as fit),
+ * group_m = row-tiles per rasterisation band (0 = heuristic), max_ctas = cap on
+ * the persistent grid (0 = one per SM).
+ * Replaces: nothing in the reference (the reference has no kernel to tune). */
+int magi_swiglu_forward_bf16_ex(const void* x, const void* w_gate_up, void* y,
+                                int64_t M, int64_t N, int64_t K,
+                                int64_t ldx, int64_t ldw, int64_t ldy,
+                                int device, void* cuda_stream, int variant,
+                                int block_n, int stages, int group_m, int max_ctas);
+
+/* Describes the schedule magi_swiglu_forward_bf16_ex would use, without
+ * launching: out[0]=variant, out[1]=block_n, out[2]=stages, out[3]=grid CTAs,
+ * out[4]=tiles, out[5]=dynamic shared memory bytes, out[6]=accumulator buffers,
+ * out[7]=MMAs per K=16 step.  `sm_count` <= 0 means "query `device`".
+ * Needs no GPU when sm_count > 0.
+ * Replaces: nothing in the reference. */
+int magi_swiglu_plan(int64_t M, int64_t N, int64_t K, int variant,
+                     int block_n, int stages, int group_m, int max_ctas,
+                     int device, int sm_count, int32_t out[8]);
+
+/* Reads (and clears) the device-side watchdog word of `device`.  Every wait in
+ * the kernels is bounded; a wait that expires records
+ * out[0]=code (0 = none; 1 = producer, 2 = mma issuer, 3 = epilogue),
+ * out[1]=block index, out[2]=pipeline stage or accumulator buffer, out[3]=phase.
+ * This call SYNCHRONISES the device; it is for tests and debugging.
+ * Replaces: nothing in the reference. */
+int magi_swiglu_device_status(int device, int32_t out[4]);
+
+/* Text of the last error returned to the calling thread ("" if none).
+ * Replaces: the Python exception text a reference custom-op body would raise. */
+const char* magi_swiglu_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MAGI_SWIGLU_H_ */

@@ -1,0 +1,23 @@
+"""B200-native fused GEMM-SwiGLU for MagiCompiler: ``Y = silu(X·Wg^T) * (X·Wu^T)`` from one packed weight.
+
+Importing the package registers the custom op ``magi_swiglu::gemm_swiglu`` (process-wide, once).  Import it
+before a model is decorated with ``magi_compile`` so the op is a graph split point for that model, and
+before ahead-of-time artifacts that mention the op are deserialised.
+"""
+from ._loader import MagiSwigluLibraryError, build_library, device_status, load_library, plan  # noqa: F401
+from .ops import OP_NAME, gemm_swiglu, gemm_swiglu_out  # noqa: F401
+from .register import COMPUTE_SENSITIVE_OPS, SPLITTING_OPS, magi_register_custom_op  # noqa: F401
+from .sharding import (  # noqa: F401
+    ColumnParallelSwiGLU,
+    TensorParallelSwiGLUMLP,
+    pack_gate_up,
+    shard_bounds,
+    shard_down,
+    shard_gate_up,
+)
+
+__all__ = [
+    "gemm_swiglu", "gemm_swiglu_out", "OP_NAME", "pack_gate_up", "shard_gate_up", "shard_down", "shard_bounds",
+    "ColumnParallelSwiGLU", "TensorParallelSwiGLUMLP", "magi_register_custom_op", "SPLITTING_OPS",
+    "COMPUTE_SENSITIVE_OPS", "build_library", "load_library", "plan", "device_status", "MagiSwigluLibraryError",
+]

@@ -1,0 +1,633 @@
+// Fused GEMM-SwiGLU for B200 (sm_100a):  Y = silu(X·Wg^T) * (X·Wu^T),  W = [Wg ; Wu] packed along rows.
+//
+// One warp-specialised kernel serves both schedules the host picks between:
+//   MMA    (large M): persistent CTAs walk 128 x block_n output tiles in a banded raster; the fp32
+//          accumulators for gate and up (2*block_n tensor-memory columns) are double-buffered so the
+//          epilogue of tile i overlaps the MMAs of tile i+1.
+//   STREAM (M <= 128): N is cut into at most one slab per SM (block_n up to 256 columns, any multiple
+//          of 16), so every SM streams a disjoint slice of the weight exactly once through a deep
+//          TMA ring; the run time is the time to read W from HBM.
+// Data path of both: TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) -> shared memory ->
+// tcgen05.mma (bf16 x bf16 -> fp32 in tensor memory) -> tcgen05.ld -> silu(g)*u in fp32 -> one
+// rounding to bf16 -> 16-byte global stores.  The 2N-wide intermediate never exists in HBM.
+//
+// Warp roles (256 threads): warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane),
+// warp 2 = tensor-memory allocator, warps 4..7 = epilogue (warp w reads TMEM lanes 32*(w%4)..+31).
+//
+// Every wait on an mbarrier is bounded: after kWaitLimitCycles the waiting role records itself in
+// g_watchdog, raises a CTA-wide abort flag and all roles fall through to the common teardown, which
+// frees tensor memory.  No wait in this file can spin forever.
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/magi_swiglu.h"
+#include "ptx_sm100.cuh"
+
+namespace magi {
+
+constexpr int kBM = 128;             // rows of X per tile = tensor-memory lanes
+constexpr int kBK = 64;              // K elements per pipeline stage = one 128-byte swizzle row
+constexpr int kThreads = 256;
+constexpr int kMaxStages = 12;
+constexpr int kTmemCols = 512;       // whole tensor memory of the SM (one CTA per SM)
+constexpr uint32_t kABytes = kBM * kBK * 2;
+constexpr int kSmemLimit = 232448 - 1024;  // dynamic part of the 227 KB opt-in maximum (static barriers take the rest)
+constexpr int kSmemFloor = 120 * 1024;  // keeps a second CTA off the SM (it would block in tcgen05.alloc)
+constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
+
+__device__ unsigned int g_watchdog[4];  // {role that gave up, block, stage/buffer, parity}
+
+struct KArgs {
+  __nv_bfloat16* y;
+  long long ldy;
+  int M, N;
+  int block_n;        // output columns per tile
+  int num_m_tiles, num_n_tiles, num_k_blocks;
+  int group_m;        // row-tiles per raster band
+  int stages;
+  uint32_t stage_bytes;
+  int n_mma;          // 1: one MMA of N = 2*block_n covers gate|up;  2: one MMA each
+  int acc_bufs;       // tensor-memory accumulator buffers (2 = epilogue overlaps next tile)
+  int w_evict_first;  // STREAM: weight tiles are read once, mark them evict-first in L2
+};
+
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned role,
+                                             unsigned idx) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  unsigned spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 255u) == 0u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *abort_flag = 1;
+        if (atomicCAS(&g_watchdog[0], 0u, role) == 0u) {
+          g_watchdog[1] = blockIdx.x;
+          g_watchdog[2] = idx;
+          g_watchdog[3] = parity;
+        }
+        return false;
+      }
+    }
+  }
+}
+
+// Banded raster: tiles are numbered band by band (group_m row-tiles per band); inside a band the
+// row-tile index runs fastest, so the CTAs of one wave share a few X row-panels and W column-panels in L2.
+__device__ __forceinline__ void tile_coords(const KArgs& a, int t, int& mt, int& nt) {
+  const int per_band = a.group_m * a.num_n_tiles;
+  const int band = t / per_band;
+  const int first_m = band * a.group_m;
+  const int rows = min(a.group_m, a.num_m_tiles - first_m);
+  const int r = t - band * per_band;
+  mt = first_m + r % rows;
+  nt = r / rows;
+}
+
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  // silu(g) = g / (1 + exp(-g)); ex2.approx + div.approx are far below bf16 resolution
+  return __fdividef(g, 1.0f + __expf(-g)) * u;
+}
+
+__device__ __forceinline__ void store8(__nv_bfloat16* dst, const uint32_t* g, const uint32_t* u) {
+  uint4 v;
+  __nv_bfloat162 p;
+  p = __floats2bfloat162_rn(silu_mul(__uint_as_float(g[0]), __uint_as_float(u[0])),
+                            silu_mul(__uint_as_float(g[1]), __uint_as_float(u[1])));
+  v.x = *reinterpret_cast<uint32_t*>(&p);
+  p = __floats2bfloat162_rn(silu_mul(__uint_as_float(g[2]), __uint_as_float(u[2])),
+                            silu_mul(__uint_as_float(g[3]), __uint_as_float(u[3])));
+  v.y = *reinterpret_cast<uint32_t*>(&p);
+  p = __floats2bfloat162_rn(silu_mul(__uint_as_float(g[4]), __uint_as_float(u[4])),
+                            silu_mul(__uint_as_float(g[5]), __uint_as_float(u[5])));
+  v.z = *reinterpret_cast<uint32_t*>(&p);
+  p = __floats2bfloat162_rn(silu_mul(__uint_as_float(g[6]), __uint_as_float(u[6])),
+                            silu_mul(__uint_as_float(g[7]), __uint_as_float(u[7])));
+  v.w = *reinterpret_cast<uint32_t*>(&p);
+  *reinterpret_cast<uint4*>(dst) = v;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const KArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * kMaxStages + 4];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  // 128-byte-swizzled tiles must start on 1024-byte boundaries
+  const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (kMaxStages + s); };
+  auto acc_full_bar = [&](int b) { return bar0 + 8u * (2 * kMaxStages + b); };
+  auto acc_empty_bar = [&](int b) { return bar0 + 8u * (2 * kMaxStages + 2 + b); };
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < a.stages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full_bar(b), 1);
+      mbar_init(acc_empty_bar(b), 4);  // lane 0 of each epilogue warp
+    }
+    fence_barrier_init();
+    prefetch_tensormap(&tm_x);
+    prefetch_tensormap(&tm_w);
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(&tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_slot;
+
+  const int num_tiles = a.num_m_tiles * a.num_n_tiles;
+  const int acc_cols = 2 * a.block_n;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const uint64_t w_policy = l2_policy_evict_first();
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int mt, nt;
+        tile_coords(a, t, mt, nt);
+        for (int kb = 0; kb < a.num_k_blocks; ++kb) {
+          if (!wait_bounded(empty_bar(stage), phase ^ 1u, &abort_flag, 1u, stage)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(full_bar(stage), a.stage_bytes);
+          const uint32_t sa = tiles_base + stage * a.stage_bytes;
+          tma_load_2d(sa, &tm_x, full_bar(stage), kb * kBK, mt * kBM);
+          if (a.w_evict_first)
+            tma_load_3d_hint(sa + kABytes, &tm_w, full_bar(stage), kb * kBK, nt * a.block_n, 0, w_policy);
+          else
+            tma_load_3d(sa + kABytes, &tm_w, full_bar(stage), kb * kBK, nt * a.block_n, 0);
+          if (++stage == a.stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t mma_n = (a.n_mma == 1) ? 2u * a.block_n : (uint32_t)a.block_n;
+      const uint32_t idesc = umma_idesc_bf16(kBM, mma_n);
+      const uint32_t up_tile_bytes = (uint32_t)a.block_n * 128u;  // gate rows, then up rows, 128 B each
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+        const int buf = (a.acc_bufs == 2) ? (it & 1) : 0;
+        const uint32_t acc_phase = (a.acc_bufs == 2) ? ((it >> 1) & 1) : (it & 1);
+        if (!wait_bounded(acc_empty_bar(buf), acc_phase ^ 1u, &abort_flag, 2u, 16 + buf)) break;
+        tc_fence_after_sync();
+        const uint32_t d_gate = tmem_base + (uint32_t)(buf * acc_cols);
+        for (int kb = 0; kb < a.num_k_blocks; ++kb) {
+          if (!wait_bounded(full_bar(stage), phase, &abort_flag, 2u, stage)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = tiles_base + stage * a.stage_bytes;
+          const uint32_t sb = sa + kABytes;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint32_t acc = (kb | k) != 0;
+            const uint64_t ad = umma_desc_k_sw128(sa + k * 32);
+            umma_bf16(d_gate, ad, umma_desc_k_sw128(sb + k * 32), idesc, acc);
+            if (a.n_mma == 2)
+              umma_bf16(d_gate + a.block_n, ad, umma_desc_k_sw128(sb + up_tile_bytes + k * 32), idesc, acc);
+          }
+          umma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+          if (++stage == a.stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) umma_commit(acc_full_bar(buf));
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------ epilogue
+    const int q = warp & 3;
+    int it = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+      const int buf = (a.acc_bufs == 2) ? (it & 1) : 0;
+      const uint32_t acc_phase = (a.acc_bufs == 2) ? ((it >> 1) & 1) : (it & 1);
+      int mt, nt;
+      tile_coords(a, t, mt, nt);
+      bool ok = wait_bounded(acc_full_bar(buf), acc_phase, &abort_flag, 3u, buf);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+
+      const int row = mt * kBM + q * 32 + lane;
+      const bool row_ok = row < a.M;
+      const int col0 = nt * a.block_n;
+      const int valid = min(a.block_n, a.N - col0);  // multiple of 8
+      const uint32_t t_gate = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * acc_cols);
+      const uint32_t t_up = t_gate + (uint32_t)a.block_n;
+      __nv_bfloat16* yrow = a.y + (long long)row * a.ldy + col0;
+
+      int c = 0;
+      for (; c + 32 <= a.block_n && c < valid; c += 32) {
+        uint32_t g[32], u[32];
+        tmem_ld_x32(t_gate + c, g);
+        tmem_ld_x32(t_up + c, u);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (c + 8 * j + 8 <= valid) store8(yrow + c + 8 * j, g + 8 * j, u + 8 * j);
+        }
+      }
+      if (c < a.block_n && c < valid) {  // block_n % 32 == 16
+        uint32_t g[16], u[16];
+        tmem_ld_x16(t_gate + c, g);
+        tmem_ld_x16(t_up + c, u);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+            if (c + 8 * j + 8 <= valid) store8(yrow + c + 8 * j, g + 8 * j, u + 8 * j);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+    }
+  }
+
+  // ------------------------------------------------------------ teardown (also the abort path)
+  __syncwarp();
+  if (*reinterpret_cast<volatile int*>(&abort_flag)) {
+    // give copies and MMAs that may still be in flight time to land before tensor memory is freed
+    const long long t0 = clock64();
+    while (clock64() - t0 < 4000000LL) {
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// Plain CUDA-core kernel: one thread per output, 16x16 outputs per block, K staged through shared
+// memory in slices of 32.  Same arithmetic contract (fp32 accumulate, one rounding).  Validation only.
+__global__ void __launch_bounds__(256)
+swiglu_simt_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                   __nv_bfloat16* __restrict__ y, int M, int N, int K, long long ldx, long long ldw, long long ldy) {
+  __shared__ float xs[16][33], gs[16][33], us[16][33];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int row0 = blockIdx.y * 16, col0 = blockIdx.x * 16;
+  float accg = 0.f, accu = 0.f;
+  for (int k0 = 0; k0 < K; k0 += 32) {
+    for (int i = threadIdx.x; i < 16 * 32; i += 256) {
+      const int r = i >> 5, k = i & 31;
+      const bool kin = (k0 + k) < K;
+      xs[r][k] = (kin && row0 + r < M) ? __bfloat162float(x[(long long)(row0 + r) * ldx + k0 + k]) : 0.f;
+      gs[r][k] = (kin && col0 + r < N) ? __bfloat162float(w[(long long)(col0 + r) * ldw + k0 + k]) : 0.f;
+      us[r][k] = (kin && col0 + r < N) ? __bfloat162float(w[(long long)(N + col0 + r) * ldw + k0 + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+      accg = fmaf(xs[ty][k], gs[tx][k], accg);
+      accu = fmaf(xs[ty][k], us[tx][k], accu);
+    }
+    __syncthreads();
+  }
+  const int row = row0 + ty, col = col0 + tx;
+  if (row < M && col < N) y[(long long)row * ldy + col] = __float2bfloat16_rn(accg / (1.0f + expf(-accg)) * accu);
+}
+
+// ================================================================== host side
+thread_local char g_err[512] = "";
+
+static int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+static int fail_cuda(cudaError_t e, const char* what) {
+  snprintf(g_err, sizeof(g_err), "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+  return e == cudaSuccess ? 1 : (int)e;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn tensor_map_encoder() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess) return (EncodeTiledFn) nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+constexpr int kMaxDevices = 64;
+struct DeviceInfo {
+  int queried = 0;  // 1 = ok, -1 = unusable
+  int sm_count = 0;
+  int cc_major = 0, cc_minor = 0;
+  int smem_optin_set = 0;
+};
+static DeviceInfo g_dev[kMaxDevices];
+static std::mutex g_dev_mutex;
+
+static const DeviceInfo* device_info(int device) {
+  if (device < 0 || device >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  DeviceInfo& d = g_dev[device];
+  if (d.queried == 0) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || device >= n) {
+      cudaGetLastError();
+      d.queried = -1;
+    } else {
+      cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device);
+      cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, device);
+      cudaDeviceGetAttribute(&d.cc_minor, cudaDevAttrComputeCapabilityMinor, device);
+      d.queried = 1;
+    }
+  }
+  return d.queried == 1 ? &d : nullptr;
+}
+
+struct Plan {
+  int variant, block_n, stages, grid, tiles, smem_bytes, acc_bufs, n_mma;
+  int num_m_tiles, num_n_tiles, num_k_blocks, group_m;
+  uint32_t stage_bytes;
+};
+
+static inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+static int make_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, int stages, int group_m, int max_ctas,
+                     int sm_count, Plan* p) {
+  if (M < 0 || N <= 0 || K <= 0 || M > 0x7fffff00LL || N > 0x3fffff00LL || K > 0x7fffff00LL)
+    return fail(MAGI_SWIGLU_ERR_SHAPE, "shape out of range: M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
+  if (N % 8 != 0 || K % 8 != 0)
+    return fail(MAGI_SWIGLU_ERR_SHAPE, "N (%lld) and K (%lld) must be multiples of 8", (long long)N, (long long)K);
+  if (variant == MAGI_SWIGLU_VARIANT_AUTO) variant = (M <= 128) ? MAGI_SWIGLU_VARIANT_STREAM : MAGI_SWIGLU_VARIANT_MMA;
+  if (variant != MAGI_SWIGLU_VARIANT_MMA && variant != MAGI_SWIGLU_VARIANT_STREAM && variant != MAGI_SWIGLU_VARIANT_SIMT)
+    return fail(MAGI_SWIGLU_ERR_VARIANT, "unknown variant %d", variant);
+  if (sm_count <= 0) return fail(MAGI_SWIGLU_ERR_DEVICE, "sm_count must be positive");
+  memset(p, 0, sizeof(*p));
+  p->variant = variant;
+  if (variant == MAGI_SWIGLU_VARIANT_SIMT) {
+    p->block_n = 16;
+    p->tiles = (int)(((M + 15) / 16) * ((N + 15) / 16));
+    p->grid = p->tiles;
+    return 0;
+  }
+  if (variant == MAGI_SWIGLU_VARIANT_STREAM && M > kBM)
+    return fail(MAGI_SWIGLU_ERR_VARIANT, "STREAM variant needs M <= %d (got %lld)", kBM, (long long)M);
+  const int ctas = (max_ctas > 0 && max_ctas < sm_count) ? max_ctas : sm_count;
+  if (block_n == 0) {
+    if (variant == MAGI_SWIGLU_VARIANT_MMA) {
+      block_n = (N >= 128) ? 128 : round_up((int)N, 16);
+    } else {
+      // one slab per SM if it fits in tensor memory (gate + up <= 512 fp32 columns)
+      int64_t per = (N + ctas - 1) / ctas;
+      block_n = round_up((int)(per < 16 ? 16 : per), 16);
+      if (block_n > 256) block_n = 256;
+    }
+  }
+  if (block_n < 16 || block_n > 256 || block_n % 16 != 0)
+    return fail(MAGI_SWIGLU_ERR_VARIANT, "block_n=%d must be a multiple of 16 in [16,256]", block_n);
+  p->block_n = block_n;
+  p->n_mma = (2 * block_n <= 256) ? 1 : 2;
+  p->acc_bufs = (4 * block_n <= kTmemCols) ? 2 : 1;
+  p->stage_bytes = kABytes + 2u * (uint32_t)block_n * 128u;
+  const int fit = (kSmemLimit - 1024) / (int)p->stage_bytes;
+  int max_stages = fit < kMaxStages ? fit : kMaxStages;
+  if (stages == 0) stages = max_stages;
+  if (stages < 2 || stages > max_stages)
+    return fail(MAGI_SWIGLU_ERR_VARIANT, "stages=%d out of range [2,%d] for block_n=%d", stages, max_stages, block_n);
+  p->stages = stages;
+  int smem = stages * (int)p->stage_bytes + 1024;
+  p->smem_bytes = smem < kSmemFloor ? kSmemFloor : smem;
+  p->num_m_tiles = (int)((M + kBM - 1) / kBM);
+  p->num_n_tiles = (int)((N + block_n - 1) / block_n);
+  p->num_k_blocks = (int)((K + kBK - 1) / kBK);
+  if ((int64_t)p->num_m_tiles * p->num_n_tiles > 0x7fffffffLL) return fail(MAGI_SWIGLU_ERR_SHAPE, "too many tiles");
+  p->tiles = p->num_m_tiles * p->num_n_tiles;
+  if (group_m <= 0) group_m = 16;
+  p->group_m = group_m;
+  p->grid = p->tiles < ctas ? p->tiles : ctas;
+  return 0;
+}
+
+static int encode_maps(const void* x, const void* w, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw,
+                       int block_n, CUtensorMap* tm_x, CUtensorMap* tm_w) {
+  EncodeTiledFn enc = tensor_map_encoder();
+  if (!enc) return fail(MAGI_SWIGLU_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from the driver");
+  {
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)kBM};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(MAGI_SWIGLU_ERR_DRIVER, "tensor map for X rejected by the driver (CUresult %d)", (int)r);
+  }
+  {
+    // W viewed as [2][N][K]: one box brings block_n gate rows and the matching block_n up rows
+    const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)N, 2};
+    const cuuint64_t strides[2] = {(cuuint64_t)ldw * 2, (cuuint64_t)N * (cuuint64_t)ldw * 2};
+    const cuuint32_t box[3] = {(cuuint32_t)kBK, (cuuint32_t)block_n, 2};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(tm_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(w), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(MAGI_SWIGLU_ERR_DRIVER, "tensor map for W rejected by the driver (CUresult %d)", (int)r);
+  }
+  return 0;
+}
+
+struct DeviceGuard {
+  int prev = -1;
+  bool changed = false;
+  cudaError_t set(int device) {
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) return e;
+    if (prev != device) {
+      e = cudaSetDevice(device);
+      changed = (e == cudaSuccess);
+    }
+    return e;
+  }
+  ~DeviceGuard() {
+    if (changed) cudaSetDevice(prev);
+  }
+};
+
+static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int64_t ldx,
+                        int64_t ldw, int64_t ldy, int device, void* stream_v, int variant, int block_n, int stages,
+                        int group_m, int max_ctas) {
+  g_err[0] = 0;
+  if (M == 0 && N > 0 && K > 0) return 0;
+  if (!x || !w || !y) return fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
+  if (ldx < K || ldw < K || ldy < N)
+    return fail(MAGI_SWIGLU_ERR_SHAPE, "row strides too small: ldx=%lld ldw=%lld (K=%lld) ldy=%lld (N=%lld)",
+                (long long)ldx, (long long)ldw, (long long)K, (long long)ldy, (long long)N);
+  if (ldx % 8 || ldw % 8 || ldy % 8) return fail(MAGI_SWIGLU_ERR_ALIGN, "row strides must be multiples of 8 elements");
+  if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15u)
+    return fail(MAGI_SWIGLU_ERR_ALIGN, "x, w_gate_up and y must be 16-byte aligned");
+  const DeviceInfo* di = device_info(device);
+  if (!di) return fail(MAGI_SWIGLU_ERR_DEVICE, "device %d is not available", device);
+  if (di->cc_major != 10 || di->cc_minor != 0)
+    return fail(MAGI_SWIGLU_ERR_DEVICE, "device %d is sm_%d%d; this library runs on sm_100 (B200) only", device,
+                di->cc_major, di->cc_minor);
+  Plan p;
+  int rc = make_plan(M, N, K, variant, block_n, stages, group_m, max_ctas, di->sm_count, &p);
+  if (rc) return rc;
+
+  DeviceGuard guard;
+  cudaError_t e = guard.set(device);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaSetDevice");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+  if (p.variant == MAGI_SWIGLU_VARIANT_SIMT) {
+    dim3 grid((unsigned)((N + 15) / 16), (unsigned)((M + 15) / 16));
+    if (grid.y > 65535u) return fail(MAGI_SWIGLU_ERR_VARIANT, "SIMT validation kernel supports M <= 1048560");
+    swiglu_simt_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
+                                                 static_cast<const __nv_bfloat16*>(w),
+                                                 static_cast<__nv_bfloat16*>(y), (int)M, (int)N, (int)K, ldx, ldw, ldy);
+    e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : fail_cuda(e, "launch of swiglu_simt_kernel");
+  }
+
+  CUtensorMap tm_x, tm_w;
+  rc = encode_maps(x, w, M, N, K, ldx, ldw, p.block_n, &tm_x, &tm_w);
+  if (rc) return rc;
+
+  {
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    DeviceInfo& d = g_dev[device];
+    if (!d.smem_optin_set) {
+      e = cudaFuncSetAttribute(swiglu_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+      if (e != cudaSuccess) return fail_cuda(e, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize)");
+      d.smem_optin_set = 1;
+    }
+  }
+
+  KArgs a;
+  a.y = static_cast<__nv_bfloat16*>(y);
+  a.ldy = ldy;
+  a.M = (int)M;
+  a.N = (int)N;
+  a.block_n = p.block_n;
+  a.num_m_tiles = p.num_m_tiles;
+  a.num_n_tiles = p.num_n_tiles;
+  a.num_k_blocks = p.num_k_blocks;
+  a.group_m = p.group_m;
+  a.stages = p.stages;
+  a.stage_bytes = p.stage_bytes;
+  a.n_mma = p.n_mma;
+  a.acc_bufs = p.acc_bufs;
+  a.w_evict_first = (p.variant == MAGI_SWIGLU_VARIANT_STREAM) ? 1 : 0;
+
+  swiglu_tc_kernel<<<p.grid, kThreads, p.smem_bytes, stream>>>(tm_x, tm_w, a);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : fail_cuda(e, "launch of swiglu_tc_kernel");
+}
+
+}  // namespace magi
+
+// ================================================================== C ABI
+extern "C" {
+
+int magi_swiglu_version(void) { return MAGI_SWIGLU_ABI_VERSION; }
+
+int magi_swiglu_supported(int device) {
+  const magi::DeviceInfo* di = magi::device_info(device);
+  return (di && di->cc_major == 10 && di->cc_minor == 0) ? 1 : 0;
+}
+
+int magi_swiglu_forward_bf16(const void* x, const void* w_gate_up, void* y, int64_t M, int64_t N, int64_t K,
+                             int64_t ldx, int64_t ldw, int64_t ldy, int device, void* cuda_stream, int variant) {
+  return magi::forward_impl(x, w_gate_up, y, M, N, K, ldx, ldw, ldy, device, cuda_stream, variant, 0, 0, 0, 0);
+}
+
+int magi_swiglu_forward_bf16_ex(const void* x, const void* w_gate_up, void* y, int64_t M, int64_t N, int64_t K,
+                                int64_t ldx, int64_t ldw, int64_t ldy, int device, void* cuda_stream, int variant,
+                                int block_n, int stages, int group_m, int max_ctas) {
+  return magi::forward_impl(x, w_gate_up, y, M, N, K, ldx, ldw, ldy, device, cuda_stream, variant, block_n, stages,
+                            group_m, max_ctas);
+}
+
+int magi_swiglu_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, int stages, int group_m, int max_ctas,
+                     int device, int sm_count, int32_t out[8]) {
+  magi::g_err[0] = 0;
+  if (!out) return magi::fail(MAGI_SWIGLU_ERR_NULL, "out is null");
+  if (sm_count <= 0) {
+    const magi::DeviceInfo* di = magi::device_info(device);
+    if (!di) return magi::fail(MAGI_SWIGLU_ERR_DEVICE, "device %d is not available", device);
+    sm_count = di->sm_count;
+  }
+  magi::Plan p;
+  int rc = magi::make_plan(M, N, K, variant, block_n, stages, group_m, max_ctas, sm_count, &p);
+  if (rc) return rc;
+  out[0] = p.variant;
+  out[1] = p.block_n;
+  out[2] = p.stages;
+  out[3] = p.grid;
+  out[4] = p.tiles;
+  out[5] = p.smem_bytes;
+  out[6] = p.acc_bufs;
+  out[7] = p.n_mma;
+  return 0;
+}
+
+int magi_swiglu_device_status(int device, int32_t out[4]) {
+  magi::g_err[0] = 0;
+  if (!out) return magi::fail(MAGI_SWIGLU_ERR_NULL, "out is null");
+  if (!magi::device_info(device)) return magi::fail(MAGI_SWIGLU_ERR_DEVICE, "device %d is not available", device);
+  magi::DeviceGuard guard;
+  cudaError_t e = guard.set(device);
+  if (e != cudaSuccess) return magi::fail_cuda(e, "cudaSetDevice");
+  e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return magi::fail_cuda(e, "cudaDeviceSynchronize");
+  unsigned int host[4] = {0, 0, 0, 0};
+  e = cudaMemcpyFromSymbol(host, magi::g_watchdog, sizeof(host));
+  if (e != cudaSuccess) return magi::fail_cuda(e, "cudaMemcpyFromSymbol(g_watchdog)");
+  for (int i = 0; i < 4; ++i) out[i] = (int32_t)host[i];
+  if (host[0] != 0) {
+    const unsigned int zero[4] = {0, 0, 0, 0};
+    e = cudaMemcpyToSymbol(magi::g_watchdog, zero, sizeof(zero));
+    if (e != cudaSuccess) return magi::fail_cuda(e, "cudaMemcpyToSymbol(g_watchdog)");
+  }
+  return 0;
+}
+
+const char* magi_swiglu_last_error(void) { return magi::g_err; }
+
+}  // extern "C"

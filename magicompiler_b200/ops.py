@@ -1,0 +1,114 @@
+"""``magi_swiglu::gemm_swiglu`` — the fused GEMM-SwiGLU custom op, registered the MagiCompiler way.
+
+    y = gemm_swiglu(x, w_gate_up)      y[..., n] = silu(x · Wg[n]) * (x · Wu[n])
+
+``w_gate_up`` is ``[2N, K]`` = ``cat([gate_proj.weight, up_proj.weight])`` (``nn.Linear`` layout, gate
+rows first), replacing ``F.silu(self.gate_proj(x)) * self.up_proj(x)`` of the reference's
+``TransformerMLP`` (tests/model_definition.py:332-339) and ``F.silu(self.w1(x)) * self.w3(x)`` of its
+Llama example (example/training/llama3.py:168-173).
+
+Registration follows ``magi_compiler/_magi_register_custom_op.py:168-204``: functional
+(``mutates_args=()``), callable fake impl that works with a symbolic row count, marked as a graph split
+point and as compute-sensitive.  The body validates its arguments on the host, allocates the output
+with ``torch.empty`` (capture-aware caching allocator) and makes ONE call into the C-ABI library on
+torch's current stream: no synchronisation, no host read, no allocation inside the library — so it can
+run on a side stream, under an offload executor and inside CUDA-graph capture
+(magi_compiler/magi_backend/cuda_graph_mgr.py:465-473, 548-569).
+
+Dtype rules (enforced before any launch): x and w_gate_up are bf16 CUDA tensors on the same device;
+the output is bf16 on that device.  There is no fp16/fp32 path, no CPU path and no fallback.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _loader
+from .register import magi_register_custom_op
+
+OP_NAME = "magi_swiglu::gemm_swiglu"
+
+
+def _check(x: torch.Tensor, w: torch.Tensor) -> tuple[int, int, int]:
+    if not isinstance(x, torch.Tensor) or not isinstance(w, torch.Tensor):
+        raise TypeError("gemm_swiglu expects two tensors")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise TypeError(f"gemm_swiglu computes in bf16 only; got x {x.dtype}, w_gate_up {w.dtype}")
+    if w.dim() != 2:
+        raise ValueError(f"w_gate_up must be 2-D [2N, K]; got shape {tuple(w.shape)}")
+    if x.dim() < 1:
+        raise ValueError("x must have at least one dimension [..., K]")
+    if w.shape[0] % 2 != 0:
+        raise ValueError(f"w_gate_up has {w.shape[0]} rows; it must hold N gate rows followed by N up rows")
+    K = x.shape[-1]
+    N = w.shape[0] // 2
+    if w.shape[1] != K:
+        raise ValueError(f"inner dimensions differ: x[..., {K}] vs w_gate_up[{w.shape[0]}, {w.shape[1]}]")
+    if K == 0 or N == 0:
+        raise ValueError("K and N must be positive")
+    if K % 8 != 0 or N % 8 != 0:
+        raise ValueError(f"K ({K}) and N ({N}) must be multiples of 8 (16-byte rows for TMA and vector stores)")
+    if not x.is_cuda or not w.is_cuda:
+        raise TypeError("gemm_swiglu runs on CUDA tensors only (there is no CPU implementation)")
+    if x.device != w.device:
+        raise ValueError(f"x is on {x.device} but w_gate_up is on {w.device}")
+    M = x.numel() // K
+    return M, N, K
+
+
+def _rows_view(t: torch.Tensor, cols: int) -> torch.Tensor:
+    """2-D view with unit inner stride, 8-element-aligned row stride and a 16-byte-aligned base (copy if not)."""
+    t2 = t.reshape(-1, cols)
+    ok = t2.stride(1) == 1 and (t2.shape[0] <= 1 or (t2.stride(0) >= cols and t2.stride(0) % 8 == 0)) \
+        and t2.data_ptr() % 16 == 0
+    return t2 if ok else t2.contiguous()
+
+
+def gemm_swiglu_out(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor | None = None, *,
+                    variant: str | int = "auto", block_n: int = 0, stages: int = 0, group_m: int = 0,
+                    max_ctas: int = 0) -> torch.Tensor:
+    """The op's body with the schedule knobs of ``magi_swiglu_forward_bf16_ex`` exposed (tests, tuning)."""
+    M, N, K = _check(x, w_gate_up)
+    lib = _loader.load_library()
+    x2 = _rows_view(x, K)
+    w2 = _rows_view(w_gate_up, K)
+    if w2.data_ptr() != w_gate_up.data_ptr() and w_gate_up.numel() > 0:
+        # a copy of the weight on every call would double the op's HBM traffic
+        raise ValueError("w_gate_up must have unit inner stride, a row stride that is a multiple of 8 and a "
+                         "16-byte-aligned base; pack it once with magicompiler_b200.pack_gate_up")
+    out_shape = (*x.shape[:-1], N)
+    if out is None:
+        y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    else:
+        if out.dtype != torch.bfloat16 or out.device != x.device or tuple(out.shape) != tuple(out_shape):
+            raise ValueError("out must be a bf16 tensor of the output shape on x's device")
+        y = out.reshape(M, N)
+        if y.data_ptr() != out.data_ptr() or y.stride(1) != 1 or y.stride(0) % 8 != 0 or y.data_ptr() % 16 != 0:
+            raise ValueError("out must be row-contiguous with a 16-byte-aligned base")
+    if M == 0:
+        return y.view(out_shape)
+    v = _loader.VARIANTS[variant] if isinstance(variant, str) else int(variant)
+    dev = x.device.index if x.device.index is not None else torch.cuda.current_device()
+    stream = torch.cuda.current_stream(x.device).cuda_stream
+    ldx = x2.stride(0) if M > 1 else K
+    rc = lib.magi_swiglu_forward_bf16_ex(x2.data_ptr(), w2.data_ptr(), y.data_ptr(), M, N, K, ldx, w2.stride(0),
+                                         y.stride(0), dev, stream, v, block_n, stages, group_m, max_ctas)
+    if rc != 0:
+        msg = f"magi_swiglu_forward_bf16 failed ({rc}): {_loader.last_error()}"
+        raise (ValueError(msg) if rc < 0 else RuntimeError(msg))
+    return y.view(out_shape)
+
+
+def _gemm_swiglu_meta(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    # shape/dtype/device only; works with a symbolic leading dimension
+    return x.new_empty((*x.shape[:-1], w_gate_up.shape[0] // 2))
+
+
+@magi_register_custom_op(
+    name=OP_NAME,
+    mutates_args=(),
+    infer_output_meta_fn=_gemm_swiglu_meta,
+    is_compute_sensitive=True,
+    is_subgraph_boundary=True,
+)
+def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    return gemm_swiglu_out(x, w_gate_up)

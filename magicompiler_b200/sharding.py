@@ -1,0 +1,111 @@
+"""Column sharding of the packed gate/up weight across the GPUs of one box, and the row-parallel
+down-projection that closes a full SwiGLU MLP.
+
+Layout follows the reference's Llama example (example/training/llama3.py:168-170): ``w1``/``w3`` are
+column-parallel with ``gather_output=False`` (rank r owns output columns ``[r*N/P, (r+1)*N/P)``), ``w2``
+is row-parallel with ``input_is_parallel=True`` (rank r owns the matching input columns and the partial
+products are summed with one all-reduce).  The fused op needs no collective: rank r multiplies the
+replicated activations by its own packed shard ``cat(Wg[rows_r], Wu[rows_r])``.  No GPU ever reads
+another GPU's memory; the only exchange is the NCCL all-reduce after the down-projection.
+"""
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+
+def pack_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """``[N,K]`` gate_proj.weight and ``[N,K]`` up_proj.weight -> packed ``[2N,K]`` (gate rows first), contiguous."""
+    if w_gate.shape != w_up.shape or w_gate.dim() != 2:
+        raise ValueError(f"gate {tuple(w_gate.shape)} and up {tuple(w_up.shape)} must be equal 2-D shapes")
+    if w_gate.dtype != w_up.dtype or w_gate.device != w_up.device:
+        raise ValueError("gate and up weights must share dtype and device")
+    return torch.cat([w_gate, w_up], dim=0).contiguous()
+
+
+def shard_bounds(n: int, rank: int, world: int, multiple: int = 8) -> tuple[int, int]:
+    """Half-open column range of rank ``rank``; every shard is a multiple of ``multiple`` columns."""
+    if world < 1 or not (0 <= rank < world):
+        raise ValueError(f"bad rank/world: {rank}/{world}")
+    if n % (world * multiple) != 0:
+        raise ValueError(f"N={n} cannot be cut into {world} shards that are multiples of {multiple}")
+    per = n // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_gate_up(w_gate_up: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """Rank ``rank``'s packed shard ``[2*N/P, K]`` of a packed ``[2N,K]`` weight (a copy, made once at load)."""
+    if w_gate_up.dim() != 2 or w_gate_up.shape[0] % 2:
+        raise ValueError("w_gate_up must be [2N, K]")
+    n = w_gate_up.shape[0] // 2
+    lo, hi = shard_bounds(n, rank, world)
+    return torch.cat([w_gate_up[lo:hi], w_gate_up[n + lo:n + hi]], dim=0).contiguous()
+
+
+def shard_down(w_down: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """Rank ``rank``'s input-column shard ``[K_out, N/P]`` of down_proj.weight ``[K_out, N]``."""
+    lo, hi = shard_bounds(w_down.shape[1], rank, world)
+    return w_down[:, lo:hi].contiguous()
+
+
+def _default_swiglu() -> Callable:
+    from .ops import gemm_swiglu
+
+    return gemm_swiglu
+
+
+class ColumnParallelSwiGLU(torch.nn.Module):
+    """Gate/up projection + SwiGLU of one rank: ``[..., K] -> [..., N/P]``, no communication."""
+
+    def __init__(self, w_gate_up_full: torch.Tensor, rank: int = 0, world: int = 1,
+                 swiglu_fn: Callable | None = None):
+        super().__init__()
+        self.rank, self.world = rank, world
+        self.weight = torch.nn.Parameter(shard_gate_up(w_gate_up_full, rank, world), requires_grad=False)
+        self._fn = swiglu_fn
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        fn = self._fn or _default_swiglu()
+        return fn(x, self.weight)
+
+
+class TensorParallelSwiGLUMLP(torch.nn.Module):
+    """Full SwiGLU MLP over ``world`` ranks: fused column-parallel gate/up, row-parallel down, one all-reduce.
+
+    ``chunks`` > 1 cuts the rows into that many slices and all-reduces slice i asynchronously while slice
+    i+1 is computed, so the NVLink transfer hides behind the GEMMs.
+    """
+
+    def __init__(self, w_gate_up_full: torch.Tensor, w_down_full: torch.Tensor, rank: int = 0, world: int = 1,
+                 group=None, chunks: int = 1, swiglu_fn: Callable | None = None):
+        super().__init__()
+        self.rank, self.world, self.group, self.chunks = rank, world, group, max(1, int(chunks))
+        self.gate_up = ColumnParallelSwiGLU(w_gate_up_full, rank, world, swiglu_fn)
+        self.w_down = torch.nn.Parameter(shard_down(w_down_full, rank, world), requires_grad=False)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        m = x2.shape[0]
+        out = torch.empty((m, self.w_down.shape[0]), dtype=self.w_down.dtype, device=x.device)
+        step = -(-m // self.chunks) if m else 0
+        works = []
+        for lo in range(0, m, step or 1):
+            hi = min(m, lo + step)
+            h = self.gate_up(x2[lo:hi])
+            torch.matmul(h, self.w_down.t(), out=out[lo:hi])  # plain library GEMM: partial sums of this rank
+            if self.world > 1:
+                works.append(dist.all_reduce(out[lo:hi], op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+        for wk in works:
+            wk.wait()
+        return out.view(*lead, self.w_down.shape[0])
+
+
+def reference_mlp(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
+    """Unsharded eager MLP, the expression of the reference's TransformerMLP.forward
+    (tests/model_definition.py:336-339) on the packed weight; used by tests as the comparison point."""
+    n = w_gate_up.shape[0] // 2
+    return F.linear(F.silu(F.linear(x, w_gate_up[:n])) * F.linear(x, w_gate_up[n:]), w_down)

@@ -1,0 +1,129 @@
+"""TEST INFRASTRUCTURE — Python face of the CPU oracle (see ``oracle/__init__.py``).
+
+The arithmetic follows MagiCompiler's eager SwiGLU, ``F.silu(gate_proj(x)) * up_proj(x)``
+(tests/model_definition.py:337-339; same expression in example/training/llama3.py:173), evaluated on
+one packed weight ``W[2N,K] = [gate_proj.weight ; up_proj.weight]``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+_HERE = Path(__file__).resolve().parent
+_SRC = _HERE / "swiglu_oracle.c"
+_SO = _HERE / "_build" / "libswiglu_oracle.so"
+_lib = None
+
+# Tolerance of the path, stated against the fp32-accumulated gold (bf16 output, K up to 8192):
+#   max|y - gold| / max|gold| <= 1e-2   and   ||y - gold||_F / ||gold||_F <= 5e-3.
+# Element-wise relative error is not usable: the reference's own eager result reaches 0.2 on tiny outputs.
+TOL_MAX_NORM = 1e-2
+TOL_FROB = 5e-3
+
+
+def build(force: bool = False) -> Path:
+    """Compile the C oracle with gcc (baseline x86-64 code, no fused multiply-add contraction)."""
+    if force or not _SO.exists() or _SO.stat().st_mtime < _SRC.stat().st_mtime:
+        _SO.parent.mkdir(parents=True, exist_ok=True)
+        cmd = ["gcc", "-O2", "-ffp-contract=off", "-fPIC", "-shared", "-o", str(_SO), str(_SRC), "-lm", "-lpthread"]
+        subprocess.run(cmd, check=True)
+    return _SO
+
+
+def _load():
+    global _lib
+    if _lib is None:
+        build()
+        lib = ctypes.CDLL(str(_SO))
+        lib.oracle_swiglu.restype = ctypes.c_int
+        lib.oracle_swiglu.argtypes = [ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int64] * 5 + [
+            ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]
+        lib.oracle_f32_to_bf16.restype = ctypes.c_uint16
+        lib.oracle_f32_to_bf16.argtypes = [ctypes.c_float]
+        lib.oracle_bf16_to_f32.restype = ctypes.c_float
+        lib.oracle_bf16_to_f32.argtypes = [ctypes.c_uint16]
+        _lib = lib
+    return _lib
+
+
+def to_bits(t: torch.Tensor) -> np.ndarray:
+    """bf16 tensor -> uint16 numpy array of its bit patterns (CPU copy)."""
+    assert t.dtype == torch.bfloat16
+    return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def from_bits(a: np.ndarray) -> torch.Tensor:
+    """uint16 bit patterns -> bf16 tensor."""
+    return torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).view(torch.bfloat16)
+
+
+def make_inputs(M: int, K: int, N: int, seed: int = 0, with_down: bool = False):
+    """The benchmark's synthetic inputs: CPU generator, X ~ N(0,1), W ~ N(0,0.02), both cast to bf16.
+
+    Returns (x[M,K], w[2N,K]) or (x, w, w_down[K,N]); gate rows first in w.
+    """
+    g = torch.Generator(device="cpu")
+    g.manual_seed(seed)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * N, K, generator=g) * 0.02).to(torch.bfloat16)
+    if with_down:
+        wd = (torch.randn(K, N, generator=g) * 0.02).to(torch.bfloat16)
+        return x, w, wd
+    return x, w
+
+
+def swiglu_gold(x: torch.Tensor, w: torch.Tensor, threads: int | None = None, want_eager: bool = True):
+    """C oracle.  x [M,K] bf16, w [2N,K] bf16 (CPU).  Returns dict with
+    ``gold`` (fp32 [M,N]), ``gold_bf16`` (bf16, gold rounded once), ``eager`` (bf16, reference rounding chain)."""
+    lib = _load()
+    assert x.dim() == 2 and w.dim() == 2 and w.shape[0] % 2 == 0 and x.shape[1] == w.shape[1]
+    M, K = x.shape
+    N = w.shape[0] // 2
+    xb, wb = to_bits(x), to_bits(w)
+    gold = np.empty((M, N), dtype=np.float32)
+    gold_bf16 = np.empty((M, N), dtype=np.uint16)
+    eager = np.empty((M, N), dtype=np.uint16) if want_eager else None
+    if threads is None:
+        threads = min(os.cpu_count() or 1, 16)
+    rc = lib.oracle_swiglu(xb.ctypes.data, wb.ctypes.data, M, N, K, K, K, gold.ctypes.data, gold_bf16.ctypes.data,
+                           eager.ctypes.data if want_eager else None, threads)
+    assert rc == 0
+    out = {"gold": torch.from_numpy(gold), "gold_bf16": from_bits(gold_bf16)}
+    if want_eager:
+        out["eager"] = from_bits(eager)
+    return out
+
+
+def swiglu_gold_numpy(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """fp32 gold in numpy (bf16 values are exact in fp32; products are summed in fp32 by BLAS)."""
+    N = w.shape[0] // 2
+    xf = x.float().numpy()
+    wf = w.float().numpy()
+    h = xf @ wf.T
+    g, u = h[:, :N], h[:, N:]
+    return torch.from_numpy((g / (1.0 + np.exp(-g))) * u)
+
+
+def swiglu_ref_eager(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """The reference's eager expression, literally, with gate_proj.weight = w[:N], up_proj.weight = w[N:]."""
+    N = w.shape[0] // 2
+    return F.silu(F.linear(x, w[:N])) * F.linear(x, w[N:])
+
+
+def error_metrics(y: torch.Tensor, gold: torch.Tensor) -> dict:
+    """Normalised error of y (any dtype) against the fp32 gold."""
+    yf = y.detach().float().cpu()
+    gf = gold.detach().float().cpu()
+    diff = (yf - gf)
+    gmax = gf.abs().max().item()
+    return {
+        "max_norm": (diff.abs().max().item() / gmax) if gmax > 0 else diff.abs().max().item(),
+        "frob": (diff.norm().item() / gf.norm().item()) if gmax > 0 else diff.norm().item(),
+        "gold_absmax": gmax,
+    }

@@ -1,0 +1,116 @@
+"""The C-ABI library loads without a GPU, exports every symbol the header declares, plans schedules and
+rejects bad arguments on the host (no launch)."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+from magicompiler_b200 import _loader
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = ROOT / "include" / "magi_swiglu.h"
+
+
+@pytest.fixture(scope="module")
+def lib():
+    _loader.build_library()
+    return _loader.load_library()
+
+
+def _declared_functions():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(magi_swiglu_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(lib):
+    names = _declared_functions()
+    assert {"magi_swiglu_version", "magi_swiglu_supported", "magi_swiglu_forward_bf16", "magi_swiglu_forward_bf16_ex",
+            "magi_swiglu_plan", "magi_swiglu_device_status", "magi_swiglu_last_error"} <= set(names)
+    for n in names:
+        assert hasattr(lib, n), n
+
+
+def test_every_declaration_cites_what_it_replaces():
+    text = HEADER.read_text()
+    for n in _declared_functions():
+        decl = re.search(r"^(?:int|const char\*)\s+" + n + r"\(", text, re.M).start()
+        comment = text[:decl].rsplit("/*", 1)[1]
+        assert "Replaces:" in comment or "no counterpart in the reference" in comment, n
+
+
+def test_version_matches_header(lib):
+    v = int(re.search(r"#define MAGI_SWIGLU_ABI_VERSION (\d+)", HEADER.read_text()).group(1))
+    assert lib.magi_swiglu_version() == v == _loader.ABI_VERSION
+
+
+def test_supported_is_false_without_a_b200(lib):
+    import torch
+
+    if not torch.cuda.is_available():
+        assert lib.magi_swiglu_supported(0) == 0
+    assert lib.magi_swiglu_supported(-1) == 0 and lib.magi_swiglu_supported(1000) == 0
+
+
+def test_plan_for_the_benchmark_configs():
+    p = _loader.plan(8192, 14336, 4096, sm_count=148)  # Llama-3-8B FFN
+    assert p["variant"] == _loader.VARIANT_MMA and p["grid"] == 148 and p["block_n"] % 16 == 0
+    assert p["tiles"] == -(-8192 // 128) * -(-14336 // p["block_n"])
+    assert p["smem_bytes"] <= 232448 and p["stages"] >= 3
+    p = _loader.plan(32760, 13824, 5120, sm_count=148)  # video-DiT FFN, ragged M
+    assert p["variant"] == _loader.VARIANT_MMA and p["tiles"] == 256 * -(-13824 // p["block_n"])
+    for M in (16, 64, 128):  # decode shapes: one slab of W per SM, a single wave
+        p = _loader.plan(M, 28672, 8192, sm_count=148)
+        assert p["variant"] == _loader.VARIANT_STREAM
+        assert p["tiles"] == p["grid"] <= 148 and p["tiles"] * p["block_n"] >= 28672
+        assert 2 * p["block_n"] <= 512
+    p = _loader.plan(129, 2816, 1024, sm_count=148)
+    assert p["variant"] == _loader.VARIANT_MMA
+    for shard in (14336, 7168, 3584):  # column shards of the decode weight at 2/4/8 GPUs
+        p = _loader.plan(64, shard, 8192, sm_count=148)
+        assert p["tiles"] <= 148 * 2
+
+
+def test_plan_respects_explicit_knobs_and_rejects_bad_ones():
+    p = _loader.plan(4096, 4096, 4096, variant="mma", block_n=64, stages=3, max_ctas=10, sm_count=148)
+    assert (p["block_n"], p["stages"], p["grid"], p["acc_bufs"], p["n_mma"]) == (64, 3, 10, 2, 1)
+    p = _loader.plan(4096, 4096, 4096, variant="mma", block_n=256, sm_count=148)
+    assert (p["acc_bufs"], p["n_mma"]) == (1, 2)
+    for bad in (dict(block_n=24), dict(block_n=272), dict(stages=1), dict(stages=13), dict(variant=9)):
+        with pytest.raises(ValueError):
+            _loader.plan(4096, 4096, 4096, sm_count=148, **{"variant": "mma", **bad})
+    with pytest.raises(ValueError):
+        _loader.plan(256, 4096, 4096, variant="stream", sm_count=148)  # STREAM is for M <= 128
+    with pytest.raises(ValueError):
+        _loader.plan(16, 100, 64, sm_count=148)  # N % 8
+    with pytest.raises(ValueError):
+        _loader.plan(16, 64, 100, sm_count=148)  # K % 8
+
+
+def test_forward_rejects_bad_arguments_before_touching_a_device(lib):
+    buf = (ctypes.c_char * 4096)()
+    base = ctypes.addressof(buf)
+    base += (-base) % 16
+    fwd = lib.magi_swiglu_forward_bf16
+
+    def call(x=base, w=base, y=base, M=8, N=8, K=8, ldx=8, ldw=8, ldy=8, dev=0, variant=0):
+        return fwd(x, w, y, M, N, K, ldx, ldw, ldy, dev, None, variant)
+
+    assert call(x=None) == -1 and "null" in _loader.last_error()
+    assert call(ldx=4) == -2          # row stride shorter than K
+    assert call(ldy=12) == -3         # stride not a multiple of 8 elements
+    assert call(x=base + 2) == -3     # misaligned pointer
+    assert call(M=0) == 0             # empty batch: successful no-op, nothing launched
+    assert call(dev=1000) == -5 and "device" in _loader.last_error()
+    import torch
+
+    if not torch.cuda.is_available():
+        assert call() == -5           # valid arguments, but no sm_100 device: refused, never a CPU fallback
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_loader, "_lib", None)
+    monkeypatch.setattr(_loader, "LIB_PATH", tmp_path / "libmagi_swiglu.so")
+    monkeypatch.delenv("MAGI_SWIGLU_AUTOBUILD", raising=False)
+    with pytest.raises(_loader.MagiSwigluLibraryError):
+        _loader.load_library()

@@ -1,0 +1,206 @@
+"""Parity of the CUDA path against the CPU oracle, the reference fixtures and size-independent properties.
+Every case goes through the C-ABI library (directly with ctypes, or through the registered op, which is one
+ctypes call).  Tolerance of the path (bf16 output, fp32 accumulation), against the fp32-accumulated gold:
+    max|y-gold|/max|gold| <= 1e-2,  ||y-gold||_F/||gold||_F <= 5e-3,  allclose(rtol=1e-2, atol=1e-2*max|gold|)."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import magicompiler_b200 as mb
+from magicompiler_b200 import _loader
+from oracle import TOL_FROB, TOL_MAX_NORM, error_metrics, from_bits, make_inputs, swiglu_gold, to_bits
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _require_b200():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    lib = _loader.load_library()  # raises if the CUDA library was not built: there is no fallback to pass on
+    assert lib.magi_swiglu_supported(0) == 1, "device 0 is not sm_100"
+    yield
+    st = mb.device_status(0)
+    assert st["code"] == 0, f"a kernel wait timed out during the tests: {st}"
+
+
+def assert_parity(y, gold, what=""):
+    m = error_metrics(y, gold)
+    assert m["max_norm"] <= TOL_MAX_NORM and m["frob"] <= TOL_FROB, (what, m)
+    assert torch.allclose(y.float().cpu(), gold.float().cpu(), rtol=1e-2, atol=1e-2 * m["gold_absmax"]), (what, m)
+    return m
+
+
+def gold_fp32_gpu(x, w):
+    """fp32 gold on the GPU for sizes the CPU oracle would take minutes for (TF32 off)."""
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        n = w.shape[0] // 2
+        h = x.float() @ w.float().t()
+        return torch.nn.functional.silu(h[:, :n]) * h[:, n:]
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
+# ---------------------------------------------------------------- small cases against the CPU oracle
+def test_c_abi_direct_call_cfg1():
+    """Reference-sized case (256 x 1024 x 2816, seed 0) through the bare C entry point."""
+    lib = _loader.load_library()
+    x, w = make_inputs(256, 1024, 2816, seed=0)
+    xd, wd = x.cuda(), w.cuda()
+    y = torch.empty(256, 2816, dtype=torch.bfloat16, device="cuda")
+    rc = lib.magi_swiglu_forward_bf16(xd.data_ptr(), wd.data_ptr(), y.data_ptr(), 256, 2816, 1024, 1024, 1024, 2816,
+                                      0, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), 0)
+    assert rc == 0, _loader.last_error()
+    torch.cuda.synchronize()
+    o = swiglu_gold(x, w)
+    m = assert_parity(y, o["gold"], "cfg1")
+    # a single-rounded result must be at least as close to the gold as the reference's own eager chain
+    assert m["frob"] <= error_metrics(o["eager"], o["gold"])["frob"] * 1.05
+
+
+@pytest.mark.parametrize("name", ["tiny_48x128x96", "ragged_37x200x72", "mid_130x512x264", "cfg1_256x1024x2816"])
+@pytest.mark.parametrize("variant", ["auto", "mma", "simt"])
+def test_against_reference_fixture(golden, name, variant):
+    M, K, N, seed, step = (int(v) for v in golden[name + "/shape"])
+    if name + "/x" in golden.files:
+        x, w = from_bits(golden[name + "/x"]), from_bits(golden[name + "/w"])
+    else:
+        x, w = make_inputs(M, K, N, seed=seed)
+    y = mb.gemm_swiglu_out(x.cuda(), w.cuda(), variant=variant).cpu()
+    ref = from_bits(golden[name + "/y_eager"]).float()  # what MagiCompiler's TransformerMLP produced
+    m = error_metrics(y[::step], ref)
+    assert m["max_norm"] <= TOL_MAX_NORM and m["frob"] <= TOL_FROB, m
+    assert_parity(y, swiglu_gold(x, w, want_eager=False)["gold"], name)
+
+
+SHAPES = [  # (M, N, K): tails in every dimension, single-tile and multi-tile
+    (1, 8, 8), (1, 64, 64), (16, 128, 64), (17, 72, 200), (64, 264, 128), (120, 136, 72), (128, 128, 1024),
+    (129, 128, 64), (255, 192, 136), (256, 8, 64), (300, 520, 328), (515, 1000, 96), (33, 2816, 64),
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("variant", ["auto", "mma", "stream"])
+def test_ragged_shapes(shape, variant):
+    M, N, K = shape
+    if variant == "stream" and M > 128:
+        pytest.skip("STREAM schedule is for M <= 128")
+    x, w = make_inputs(M, K, N, seed=M + N + K)
+    y = mb.gemm_swiglu_out(x.cuda(), w.cuda(), variant=variant)
+    assert_parity(y, swiglu_gold(x, w, want_eager=False)["gold"], f"{shape} {variant}")
+
+
+@pytest.mark.parametrize("block_n", [16, 32, 48, 64, 96, 112, 128, 144, 208, 256])
+@pytest.mark.parametrize("stages,max_ctas,group_m", [(0, 0, 0), (2, 1, 1), (3, 5, 2)])
+def test_schedule_knobs(block_n, stages, max_ctas, group_m):
+    """Every tile width (one or two MMAs per step, one or two accumulator buffers), shallow pipelines and a
+    single persistent CTA walking all tiles (many barrier phase wraps) give the same answer."""
+    M, N, K = 300, 528, 320
+    x, w = make_inputs(M, K, N, seed=block_n)
+    y = mb.gemm_swiglu_out(x.cuda(), w.cuda(), variant="mma", block_n=block_n, stages=stages, max_ctas=max_ctas,
+                           group_m=group_m)
+    base = mb.gemm_swiglu_out(x.cuda(), w.cuda(), variant="mma")
+    assert_parity(y, swiglu_gold(x, w, want_eager=False)["gold"], f"bn={block_n}")
+    # the K loop order per output is the same for every schedule, so the bits are too
+    assert torch.equal(y, base)
+
+
+def test_guard_bands_strides_and_determinism():
+    M, N, K = 200, 264, 136
+    x, w = make_inputs(M, K, N, seed=77)
+    ldx, ldw, ldy = K + 8, K + 16, N + 24
+    xb = torch.full((M + 2, ldx), float("nan"), dtype=torch.bfloat16, device="cuda")
+    wb = torch.full((2 * N + 2, ldw), float("nan"), dtype=torch.bfloat16, device="cuda")
+    yb = torch.full((M + 4, ldy), 123.0, dtype=torch.bfloat16, device="cuda")
+    xv, wv, yv = xb[1:M + 1, :K], wb[1:2 * N + 1, :K], yb[2:M + 2, :N]
+    xv.copy_(x)
+    wv.copy_(w)
+    lib = _loader.load_library()
+    runs = []
+    for variant in (1, 1, 3):
+        rc = lib.magi_swiglu_forward_bf16(xv.data_ptr(), wv.data_ptr(), yv.data_ptr(), M, N, K, ldx, ldw, ldy, 0,
+                                          ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), variant)
+        assert rc == 0, _loader.last_error()
+        torch.cuda.synchronize()
+        got = yv.clone()
+        assert_parity(got, swiglu_gold(x, w, want_eager=False)["gold"], "strided")
+        # nothing outside [M,N] was written: NaN padding of the inputs never leaked in, guard values intact
+        assert (yb[:2] == 123.0).all() and (yb[M + 2:] == 123.0).all() and (yb[:, N:] == 123.0).all()
+        runs.append(got)
+    assert torch.equal(runs[0], runs[1]), "two runs of the same launch differ"
+
+
+def test_empty_and_noncontiguous_inputs():
+    x, w = make_inputs(64, 128, 96, seed=5)
+    xd, wd = x.cuda(), w.cuda()
+    assert mb.gemm_swiglu(xd[:0], wd).shape == (0, 96)
+    y = mb.gemm_swiglu(xd.view(4, 16, 128), wd)
+    assert y.shape == (4, 16, 96)
+    base = mb.gemm_swiglu(xd, wd)
+    assert torch.equal(y.view(64, 96), base)
+    xt = xd.t().contiguous().t()  # column-major view: the wrapper must copy, not mis-read
+    assert torch.equal(mb.gemm_swiglu(xt, wd), base)
+    with pytest.raises(ValueError):
+        mb.gemm_swiglu(xd, wd.t().contiguous().t())  # the weight is never silently copied
+    with pytest.raises(TypeError):
+        mb.gemm_swiglu(xd.half(), wd.half())
+
+
+def test_special_values():
+    M, N, K = 32, 64, 64
+    x = torch.zeros(M, K, dtype=torch.bfloat16)
+    w = torch.zeros(2 * N, K, dtype=torch.bfloat16)
+    x[:, 0] = 1.0
+    w[:N, 0] = torch.linspace(-120, 120, N).to(torch.bfloat16)  # gate pre-activations from -120 to 120
+    w[N:, 0] = 3.0
+    y = mb.gemm_swiglu(x.cuda(), w.cuda()).cpu()
+    g = w[:N, 0].float()
+    exp = (torch.nn.functional.silu(g) * 3.0).expand(M, N)
+    assert torch.isfinite(y.float()).all()
+    assert torch.allclose(y.float(), exp, rtol=1e-2, atol=1e-6)
+
+
+# ---------------------------------------------------------------- benchmark sizes: properties + sampled gold
+@pytest.mark.parametrize("M", [16, 64, 128])
+def test_decode_shapes_full_size(M):
+    """Decode-shaped weight streaming at full size (K=8192, N=28672) against the fp32 gold on the GPU."""
+    x, w = make_inputs(M, 8192, 28672, seed=0)
+    xd, wd = x.cuda(), w.cuda()
+    y = mb.gemm_swiglu(xd, wd)
+    assert_parity(y, gold_fp32_gpu(xd, wd), f"decode M={M}")
+    assert torch.equal(y, mb.gemm_swiglu_out(xd, wd, variant="mma")), "both schedules accumulate in the same order"
+
+
+def test_llama_ffn_full_size_properties():
+    """8192 x 4096 x 14336: sampled rows against fp32 gold; exact scaling, permutation and shard properties."""
+    M, K, N = 8192, 4096, 14336
+    x, w = make_inputs(M, K, N, seed=0)
+    xd, wd = x.cuda(), w.cuda()
+    y = mb.gemm_swiglu(xd, wd)
+    rows = torch.randperm(M, generator=torch.Generator().manual_seed(1))[:384].cuda()
+    assert_parity(y[rows], gold_fp32_gpu(xd[rows], wd), "llama ffn sample")
+    # (1) doubling the up weights doubles every output exactly (power-of-two scaling commutes with rounding)
+    w2 = wd.clone()
+    w2[N:] *= 2
+    assert torch.equal(mb.gemm_swiglu(xd, w2), y * 2)
+    # (2) permuting the rows of X permutes the rows of Y bit for bit (no dependence on tile position)
+    perm = torch.randperm(M, generator=torch.Generator().manual_seed(2)).cuda()
+    assert torch.equal(mb.gemm_swiglu(xd[perm].contiguous(), wd), y[perm])
+    # (3) column shards are independent units: 8 shards side by side are the unsharded result bit for bit
+    parts = [mb.gemm_swiglu(xd, mb.shard_gate_up(wd, r, 8)) for r in range(8)]
+    assert torch.equal(torch.cat(parts, dim=1), y)
+
+
+def test_video_dit_ffn_sampled():
+    """32760 x 5120 x 13824 (ragged M): sampled rows incl. the last partial tile against fp32 gold."""
+    M, K, N = 32760, 5120, 13824
+    x, w = make_inputs(M, K, N, seed=0)
+    xd, wd = x.cuda(), w.cuda()
+    y = mb.gemm_swiglu(xd, wd)
+    rows = torch.cat([torch.arange(M - 130, M), torch.randperm(M - 130, generator=torch.Generator().manual_seed(3))[:254]]).cuda()
+    assert_parity(y[rows], gold_fp32_gpu(xd[rows], wd), "video dit sample")
+    shard = mb.shard_gate_up(wd, 7, 8)  # 1728 columns: 13.5 tiles of 128
+    assert torch.equal(mb.gemm_swiglu(xd, shard), y[:, 7 * 1728:])

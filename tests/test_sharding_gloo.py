@@ -1,0 +1,138 @@
+"""Column sharding of the packed weight and the row-parallel MLP, on CPU: shard algebra in-process and the
+multi-rank path as two gloo ranks.  The kernel is replaced by the CPU oracle here (this is a test); what is
+under test is the host logic around it — packing, shard bounds, chunked all-reduce, failure behaviour."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from magicompiler_b200 import (ColumnParallelSwiGLU, TensorParallelSwiGLUMLP, pack_gate_up, shard_bounds,
+                               shard_down, shard_gate_up)
+from magicompiler_b200.sharding import reference_mlp
+from oracle import make_inputs, swiglu_gold
+
+
+def _oracle_fn(x, w):
+    return swiglu_gold(x.reshape(-1, x.shape[-1]).contiguous(), w, threads=2, want_eager=False)["gold_bf16"].view(
+        *x.shape[:-1], w.shape[0] // 2)
+
+
+def test_pack_and_shard_algebra():
+    x, w = make_inputs(8, 64, 96, seed=3)
+    n = 96
+    assert torch.equal(pack_gate_up(w[:n], w[n:]), w)
+    with pytest.raises(ValueError):
+        pack_gate_up(w[:n], w[n:n + 8])
+    for world in (1, 2, 4):
+        cols = []
+        for r in range(world):
+            lo, hi = shard_bounds(n, r, world)
+            s = shard_gate_up(w, r, world)
+            assert s.shape == (2 * (hi - lo), 64) and s.is_contiguous()
+            assert torch.equal(s[: hi - lo], w[lo:hi]) and torch.equal(s[hi - lo:], w[n + lo:n + hi])
+            cols.append(_oracle_fn(x, s))
+        # shards are independent units: concatenating their outputs IS the unsharded result, bit for bit
+        assert torch.equal(torch.cat(cols, dim=1), _oracle_fn(x, w))
+    with pytest.raises(ValueError):
+        shard_bounds(96, 0, 5)       # 96 columns cannot be cut into 5 shards of multiples of 8
+    with pytest.raises(ValueError):
+        shard_bounds(96, 2, 2)
+    wd = torch.randn(64, n)
+    assert torch.equal(torch.cat([shard_down(wd, r, 4) for r in range(4)], dim=1), wd)
+
+
+def test_single_rank_modules_match_reference_mlp():
+    x, w, wd = make_inputs(24, 64, 96, seed=4, with_down=True)
+    col = ColumnParallelSwiGLU(w, swiglu_fn=_oracle_fn)
+    assert torch.equal(col(x), _oracle_fn(x, w))
+    mlp = TensorParallelSwiGLUMLP(w, wd, chunks=3, swiglu_fn=_oracle_fn)
+    got = mlp(x.view(2, 12, 64))
+    ref = reference_mlp(x, w, wd).view(2, 12, 64)
+    assert got.shape == ref.shape
+    assert torch.allclose(got.float(), ref.float(), rtol=2e-2, atol=2e-2 * ref.float().abs().max().item())
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, chunks, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.set_num_threads(1)
+        x, w, wd = make_inputs(40, 64, 96, seed=9, with_down=True)  # same seed on every rank: X replicated
+        # column-parallel op: no collective; gathering the shards reproduces the full output
+        y_r = ColumnParallelSwiGLU(w, rank, world, swiglu_fn=_oracle_fn)(x)
+        parts = [torch.empty_like(y_r) for _ in range(world)]
+        dist.all_gather(parts, y_r)
+        full = _oracle_fn(x, w)
+        ok_cols = torch.equal(torch.cat(parts, dim=1), full)
+        # full MLP: row-parallel down-projection + (chunked, asynchronous) all-reduce; fp32 so the sum is order-free enough
+        mlp = TensorParallelSwiGLUMLP(w, wd.float(), rank, world, chunks=chunks,
+                                      swiglu_fn=lambda a, b: _oracle_fn(a, b).float())
+        z = mlp(x)
+        ref = torch.matmul(full.float(), wd.float().t())
+        ok_mlp = torch.allclose(z, ref, rtol=1e-4, atol=1e-4)
+        q.put((rank, ok_cols, ok_mlp, list(z.shape)))
+    except Exception as exc:  # report instead of leaving the parent to time out
+        q.put((rank, False, False, [repr(exc)]))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("chunks", [1, 3])
+def test_two_gloo_ranks_column_shards_and_row_parallel_allreduce(chunks):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, chunks, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert [r[0] for r in res] == [0, 1]
+    for _, ok_cols, ok_mlp, shape in res:
+        assert ok_cols and ok_mlp and shape == [40, 64]
+
+
+def _failing_rank(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import datetime
+
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    try:
+        if rank == 1:
+            q.put((rank, "left"))  # leaves between steps, nothing in flight
+            return
+        t = torch.ones(4)
+        try:
+            dist.all_reduce(t)
+            q.put((rank, "no-error"))
+        except Exception as exc:  # the survivor learns of the loss as a host-side error, not a hang
+            q.put((rank, "error:" + type(exc).__name__))
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def test_rank_loss_surfaces_as_host_error():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_rank, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+    assert res[1] == "left" and res[0].startswith("error:"), res

@@ -1,0 +1,386 @@
+#!/usr/bin/env python
+"""Benchmark of the fused GEMM-SwiGLU path:  python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+A step is one pass of the op over one batch of synthetic input (CPU generator, seed 0, X ~ N(0,1),
+W ~ N(0,0.02), bf16).  Default workload: the Llama-3-8B-shaped FFN up-projection, X[8192,4096] x
+W[2*14336,4096] -> Y[8192,14336].  On N > 1 GPUs the packed weight is column-sharded along N (rank r
+owns N/P gate and N/P up rows), X is replicated and no collective is on the data path; the job's work is
+the whole problem, so scaling is "strong".
+
+Timing: W warm-up steps, then exactly K steps, each bracketed by its own pair of CUDA events on the launch
+stream with an L2 flush (256 MiB memset) before it; a barrier and a device synchronise surround the timed
+region; the per-rank sum of the K step times is reduced with MAX over ranks.  SM clocks and throttle
+reasons are sampled with nvidia-smi (read-only) while the steps run.
+
+One JSON line is printed by rank 0.  `value` is device-resident throughput; `e2e` is the same metric with
+the step's X copied from pinned host memory and its Y copied back inside the timed region; `roofline`
+describes the kernel against the measured peak of this GPU pool; `cpu_baseline` times the reference's eager
+PyTorch expression on the host cores on a bounded slice of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: (M, K, N, bound, description)
+    "llama3_8b_ffn": (8192, 4096, 14336, "tensor", "Llama-3-8B-shaped FFN up-projection X[8192,4096] W[2x14336,4096]"),
+    "video_dit_ffn": (32760, 5120, 13824, "tensor", "video-DiT-shaped FFN X[32760,5120] W[2x13824,5120]"),
+    "decode_m16": (16, 8192, 28672, "hbm", "decode-shaped weight streaming X[16,8192] W[2x28672,8192]"),
+    "decode_m64": (64, 8192, 28672, "hbm", "decode-shaped weight streaming X[64,8192] W[2x28672,8192]"),
+    "decode_m128": (128, 8192, 28672, "hbm", "decode-shaped weight streaming X[128,8192] W[2x28672,8192]"),
+    "cpu_ref_case": (256, 1024, 2816, "tensor", "reference CPU-sized case X[256,1024] W[2x2816,1024]"),
+}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+L2_FLUSH_BYTES = 256 << 20
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return json.loads(p.read_text()), "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+def flops_of(M, K, N):
+    return 2.0 * M * K * 2 * N
+
+
+def bytes_of(M, K, N):
+    return 2.0 * (M * K + 2 * N * K + M * N)
+
+
+class ClockSampler:
+    """Reads SM clock and throttle reasons with nvidia-smi while the timed region runs (never sets anything)."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, smax, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+                power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = [c for c, p in zip(sm, power) if p >= 0.5 * max(power)] or sm
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": max(power)}
+
+
+def cpu_eager_tflops(M, K, N, x, w, target_s=12.0, max_rows=None):
+    """The reference's eager expression on the host cores, on the first rows of the same X (bounded sample)."""
+    from oracle import swiglu_ref_eager
+
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    rows = min(M, 256)
+    xs = x[:rows].contiguous()
+    swiglu_ref_eager(xs, w)  # warm-up (thread pool, oneDNN primitive cache)
+    t0 = time.perf_counter()
+    swiglu_ref_eager(xs, w)
+    dt = max(time.perf_counter() - t0, 1e-6)
+    # grow the slice towards ~target_s of work in total, 3 timed repetitions
+    rows2 = int(min(max_rows or M, M, max(rows, rows * (target_s / 3.0) / dt)))
+    rows2 = max(16, rows2 // 16 * 16) if M >= 16 else M
+    xs = x[:rows2].contiguous()
+    times = []
+    for _ in range(3):
+        t0 = time.perf_counter()
+        swiglu_ref_eager(xs, w)
+        times.append(time.perf_counter() - t0)
+    t = statistics.median(times)
+    return flops_of(rows2, K, N) / t / 1e12, rows2, threads, t
+
+
+def run_reference_arm(args, rank, world):
+    """--impl reference: MagiCompiler's eager SwiGLU on the host CPU (its only implementation of this path)."""
+    if rank != 0:
+        return
+    from oracle import make_inputs, swiglu_ref_eager
+
+    M, K, N, bound, desc = WORKLOADS[args.workload]
+    x, w = make_inputs(M, K, N, seed=0)
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    # one step = the expression on a bounded row-slice of the workload; size it from a probe so K+W steps take ~1-2 min
+    rows = min(M, 128)
+    swiglu_ref_eager(x[:rows], w)
+    t0 = time.perf_counter()
+    swiglu_ref_eager(x[:rows], w)
+    dt = max(time.perf_counter() - t0, 1e-6)
+    budget_per_step = 90.0 / max(1, args.steps + args.warmup)
+    rows = int(min(M, max(16, rows * budget_per_step / dt)))
+    rows = rows // 16 * 16 if rows >= 16 else rows
+    xs = x[:rows].contiguous()
+    for _ in range(args.warmup):
+        swiglu_ref_eager(xs, w)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        swiglu_ref_eager(xs, w)
+    total = time.perf_counter() - t0
+    per_step = total / args.steps
+    if bound == "hbm":
+        value, unit, metric = bytes_of(rows, K, N) / per_step / 1e9, "GB/s", "fused GEMM-SwiGLU HBM GB/s (small-M)"
+    else:
+        value, unit, metric = flops_of(rows, K, N) / per_step / 1e12, "TFLOP/s", "fused GEMM-SwiGLU TFLOP/s"
+    sample = f"eager F.silu(F.linear(x,Wg))*F.linear(x,Wu) on the first {rows} of {M} rows, full W, {threads} threads"
+    line = {
+        "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seed 0, X~N(0,1), W~N(0,0.02))",
+        "config": {"workload": args.workload, "shape": desc, "rows_per_step": rows},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="llama3_8b_ffn", choices=sorted(WORKLOADS))
+    ap.add_argument("--variant", default="auto")
+    ap.add_argument("--block-n", type=int, default=0)
+    ap.add_argument("--stages", type=int, default=0)
+    ap.add_argument("--group-m", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-flush", action="store_true", help="profiling runs only: skip the L2 flush kernels")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" and not args.no_flush else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run for N > 1")
+
+    import torch.distributed as dist
+
+    import magicompiler_b200 as mb
+    from oracle import make_inputs  # input generator only; the oracle's compute is used for cpu_baseline alone
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    lib = mb.load_library()  # raises if the CUDA library is missing: there is no fallback
+    if lib.magi_swiglu_supported(local_rank) != 1:
+        raise SystemExit("this benchmark needs a B200 (sm_100)")
+
+    M, K, N, bound, desc = WORKLOADS[args.workload]
+    x_cpu, w_cpu = make_inputs(M, K, N, seed=0)
+    w_local_cpu = mb.shard_gate_up(w_cpu, rank, world) if world > 1 else w_cpu
+    n_local = w_local_cpu.shape[0] // 2
+    x = x_cpu.to(dev)
+    w = w_local_cpu.to(dev)
+    y = torch.empty(M, n_local, dtype=torch.bfloat16, device=dev)
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+    knobs = dict(variant=args.variant, block_n=args.block_n, stages=args.stages, group_m=args.group_m)
+    plan = mb.plan(M, n_local, K, device=local_rank, **knobs)
+
+    def step():
+        mb.gemm_swiglu_out(x, w, out=y, **knobs)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # ---------------------------------------------------------------- device-resident timing
+    for _ in range(args.warmup):
+        if not args.no_flush:
+            flush.zero_()
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    barrier()
+    wall0 = time.perf_counter()
+    for i in range(args.steps):
+        if not args.no_flush:
+            flush.zero_()
+        starts[i].record()
+        step()
+        ends[i].record()
+    barrier()
+    wall = time.perf_counter() - wall0
+    step_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+    total_ms = torch.tensor([sum(step_ms)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
+    total_ms = float(total_ms.item())
+    ms_per_step = total_ms / args.steps
+    status = mb.device_status(local_rank)
+    if status["code"] != 0:
+        raise SystemExit(f"kernel watchdog fired: {status}")
+
+    # ---------------------------------------------------------------- end to end from host buffers
+    e2e = None
+    if not args.no_e2e:
+        x_host = x_cpu.pin_memory()
+        y_host = torch.empty(M, n_local, dtype=torch.bfloat16).pin_memory()
+        chunks = 4 if M >= 4096 else 1
+        rows = -(-M // chunks)
+        streams = [torch.cuda.Stream(dev) for _ in range(min(chunks, 3))]
+        x_dev = torch.empty_like(x)
+
+        def e2e_step():
+            cur = torch.cuda.current_stream(dev)
+            for c in range(chunks):
+                lo, hi = c * rows, min(M, (c + 1) * rows)
+                s = streams[c % len(streams)]
+                s.wait_stream(cur)
+                with torch.cuda.stream(s):
+                    x_dev[lo:hi].copy_(x_host[lo:hi], non_blocking=True)
+                    mb.gemm_swiglu_out(x_dev[lo:hi], w, out=y[lo:hi], **knobs)
+                    y_host[lo:hi].copy_(y[lo:hi], non_blocking=True)
+            for s in streams:
+                cur.wait_stream(s)
+
+        n_e2e = max(3, min(args.steps, 10))
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        e1.record()
+        barrier()
+        e2e_ms = torch.tensor([e0.elapsed_time(e1) / n_e2e], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+        e2e = (float(e2e_ms.item()), x_host.numel() * 2, y_host.numel() * 2, chunks)
+    clocks = sampler.stop() if rank == 0 else None
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks, peak_kind = measured_peaks()
+    flops, nbytes = flops_of(M, K, N), bytes_of(M, K, N)
+    flops_rank, bytes_rank = flops_of(M, K, n_local), bytes_of(M, K, n_local)
+    rank0_ms = sum(step_ms) / args.steps
+    if bound == "hbm":
+        metric, unit = "fused GEMM-SwiGLU HBM GB/s (small-M)", "GB/s"
+        value = nbytes / (ms_per_step * 1e-3) / 1e9
+        achieved = bytes_rank / (rank0_ms * 1e-3) / 1e9
+        peak = float(peaks["hbm_gbs"])
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": None, "peak_kind": f"{peak_kind} copy bandwidth", "nominal_frac": achieved / 8000.0}
+        e2e_scale = nbytes
+    else:
+        metric, unit = "fused GEMM-SwiGLU TFLOP/s", "TFLOP/s"
+        value = flops / (ms_per_step * 1e-3) / 1e12
+        achieved = flops_rank / (rank0_ms * 1e-3) / 1e12
+        peak = float(peaks["bf16_tflops"])
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "traffic": None, "peak_kind": f"{peak_kind} cuBLAS bf16 burst (kernel timed alone)",
+                "nominal_frac": achieved / 2250.0}
+        e2e_scale = flops
+    roof["kernel"] = "swiglu_tc_kernel"
+    roof["kernel_ms"] = rank0_ms
+    traffic_file = ROOT / "profiles" / "traffic.json"
+    if traffic_file.exists():
+        try:
+            t = json.loads(traffic_file.read_text()).get(f"{args.workload}@{world}")
+            if t:
+                roof["traffic"] = t
+        except Exception:
+            pass
+
+    line = {
+        "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (CPU generator seed 0, X~N(0,1), W~N(0,0.02), bf16)",
+        "config": {"workload": args.workload, "shape": desc, "M": M, "K": K, "N": N, "n_per_gpu": n_local,
+                   "parallelism": f"column-shard of W over {world} GPU(s), X replicated, no collective",
+                   "l2": "flushed before every timed step (256 MiB memset)" if not args.no_flush else "not flushed",
+                   "plan": plan, "wall_s_timed_region": wall},
+        "roofline": roof,
+        "gpu_launches": args.steps,
+        "clocks": clocks,
+    }
+    if e2e is not None:
+        ms, h2d, d2h, chunks = e2e
+        line["e2e"] = {"value": e2e_scale / (ms * 1e-3) / (1e9 if bound == "hbm" else 1e12), "unit": unit,
+                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms,
+                       "how": f"pinned X -> device, op, Y -> pinned host, {chunks} row chunk(s) pipelined on side streams"}
+    if world == 1 and not args.no_cpu_baseline:
+        v, rows, threads, t = cpu_eager_tflops(M, K, N, x_cpu, w_cpu)
+        if bound == "hbm":
+            v = bytes_of(rows, K, N) / t / 1e9
+        line["cpu_baseline"] = {
+            "value": v, "unit": unit, "cores": threads, "kind": "port",
+            "sample": f"reference eager expression (torch CPU, bf16) on the first {rows} of {M} rows with the full W, "
+                      f"median of 3 runs of {t:.2f} s"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -8,7 +8,7 @@ owns N/P gate and N/P up rows), X is replicated and no collective is on the data
 the whole problem, so scaling is "strong".
 
 Timing: W warm-up steps, then exactly K steps, each bracketed by its own pair of CUDA events on the launch
-stream with an L2 flush (256 MiB memset) before it; a barrier and a device synchronise surround the timed
+stream with an L2 flush (256 MiB written, then 256 MiB read, so no dirty lines remain) before it; a barrier and a device synchronise surround the timed
 region; the per-rank sum of the K step times is reduced with MAX over ranks.  SM clocks and throttle
 reasons are sampled with nvidia-smi (read-only) while the steps run.
 
@@ -231,7 +231,14 @@ def main():
     x = x_cpu.to(dev)
     w = w_local_cpu.to(dev)
     y = torch.empty(M, n_local, dtype=torch.bfloat16, device=dev)
-    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+    flush_w = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+    flush_r = torch.zeros(L2_FLUSH_BYTES // 4, dtype=torch.int32, device=dev)
+
+    def flush_l2():
+        # write a buffer larger than L2, then read another one: the timed kernel starts from an L2 that holds
+        # neither its inputs nor dirty lines whose write-back would be charged to it
+        flush_w.zero_()
+        flush_r.max()
     knobs = dict(variant=args.variant, block_n=args.block_n, stages=args.stages, group_m=args.group_m)
     plan = mb.plan(M, n_local, K, device=local_rank, **knobs)
 
@@ -246,7 +253,7 @@ def main():
     # ---------------------------------------------------------------- device-resident timing
     for _ in range(args.warmup):
         if not args.no_flush:
-            flush.zero_()
+            flush_l2()
         step()
     barrier()
     sampler = ClockSampler(local_rank)
@@ -259,7 +266,7 @@ def main():
     wall0 = time.perf_counter()
     for i in range(args.steps):
         if not args.no_flush:
-            flush.zero_()
+            flush_l2()
         starts[i].record()
         step()
         ends[i].record()
@@ -358,7 +365,7 @@ def main():
         "dtype": "bf16", "data": "synthetic (CPU generator seed 0, X~N(0,1), W~N(0,0.02), bf16)",
         "config": {"workload": args.workload, "shape": desc, "M": M, "K": K, "N": N, "n_per_gpu": n_local,
                    "parallelism": f"column-shard of W over {world} GPU(s), X replicated, no collective",
-                   "l2": "flushed before every timed step (256 MiB memset)" if not args.no_flush else "not flushed",
+                   "l2": "flushed before every timed step (256 MiB written, then 256 MiB read)" if not args.no_flush else "not flushed",
                    "plan": plan, "wall_s_timed_region": wall},
         "roofline": roof,
         "gpu_launches": args.steps,

@@ -34,13 +34,14 @@
 extern "C" {
 #endif
 
-#define MAGI_SWIGLU_ABI_VERSION 1
+#define MAGI_SWIGLU_ABI_VERSION 2
 
 /* variant selector of magi_swiglu_forward_bf16 */
-#define MAGI_SWIGLU_VARIANT_AUTO   0  /* M <= 128 -> STREAM, else MMA            */
-#define MAGI_SWIGLU_VARIANT_MMA    1  /* persistent tcgen05 tile kernel          */
+#define MAGI_SWIGLU_VARIANT_AUTO   0  /* M <= 128 -> STREAM, else MMA2           */
+#define MAGI_SWIGLU_VARIANT_MMA    1  /* persistent tcgen05 tile kernel, 1 CTA per tile */
 #define MAGI_SWIGLU_VARIANT_STREAM 2  /* weight-streaming schedule for small M   */
 #define MAGI_SWIGLU_VARIANT_SIMT   3  /* plain CUDA-core kernel, validation only */
+#define MAGI_SWIGLU_VARIANT_MMA2   4  /* MMA schedule on CTA pairs (tcgen05 cta_group::2, clusters of 2) */
 
 /* host-side argument errors (negative return values) */
 #define MAGI_SWIGLU_ERR_NULL       -1  /* null pointer                                */
@@ -88,12 +89,13 @@ int magi_swiglu_forward_bf16_ex(const void* x, const void* w_gate_up, void* y,
 /* Describes the schedule magi_swiglu_forward_bf16_ex would use, without
  * launching: out[0]=variant, out[1]=block_n, out[2]=stages, out[3]=grid CTAs,
  * out[4]=tiles, out[5]=dynamic shared memory bytes, out[6]=accumulator buffers,
- * out[7]=MMAs per K=16 step.  `sm_count` <= 0 means "query `device`".
+ * out[7]=MMAs per K=16 step, out[8]=CTAs per tile (1 or 2), out[9]=row units per raster band,
+ * out[10..11]=0 (reserved).  `sm_count` <= 0 means "query `device`".
  * Needs no GPU when sm_count > 0.
  * Replaces: nothing in the reference. */
 int magi_swiglu_plan(int64_t M, int64_t N, int64_t K, int variant,
                      int block_n, int stages, int group_m, int max_ctas,
-                     int device, int sm_count, int32_t out[8]);
+                     int device, int sm_count, int32_t out[12]);
 
 /* Reads (and clears) the device-side watchdog word of `device`.  Every wait in
  * the kernels is bounded; a wait that expires records
@@ -102,6 +104,13 @@ int magi_swiglu_plan(int64_t M, int64_t N, int64_t K, int variant,
  * This call SYNCHRONISES the device; it is for tests and debugging.
  * Replaces: nothing in the reference. */
 int magi_swiglu_device_status(int device, int32_t out[4]);
+
+/* SM clock the most recent MMA/MMA2/STREAM kernel on `device` really ran at: out[0] = average MHz
+ * (SM cycles / wall nanoseconds, both read inside the kernel by block 0), out[1] = that span in
+ * microseconds.  Power capping moves the clock within a millisecond, which a sampling tool cannot see.
+ * This call SYNCHRONISES the device; it is a measurement aid for the benchmark.
+ * Replaces: nothing in the reference. */
+int magi_swiglu_kernel_clock(int device, double out[2]);
 
 /* Text of the last error returned to the calling thread ("" if none).
  * Replaces: the Python exception text a reference custom-op body would raise. */

@@ -25,9 +25,10 @@ NVCC_FLAGS = [
     "-shared", "-Xcompiler", "-fPIC",
 ]
 
-ABI_VERSION = 1
-VARIANT_AUTO, VARIANT_MMA, VARIANT_STREAM, VARIANT_SIMT = 0, 1, 2, 3
-VARIANTS = {"auto": VARIANT_AUTO, "mma": VARIANT_MMA, "stream": VARIANT_STREAM, "simt": VARIANT_SIMT}
+ABI_VERSION = 2
+VARIANT_AUTO, VARIANT_MMA, VARIANT_STREAM, VARIANT_SIMT, VARIANT_MMA2 = 0, 1, 2, 3, 4
+VARIANTS = {"auto": VARIANT_AUTO, "mma": VARIANT_MMA, "stream": VARIANT_STREAM, "simt": VARIANT_SIMT,
+            "mma2": VARIANT_MMA2}
 
 _lib = None
 
@@ -79,6 +80,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.magi_swiglu_plan.argtypes = [i64, i64, i64, i32, i32, i32, i32, i32, i32, i32, ctypes.POINTER(ctypes.c_int32)]
     lib.magi_swiglu_device_status.restype = i32
     lib.magi_swiglu_device_status.argtypes = [i32, ctypes.POINTER(ctypes.c_int32)]
+    lib.magi_swiglu_kernel_clock.restype = i32
+    lib.magi_swiglu_kernel_clock.argtypes = [i32, ctypes.POINTER(ctypes.c_double)]
     lib.magi_swiglu_last_error.restype = ctypes.c_char_p
     lib.magi_swiglu_last_error.argtypes = []
 
@@ -115,12 +118,12 @@ def plan(M: int, N: int, K: int, variant: str | int = "auto", block_n: int = 0, 
          max_ctas: int = 0, device: int = 0, sm_count: int = 0) -> dict:
     """Schedule the library would use (pure host arithmetic when ``sm_count`` > 0)."""
     lib = load_library()
-    out = (ctypes.c_int32 * 8)()
+    out = (ctypes.c_int32 * 12)()
     v = VARIANTS[variant] if isinstance(variant, str) else int(variant)
     rc = lib.magi_swiglu_plan(M, N, K, v, block_n, stages, group_m, max_ctas, device, sm_count, out)
     if rc != 0:
         raise ValueError(f"magi_swiglu_plan failed ({rc}): {last_error()}")
-    keys = ["variant", "block_n", "stages", "grid", "tiles", "smem_bytes", "acc_bufs", "n_mma"]
+    keys = ["variant", "block_n", "stages", "grid", "tiles", "smem_bytes", "acc_bufs", "n_mma", "ctas", "group_m"]
     return dict(zip(keys, list(out)))
 
 
@@ -132,3 +135,13 @@ def device_status(device: int = 0) -> dict:
     if rc != 0:
         raise RuntimeError(f"magi_swiglu_device_status failed ({rc}): {last_error()}")
     return {"code": out[0], "block": out[1], "index": out[2], "parity": out[3]}
+
+
+def kernel_clock(device: int = 0) -> dict:
+    """Average SM clock (MHz) the most recent tile kernel ran at, measured inside the kernel (synchronises)."""
+    lib = load_library()
+    out = (ctypes.c_double * 2)()
+    rc = lib.magi_swiglu_kernel_clock(device, out)
+    if rc != 0:
+        raise RuntimeError(f"magi_swiglu_kernel_clock failed ({rc}): {last_error()}")
+    return {"sm_mhz": out[0], "span_us": out[1]}

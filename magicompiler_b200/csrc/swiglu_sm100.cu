@@ -11,8 +11,14 @@
 // tcgen05.mma (bf16 x bf16 -> fp32 in tensor memory) -> tcgen05.ld -> silu(g)*u in fp32 -> one
 // rounding to bf16 -> 16-byte global stores.  The 2N-wide intermediate never exists in HBM.
 //
-// Warp roles (256 threads): warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane),
-// warp 2 = tensor-memory allocator, warps 4..7 = epilogue (warp w reads TMEM lanes 32*(w%4)..+31).
+// MMA2 is the MMA schedule on CTA pairs (thread-block clusters of 2, tcgen05 cta_group::2): one 256-row MMA
+// spans both CTAs, each CTA loads its own 128 rows of X and only HALF of the weight tile, so every SM
+// pulls a third fewer bytes per FLOP through L2 and the ring is deeper.  The leader CTA (cluster rank 0)
+// issues the MMAs and owns the "stage full" barriers; both CTAs run their own producer and epilogue.
+//
+// Warp roles (384 threads): warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane),
+// warp 2 = tensor-memory allocator, warps 4..11 = epilogue (warp w reads TMEM lanes 32*(w%4)..+31;
+// the two warps of a lane quarter take alternate 32-column chunks of the tile).
 //
 // Every wait on an mbarrier is bounded: after kWaitLimitCycles the waiting role records itself in
 // g_watchdog, raises a CTA-wide abort flag and all roles fall through to the common teardown, which
@@ -21,6 +27,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -31,7 +38,8 @@ namespace magi {
 
 constexpr int kBM = 128;             // rows of X per tile = tensor-memory lanes
 constexpr int kBK = 64;              // K elements per pipeline stage = one 128-byte swizzle row
-constexpr int kThreads = 256;
+constexpr int kEpiWarps = 8;          // two warps per tensor-memory lane quarter share a tile's columns
+constexpr int kThreads = 128 + 32 * kEpiWarps;
 constexpr int kMaxStages = 12;
 constexpr int kTmemCols = 512;       // whole tensor memory of the SM (one CTA per SM)
 constexpr uint32_t kABytes = kBM * kBK * 2;
@@ -40,19 +48,37 @@ constexpr int kSmemFloor = 120 * 1024;  // keeps a second CTA off the SM (it wou
 constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
 
 __device__ unsigned int g_watchdog[4];  // {role that gave up, block, stage/buffer, parity}
+// {SM cycles, nanoseconds} block 0 of the most recent tile kernel spent between set-up and teardown: the
+// SM clock the kernel really ran at (power capping moves it within a millisecond; nvidia-smi cannot see that)
+__device__ unsigned long long g_clock_probe[2];
+
+#ifdef MAGI_SWIGLU_TRACE
+// Tuning builds only: SM-cycle timestamps of block 0's second tile (MMA issuer and first epilogue warp).
+__device__ long long g_trace[16];
+#define MAGI_TRACE(slot, cond) do { if (blockIdx.x == 0 && (cond)) g_trace[slot] = clock64(); } while (0)
+#else
+#define MAGI_TRACE(slot, cond) do { } while (0)
+#endif
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 struct KArgs {
   __nv_bfloat16* y;
   long long ldy;
   int M, N;
   int block_n;        // output columns per tile
-  int num_m_tiles, num_n_tiles, num_k_blocks;
+  int num_m_tiles, num_n_tiles, num_k_blocks;  // num_m_tiles counts 128-row (256-row for CTA pairs) units
   int group_m;        // row-tiles per raster band
   int stages;
   uint32_t stage_bytes;
   int n_mma;          // 1: one MMA of N = 2*block_n covers gate|up;  2: one MMA each
+  uint32_t b_second;  // byte offset of the second MMA's weight rows inside a stage's weight tile
   int acc_bufs;       // tensor-memory accumulator buffers (2 = epilogue overlaps next tile)
-  int w_evict_first;  // STREAM: weight tiles are read once, mark them evict-first in L2
+  int x_hint, w_hint, y_hint;  // L2 eviction priority of X tiles, W tiles and Y stores: 0 normal, 1 first, 2 last
 };
 
 __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned role,
@@ -91,10 +117,18 @@ __device__ __forceinline__ void tile_coords(const KArgs& a, int t, int& mt, int&
 
 __device__ __forceinline__ float silu_mul(float g, float u) {
   // silu(g) = g / (1 + exp(-g)); ex2.approx + div.approx are far below bf16 resolution
+#ifdef MAGI_EXP_NOSILU  // tuning experiment: epilogue without the two special-function operations
+  return g * u;
+#else
   return __fdividef(g, 1.0f + __expf(-g)) * u;
+#endif
 }
 
-__device__ __forceinline__ void store8(__nv_bfloat16* dst, const uint32_t* g, const uint32_t* u) {
+__device__ __forceinline__ uint64_t l2_policy(int hint) {
+  return hint == 1 ? l2_policy_evict_first() : (hint == 2 ? l2_policy_evict_last() : l2_policy_evict_normal());
+}
+
+__device__ __forceinline__ void store8(__nv_bfloat16* dst, const uint32_t* g, const uint32_t* u, uint64_t policy) {
   uint4 v;
   __nv_bfloat162 p;
   p = __floats2bfloat162_rn(silu_mul(__uint_as_float(g[0]), __uint_as_float(u[0])),
@@ -109,9 +143,14 @@ __device__ __forceinline__ void store8(__nv_bfloat16* dst, const uint32_t* g, co
   p = __floats2bfloat162_rn(silu_mul(__uint_as_float(g[6]), __uint_as_float(u[6])),
                             silu_mul(__uint_as_float(g[7]), __uint_as_float(u[7])));
   v.w = *reinterpret_cast<uint32_t*>(&p);
-  *reinterpret_cast<uint4*>(dst) = v;
+#ifdef MAGI_EXP_NOSTORE  // tuning experiment: epilogue without (almost all of) its global stores
+  if (v.x == 0x7fc07fc1u) st_global_v4_hint(dst, v, policy);
+#else
+  st_global_v4_hint(dst, v, policy);
+#endif
 }
 
+template <int kCtas>
 __global__ void __launch_bounds__(kThreads, 1)
 swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const KArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -121,7 +160,10 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  // 128-byte-swizzled tiles must start on 1024-byte boundaries
+  const uint32_t cta_rank = (kCtas == 2) ? cluster_ctarank() : 0u;  // rank 0 of a pair leads
+  const int unit = blockIdx.x / kCtas;                              // index of this CTA (pair) in the grid
+  const int units = gridDim.x / kCtas;
+  // 128-byte-swizzled tiles must start on 1024-byte boundaries (same offset in both CTAs of a pair)
   const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
@@ -137,46 +179,64 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full_bar(b), 1);
-      mbar_init(acc_empty_bar(b), 4);  // lane 0 of each epilogue warp
+      mbar_init(acc_empty_bar(b), kEpiWarps * kCtas);  // lane 0 of each epilogue warp (of both CTAs of a pair)
     }
     fence_barrier_init();
     prefetch_tensormap(&tm_x);
     prefetch_tensormap(&tm_w);
   }
   if (warp == 2) {
-    tmem_alloc(smem_u32(&tmem_slot), kTmemCols);
-    tmem_relinquish();
+    tmem_alloc<kCtas>(smem_u32(&tmem_slot), kTmemCols);
+    tmem_relinquish<kCtas>();
   }
   tc_fence_before_sync();
   __syncthreads();
+  if constexpr (kCtas == 2) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
+  long long probe_c0 = 0;
+  unsigned long long probe_t0 = 0;
+  if (blockIdx.x == 0 && threadIdx.x == 96) {  // an otherwise idle thread of warp 3
+    probe_c0 = clock64();
+    probe_t0 = global_timer_ns();
+  }
 
   const int num_tiles = a.num_m_tiles * a.num_n_tiles;
   const int acc_cols = 2 * a.block_n;
 
   if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------ TMA producer (every CTA loads its own tiles)
     if (lane == 0) {
-      const uint64_t w_policy = l2_policy_evict_first();
+      const uint64_t x_policy = l2_policy(a.x_hint), w_policy = l2_policy(a.w_hint);
+      // CTA pairs: the bytes of both CTAs are counted on the leader's barrier
+      const uint32_t full_remote0 = (kCtas == 2) ? map_to_cta(full_bar(0), 0) : 0u;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = unit; t < num_tiles && ok; t += units) {
         int mt, nt;
         tile_coords(a, t, mt, nt);
+        const int row0 = (mt * kCtas + (int)cta_rank) * kBM;
         for (int kb = 0; kb < a.num_k_blocks; ++kb) {
           if (!wait_bounded(empty_bar(stage), phase ^ 1u, &abort_flag, 1u, stage)) {
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(full_bar(stage), a.stage_bytes);
           const uint32_t sa = tiles_base + stage * a.stage_bytes;
-          tma_load_2d(sa, &tm_x, full_bar(stage), kb * kBK, mt * kBM);
-          if (a.w_evict_first)
+          if constexpr (kCtas == 1) {
+            mbar_arrive_expect_tx(full_bar(stage), a.stage_bytes);
+            tma_load_2d_hint(sa, &tm_x, full_bar(stage), kb * kBK, row0, x_policy);
             tma_load_3d_hint(sa + kABytes, &tm_w, full_bar(stage), kb * kBK, nt * a.block_n, 0, w_policy);
-          else
-            tma_load_3d(sa + kABytes, &tm_w, full_bar(stage), kb * kBK, nt * a.block_n, 0);
+          } else {
+            if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2u * a.stage_bytes);
+            const uint32_t bar = full_remote0 + 8u * stage;
+            tma_load_2d_pair_hint(sa, &tm_x, bar, kb * kBK, row0, x_policy);
+            if (a.n_mma == 1)  // this CTA's half of the N = 2*block_n operand: rank 0 = gate rows, rank 1 = up rows
+              tma_load_3d_pair_hint(sa + kABytes, &tm_w, bar, kb * kBK, nt * a.block_n, (int)cta_rank, w_policy);
+            else               // half of the gate rows and the matching half of the up rows
+              tma_load_3d_pair_hint(sa + kABytes, &tm_w, bar, kb * kBK,
+                                    nt * a.block_n + (int)cta_rank * (a.block_n / 2), 0, w_policy);
+          }
           if (++stage == a.stages) {
             stage = 0;
             phase ^= 1u;
@@ -185,19 +245,20 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && cta_rank == 0) {
       const uint32_t mma_n = (a.n_mma == 1) ? 2u * a.block_n : (uint32_t)a.block_n;
-      const uint32_t idesc = umma_idesc_bf16(kBM, mma_n);
-      const uint32_t up_tile_bytes = (uint32_t)a.block_n * 128u;  // gate rows, then up rows, 128 B each
+      const uint32_t idesc = umma_idesc_bf16(kBM * kCtas, mma_n);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+      for (int t = unit; t < num_tiles && ok; t += units, ++it) {
         const int buf = (a.acc_bufs == 2) ? (it & 1) : 0;
         const uint32_t acc_phase = (a.acc_bufs == 2) ? ((it >> 1) & 1) : (it & 1);
+        MAGI_TRACE(0, it == 2);  // issuer starts waiting for the accumulator of tile 2
         if (!wait_bounded(acc_empty_bar(buf), acc_phase ^ 1u, &abort_flag, 2u, 16 + buf)) break;
+        MAGI_TRACE(1, it == 2);  // accumulator free
         tc_fence_after_sync();
         const uint32_t d_gate = tmem_base + (uint32_t)(buf * acc_cols);
         for (int kb = 0; kb < a.num_k_blocks; ++kb) {
@@ -205,6 +266,8 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
             ok = false;
             break;
           }
+          MAGI_TRACE(2, it == 2 && kb == 0);                   // first stage of tile 2 available
+          MAGI_TRACE(3, it == 1 && kb == a.num_k_blocks - 1);  // last stage of tile 1 available
           tc_fence_after_sync();
           const uint32_t sa = tiles_base + stage * a.stage_bytes;
           const uint32_t sb = sa + kABytes;
@@ -212,24 +275,28 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
           for (int k = 0; k < kBK / 16; ++k) {
             const uint32_t acc = (kb | k) != 0;
             const uint64_t ad = umma_desc_k_sw128(sa + k * 32);
-            umma_bf16(d_gate, ad, umma_desc_k_sw128(sb + k * 32), idesc, acc);
+            umma_bf16<kCtas>(d_gate, ad, umma_desc_k_sw128(sb + k * 32), idesc, acc);
             if (a.n_mma == 2)
-              umma_bf16(d_gate + a.block_n, ad, umma_desc_k_sw128(sb + up_tile_bytes + k * 32), idesc, acc);
+              umma_bf16<kCtas>(d_gate + a.block_n, ad, umma_desc_k_sw128(sb + a.b_second + k * 32), idesc, acc);
           }
-          umma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+          umma_commit<kCtas>(empty_bar(stage));  // frees the stage (in both CTAs) once these MMAs have read it
           if (++stage == a.stages) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        if (ok) umma_commit(acc_full_bar(buf));
+        if (ok) umma_commit<kCtas>(acc_full_bar(buf));
+        MAGI_TRACE(4, it == 1);  // all MMAs of tile 1 issued
+        MAGI_TRACE(9, it == 2);  // all MMAs of tile 2 issued
       }
     }
   } else if (warp >= 4) {
-    // ------------------------------------------------------------ epilogue
+    // ------------------------------------------------------------ epilogue (every CTA drains its own 128 rows)
     const int q = warp & 3;
+    const uint64_t y_policy = l2_policy(a.y_hint);
+    const uint32_t acc_empty_remote0 = (kCtas == 2) ? map_to_cta(acc_empty_bar(0), 0) : 0u;
     int it = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+    for (int t = unit; t < num_tiles; t += units, ++it) {
       const int buf = (a.acc_bufs == 2) ? (it & 1) : 0;
       const uint32_t acc_phase = (a.acc_bufs == 2) ? ((it >> 1) & 1) : (it & 1);
       int mt, nt;
@@ -237,9 +304,10 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       bool ok = wait_bounded(acc_full_bar(buf), acc_phase, &abort_flag, 3u, buf);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      MAGI_TRACE(5, it == 1 && warp == 4 && lane == 0);  // epilogue sees tile 1 complete
       tc_fence_after_sync();
 
-      const int row = mt * kBM + q * 32 + lane;
+      const int row = (mt * kCtas + (int)cta_rank) * kBM + q * 32 + lane;
       const bool row_ok = row < a.M;
       const int col0 = nt * a.block_n;
       const int valid = min(a.block_n, a.N - col0);  // multiple of 8
@@ -247,8 +315,11 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       const uint32_t t_up = t_gate + (uint32_t)a.block_n;
       __nv_bfloat16* yrow = a.y + (long long)row * a.ldy + col0;
 
-      int c = 0;
-      for (; c + 32 <= a.block_n && c < valid; c += 32) {
+      // 32-column chunks alternate between the two warps of this lane quarter; a 16-column remainder
+      // (block_n % 32 == 16) goes to whichever warp is next in turn
+      const int half = (warp - 4) >> 2;
+      int c = 32 * half;
+      for (; c + 32 <= a.block_n && c < valid; c += 64) {
         uint32_t g[32], u[32];
         tmem_ld_x32(t_gate + c, g);
         tmem_ld_x32(t_up + c, u);
@@ -256,10 +327,10 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         if (row_ok) {
 #pragma unroll
           for (int j = 0; j < 4; ++j)
-            if (c + 8 * j + 8 <= valid) store8(yrow + c + 8 * j, g + 8 * j, u + 8 * j);
+            if (c + 8 * j + 8 <= valid) store8(yrow + c + 8 * j, g + 8 * j, u + 8 * j, y_policy);
         }
       }
-      if (c < a.block_n && c < valid) {  // block_n % 32 == 16
+      if (c + 16 == a.block_n && c < valid) {
         uint32_t g[16], u[16];
         tmem_ld_x16(t_gate + c, g);
         tmem_ld_x16(t_up + c, u);
@@ -267,12 +338,19 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         if (row_ok) {
 #pragma unroll
           for (int j = 0; j < 2; ++j)
-            if (c + 8 * j + 8 <= valid) store8(yrow + c + 8 * j, g + 8 * j, u + 8 * j);
+            if (c + 8 * j + 8 <= valid) store8(yrow + c + 8 * j, g + 8 * j, u + 8 * j, y_policy);
         }
       }
+      MAGI_TRACE(6, it == 1 && warp == 4 && lane == 0);   // warp 4 drained its columns
+      MAGI_TRACE(7, it == 1 && warp == 11 && lane == 0);  // warp 11 drained its columns
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+      if (lane == 0) {
+        if constexpr (kCtas == 1)
+          mbar_arrive(acc_empty_bar(buf));
+        else
+          mbar_arrive_cluster(acc_empty_remote0 + 8u * buf);  // the leader's MMA issuer waits for both CTAs
+      }
     }
   }
 
@@ -286,9 +364,15 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x == 96) {
+    g_clock_probe[0] = (unsigned long long)(clock64() - probe_c0);
+    g_clock_probe[1] = global_timer_ns() - probe_t0;
+  }
+  // a pair leaves together: the leader's MMAs read the peer's shared memory and both barriers sets are shared
+  if constexpr (kCtas == 2) cluster_sync_all();
   if (warp == 2) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc<kCtas>(tmem_base, kTmemCols);
   }
 }
 
@@ -357,6 +441,7 @@ struct DeviceInfo {
   int sm_count = 0;
   int cc_major = 0, cc_minor = 0;
   int smem_optin_set = 0;
+  int pair_clusters = 0;  // co-resident 2-CTA clusters of the pair kernel (0 = not queried yet, -1 = none)
 };
 static DeviceInfo g_dev[kMaxDevices];
 static std::mutex g_dev_mutex;
@@ -383,7 +468,8 @@ static const DeviceInfo* device_info(int device) {
 struct Plan {
   int variant, block_n, stages, grid, tiles, smem_bytes, acc_bufs, n_mma;
   int num_m_tiles, num_n_tiles, num_k_blocks, group_m;
-  uint32_t stage_bytes;
+  int ctas;  // CTAs per tile: 1, or 2 for the CTA-pair schedule
+  uint32_t stage_bytes, b_second;
 };
 
 static inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
@@ -394,8 +480,9 @@ static int make_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
     return fail(MAGI_SWIGLU_ERR_SHAPE, "shape out of range: M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
   if (N % 8 != 0 || K % 8 != 0)
     return fail(MAGI_SWIGLU_ERR_SHAPE, "N (%lld) and K (%lld) must be multiples of 8", (long long)N, (long long)K);
-  if (variant == MAGI_SWIGLU_VARIANT_AUTO) variant = (M <= 128) ? MAGI_SWIGLU_VARIANT_STREAM : MAGI_SWIGLU_VARIANT_MMA;
-  if (variant != MAGI_SWIGLU_VARIANT_MMA && variant != MAGI_SWIGLU_VARIANT_STREAM && variant != MAGI_SWIGLU_VARIANT_SIMT)
+  if (variant == MAGI_SWIGLU_VARIANT_AUTO) variant = (M <= 128) ? MAGI_SWIGLU_VARIANT_STREAM : MAGI_SWIGLU_VARIANT_MMA2;
+  if (variant != MAGI_SWIGLU_VARIANT_MMA && variant != MAGI_SWIGLU_VARIANT_STREAM &&
+      variant != MAGI_SWIGLU_VARIANT_SIMT && variant != MAGI_SWIGLU_VARIANT_MMA2)
     return fail(MAGI_SWIGLU_ERR_VARIANT, "unknown variant %d", variant);
   if (sm_count <= 0) return fail(MAGI_SWIGLU_ERR_DEVICE, "sm_count must be positive");
   memset(p, 0, sizeof(*p));
@@ -408,9 +495,26 @@ static int make_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
   }
   if (variant == MAGI_SWIGLU_VARIANT_STREAM && M > kBM)
     return fail(MAGI_SWIGLU_ERR_VARIANT, "STREAM variant needs M <= %d (got %lld)", kBM, (long long)M);
-  const int ctas = (max_ctas > 0 && max_ctas < sm_count) ? max_ctas : sm_count;
+  const int pair = (variant == MAGI_SWIGLU_VARIANT_MMA2) ? 2 : 1;
+  p->ctas = pair;
+  int ctas = (max_ctas > 0 && max_ctas < sm_count) ? max_ctas : sm_count;
+  if (pair == 2) ctas = ctas / 2 * 2;
+  if (ctas < pair) return fail(MAGI_SWIGLU_ERR_VARIANT, "max_ctas=%d leaves no room for a CTA pair", max_ctas);
   if (block_n == 0) {
-    if (variant == MAGI_SWIGLU_VARIANT_MMA) {
+    if (variant == MAGI_SWIGLU_VARIANT_MMA2) {
+      // Widest tile that tensor memory holds (gate + up = 512 fp32 columns): fewest operand bytes per
+      // FLOP.  Among widths that waste no more columns than 256 does, take the widest.
+      int best = 256;
+      double best_waste = 1e30;
+      for (int bn = 256; bn >= 128; bn -= 16) {
+        const double waste = (double)((N + bn - 1) / bn * bn) / (double)N;
+        if (waste < best_waste - 0.02) {
+          best_waste = waste;
+          best = bn;
+        }
+      }
+      block_n = (N >= 128) ? best : round_up((int)N, 16);
+    } else if (variant == MAGI_SWIGLU_VARIANT_MMA) {
       block_n = (N >= 128) ? 128 : round_up((int)N, 16);
     } else {
       // one slab per SM if it fits in tensor memory (gate + up <= 512 fp32 columns)
@@ -424,7 +528,9 @@ static int make_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
   p->block_n = block_n;
   p->n_mma = (2 * block_n <= 256) ? 1 : 2;
   p->acc_bufs = (4 * block_n <= kTmemCols) ? 2 : 1;
-  p->stage_bytes = kABytes + 2u * (uint32_t)block_n * 128u;
+  // weight rows per CTA and stage: gate + up rows of the tile, split between the CTAs of a pair
+  p->stage_bytes = kABytes + 2u * (uint32_t)block_n * 128u / (uint32_t)pair;
+  p->b_second = (uint32_t)block_n * 128u / (uint32_t)pair;
   const int fit = (kSmemLimit - 1024) / (int)p->stage_bytes;
   int max_stages = fit < kMaxStages ? fit : kMaxStages;
   if (stages == 0) stages = max_stages;
@@ -433,19 +539,24 @@ static int make_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
   p->stages = stages;
   int smem = stages * (int)p->stage_bytes + 1024;
   p->smem_bytes = smem < kSmemFloor ? kSmemFloor : smem;
-  p->num_m_tiles = (int)((M + kBM - 1) / kBM);
+  p->num_m_tiles = (int)((M + kBM * pair - 1) / (kBM * pair));
   p->num_n_tiles = (int)((N + block_n - 1) / block_n);
   p->num_k_blocks = (int)((K + kBK - 1) / kBK);
   if ((int64_t)p->num_m_tiles * p->num_n_tiles > 0x7fffffffLL) return fail(MAGI_SWIGLU_ERR_SHAPE, "too many tiles");
   p->tiles = p->num_m_tiles * p->num_n_tiles;
-  if (group_m <= 0) group_m = 16;
+  if (group_m <= 0) {
+    // band height: keep one band of X rows (group_m units x K) around 32 MB so it stays in L2 while W streams by
+    const int64_t unit_bytes = (int64_t)kBM * pair * K * 2;
+    int64_t g = (32LL << 20) / (unit_bytes > 0 ? unit_bytes : 1);
+    group_m = (int)(g < 4 ? 4 : (g > 64 ? 64 : g));
+  }
   p->group_m = group_m;
-  p->grid = p->tiles < ctas ? p->tiles : ctas;
+  p->grid = (p->tiles * pair < ctas) ? p->tiles * pair : ctas;
   return 0;
 }
 
 static int encode_maps(const void* x, const void* w, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw,
-                       int block_n, CUtensorMap* tm_x, CUtensorMap* tm_w) {
+                       const Plan& p, CUtensorMap* tm_x, CUtensorMap* tm_w) {
   EncodeTiledFn enc = tensor_map_encoder();
   if (!enc) return fail(MAGI_SWIGLU_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from the driver");
   {
@@ -462,7 +573,14 @@ static int encode_maps(const void* x, const void* w, int64_t M, int64_t N, int64
     // W viewed as [2][N][K]: one box brings block_n gate rows and the matching block_n up rows
     const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)N, 2};
     const cuuint64_t strides[2] = {(cuuint64_t)ldw * 2, (cuuint64_t)N * (cuuint64_t)ldw * 2};
-    const cuuint32_t box[3] = {(cuuint32_t)kBK, (cuuint32_t)block_n, 2};
+    // one CTA per tile: block_n gate rows + block_n up rows.  CTA pair: each CTA brings half of the MMA's
+    // weight rows — all gate rows or all up rows when one MMA covers gate|up, else half of each.
+    cuuint32_t box_rows = (cuuint32_t)p.block_n, box_halves = 2;
+    if (p.ctas == 2) {
+      if (p.n_mma == 1) box_halves = 1;
+      else box_rows = (cuuint32_t)p.block_n / 2;
+    }
+    const cuuint32_t box[3] = {(cuuint32_t)kBK, box_rows, box_halves};
     const cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = enc(tm_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(w), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -526,17 +644,42 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   }
 
   CUtensorMap tm_x, tm_w;
-  rc = encode_maps(x, w, M, N, K, ldx, ldw, p.block_n, &tm_x, &tm_w);
+  rc = encode_maps(x, w, M, N, K, ldx, ldw, p, &tm_x, &tm_w);
   if (rc) return rc;
 
+  int pair_clusters = 0;
   {
     std::lock_guard<std::mutex> lock(g_dev_mutex);
     DeviceInfo& d = g_dev[device];
     if (!d.smem_optin_set) {
-      e = cudaFuncSetAttribute(swiglu_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+      e = cudaFuncSetAttribute(swiglu_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(swiglu_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
       if (e != cudaSuccess) return fail_cuda(e, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize)");
       d.smem_optin_set = 1;
     }
+    if (p.ctas == 2 && d.pair_clusters == 0) {
+      // how many CTA pairs the GPU can hold at once (GPCs with an odd SM count leave one SM out)
+      cudaLaunchConfig_t qc = {};
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = 2;
+      qa[0].val.clusterDim.y = 1;
+      qa[0].val.clusterDim.z = 1;
+      qc.gridDim = dim3((unsigned)(d.sm_count / 2 * 2));
+      qc.blockDim = dim3(kThreads);
+      qc.dynamicSmemBytes = kSmemLimit;
+      qc.attrs = qa;
+      qc.numAttrs = 1;
+      int n = 0;
+      e = cudaOccupancyMaxActiveClusters(&n, swiglu_tc_kernel<2>, &qc);
+      if (e != cudaSuccess) {
+        cudaGetLastError();
+        n = 0;
+      }
+      d.pair_clusters = n > 0 ? n : -1;
+    }
+    pair_clusters = d.pair_clusters;
   }
 
   KArgs a;
@@ -552,12 +695,42 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   a.stages = p.stages;
   a.stage_bytes = p.stage_bytes;
   a.n_mma = p.n_mma;
+  a.b_second = p.b_second;
   a.acc_bufs = p.acc_bufs;
-  a.w_evict_first = (p.variant == MAGI_SWIGLU_VARIANT_STREAM) ? 1 : 0;
+  // default L2 priorities: a band of X rows is re-read by every column tile -> keep; W tiles and Y are streamed
+  a.x_hint = 2;
+  a.w_hint = 1;
+  a.y_hint = 1;
+  if (const char* env = getenv("MAGI_SWIGLU_L2_HINTS")) {  // three digits "xwy", each 0/1/2 (tuning aid)
+    if (strlen(env) == 3) {
+      a.x_hint = env[0] - '0';
+      a.w_hint = env[1] - '0';
+      a.y_hint = env[2] - '0';
+    }
+  }
 
-  swiglu_tc_kernel<<<p.grid, kThreads, p.smem_bytes, stream>>>(tm_x, tm_w, a);
-  e = cudaGetLastError();
-  return e == cudaSuccess ? 0 : fail_cuda(e, "launch of swiglu_tc_kernel");
+  if (p.ctas == 1) {
+    swiglu_tc_kernel<1><<<p.grid, kThreads, p.smem_bytes, stream>>>(tm_x, tm_w, a);
+    e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : fail_cuda(e, "launch of swiglu_tc_kernel<1>");
+  }
+  if (pair_clusters <= 0) return fail(MAGI_SWIGLU_ERR_VARIANT, "this device cannot co-schedule 2-CTA clusters of the pair kernel");
+  int grid = p.grid;
+  if (grid > 2 * pair_clusters) grid = 2 * pair_clusters;  // persistent: never more pairs than fit at once
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = (size_t)p.smem_bytes;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, swiglu_tc_kernel<2>, tm_x, tm_w, a);
+  return e == cudaSuccess ? 0 : fail_cuda(e, "launch of swiglu_tc_kernel<2>");
 }
 
 }  // namespace magi
@@ -585,7 +758,7 @@ int magi_swiglu_forward_bf16_ex(const void* x, const void* w_gate_up, void* y, i
 }
 
 int magi_swiglu_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, int stages, int group_m, int max_ctas,
-                     int device, int sm_count, int32_t out[8]) {
+                     int device, int sm_count, int32_t out[12]) {
   magi::g_err[0] = 0;
   if (!out) return magi::fail(MAGI_SWIGLU_ERR_NULL, "out is null");
   if (sm_count <= 0) {
@@ -604,6 +777,10 @@ int magi_swiglu_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
   out[5] = p.smem_bytes;
   out[6] = p.acc_bufs;
   out[7] = p.n_mma;
+  out[8] = p.ctas;
+  out[9] = p.group_m;
+  out[10] = 0;
+  out[11] = 0;
   return 0;
 }
 
@@ -625,6 +802,30 @@ int magi_swiglu_device_status(int device, int32_t out[4]) {
     e = cudaMemcpyToSymbol(magi::g_watchdog, zero, sizeof(zero));
     if (e != cudaSuccess) return magi::fail_cuda(e, "cudaMemcpyToSymbol(g_watchdog)");
   }
+  return 0;
+}
+
+#ifdef MAGI_SWIGLU_TRACE
+int magi_swiglu_trace(long long out[16]) {
+  cudaDeviceSynchronize();
+  return (int)cudaMemcpyFromSymbol(out, magi::g_trace, sizeof(long long) * 16);
+}
+#endif
+
+int magi_swiglu_kernel_clock(int device, double out[2]) {
+  magi::g_err[0] = 0;
+  if (!out) return magi::fail(MAGI_SWIGLU_ERR_NULL, "out is null");
+  if (!magi::device_info(device)) return magi::fail(MAGI_SWIGLU_ERR_DEVICE, "device %d is not available", device);
+  magi::DeviceGuard guard;
+  cudaError_t e = guard.set(device);
+  if (e != cudaSuccess) return magi::fail_cuda(e, "cudaSetDevice");
+  e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return magi::fail_cuda(e, "cudaDeviceSynchronize");
+  unsigned long long host[2] = {0, 0};
+  e = cudaMemcpyFromSymbol(host, magi::g_clock_probe, sizeof(host));
+  if (e != cudaSuccess) return magi::fail_cuda(e, "cudaMemcpyFromSymbol(g_clock_probe)");
+  out[0] = host[1] ? (double)host[0] * 1e3 / (double)host[1] : 0.0;  // cycles per ns -> MHz
+  out[1] = (double)host[1] * 1e-3;
   return 0;
 }
 

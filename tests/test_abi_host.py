@@ -26,7 +26,7 @@ def _declared_functions():
 def test_every_declared_symbol_is_exported(lib):
     names = _declared_functions()
     assert {"magi_swiglu_version", "magi_swiglu_supported", "magi_swiglu_forward_bf16", "magi_swiglu_forward_bf16_ex",
-            "magi_swiglu_plan", "magi_swiglu_device_status", "magi_swiglu_last_error"} <= set(names)
+            "magi_swiglu_plan", "magi_swiglu_device_status", "magi_swiglu_kernel_clock", "magi_swiglu_last_error"} <= set(names)
     for n in names:
         assert hasattr(lib, n), n
 
@@ -53,22 +53,38 @@ def test_supported_is_false_without_a_b200(lib):
 
 
 def test_plan_for_the_benchmark_configs():
-    p = _loader.plan(8192, 14336, 4096, sm_count=148)  # Llama-3-8B FFN
-    assert p["variant"] == _loader.VARIANT_MMA and p["grid"] == 148 and p["block_n"] % 16 == 0
-    assert p["tiles"] == -(-8192 // 128) * -(-14336 // p["block_n"])
+    p = _loader.plan(8192, 14336, 4096, sm_count=148)  # Llama-3-8B FFN: CTA pairs, 256-row tiles
+    assert p["variant"] == _loader.VARIANT_MMA2 and p["ctas"] == 2 and p["grid"] == 148 and p["block_n"] % 16 == 0
+    assert p["tiles"] == -(-8192 // 256) * -(-14336 // p["block_n"])
     assert p["smem_bytes"] <= 232448 and p["stages"] >= 3
     p = _loader.plan(32760, 13824, 5120, sm_count=148)  # video-DiT FFN, ragged M
-    assert p["variant"] == _loader.VARIANT_MMA and p["tiles"] == 256 * -(-13824 // p["block_n"])
+    assert p["variant"] == _loader.VARIANT_MMA2 and p["tiles"] == 128 * -(-13824 // p["block_n"])
+    p = _loader.plan(32760, 1728, 5120, sm_count=148)  # its 8-GPU column shard: a width that divides 1728
+    assert 1728 % p["block_n"] == 0
     for M in (16, 64, 128):  # decode shapes: one slab of W per SM, a single wave
         p = _loader.plan(M, 28672, 8192, sm_count=148)
         assert p["variant"] == _loader.VARIANT_STREAM
         assert p["tiles"] == p["grid"] <= 148 and p["tiles"] * p["block_n"] >= 28672
         assert 2 * p["block_n"] <= 512
     p = _loader.plan(129, 2816, 1024, sm_count=148)
-    assert p["variant"] == _loader.VARIANT_MMA
+    assert p["variant"] == _loader.VARIANT_MMA2
     for shard in (14336, 7168, 3584):  # column shards of the decode weight at 2/4/8 GPUs
         p = _loader.plan(64, shard, 8192, sm_count=148)
         assert p["tiles"] <= 148 * 2
+
+
+def test_plan_for_cta_pairs():
+    p = _loader.plan(8192, 14336, 4096, variant="mma2", block_n=128, sm_count=148)
+    assert p["ctas"] == 2 and p["grid"] == 148 and p["tiles"] == 32 * 112 and p["n_mma"] == 1 and p["acc_bufs"] == 2
+    assert p["stages"] >= 6, "half the weight tile per CTA leaves room for a deeper ring"
+    p1 = _loader.plan(8192, 14336, 4096, variant="mma", sm_count=148)
+    assert p1["ctas"] == 1 and p["stages"] > p1["stages"]
+    p = _loader.plan(32760, 13824, 5120, variant="mma2", block_n=128, sm_count=147)  # odd SM count: whole pairs only
+    assert p["grid"] == 146 and p["tiles"] == 128 * 108
+    p = _loader.plan(300, 528, 320, variant="mma2", block_n=256, sm_count=148)
+    assert (p["n_mma"], p["acc_bufs"], p["tiles"]) == (2, 1, 2 * 3)
+    with pytest.raises(ValueError):
+        _loader.plan(300, 528, 320, variant="mma2", max_ctas=1, sm_count=148)
 
 
 def test_plan_respects_explicit_knobs_and_rejects_bad_ones():

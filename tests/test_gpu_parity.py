@@ -62,7 +62,7 @@ def test_c_abi_direct_call_cfg1():
 
 
 @pytest.mark.parametrize("name", ["tiny_48x128x96", "ragged_37x200x72", "mid_130x512x264", "cfg1_256x1024x2816"])
-@pytest.mark.parametrize("variant", ["auto", "mma", "simt"])
+@pytest.mark.parametrize("variant", ["auto", "mma", "mma2", "simt"])
 def test_against_reference_fixture(golden, name, variant):
     M, K, N, seed, step = (int(v) for v in golden[name + "/shape"])
     if name + "/x" in golden.files:
@@ -83,7 +83,7 @@ SHAPES = [  # (M, N, K): tails in every dimension, single-tile and multi-tile
 
 
 @pytest.mark.parametrize("shape", SHAPES)
-@pytest.mark.parametrize("variant", ["auto", "mma", "stream"])
+@pytest.mark.parametrize("variant", ["auto", "mma", "mma2", "stream"])
 def test_ragged_shapes(shape, variant):
     M, N, K = shape
     if variant == "stream" and M > 128:
@@ -94,15 +94,18 @@ def test_ragged_shapes(shape, variant):
 
 
 @pytest.mark.parametrize("block_n", [16, 32, 48, 64, 96, 112, 128, 144, 208, 256])
-@pytest.mark.parametrize("stages,max_ctas,group_m", [(0, 0, 0), (2, 1, 1), (3, 5, 2)])
-def test_schedule_knobs(block_n, stages, max_ctas, group_m):
+@pytest.mark.parametrize("stages,max_ctas,group_m", [(0, 0, 0), (2, 2, 1), (3, 6, 2)])
+@pytest.mark.parametrize("variant", ["mma", "mma2"])
+def test_schedule_knobs(variant, block_n, stages, max_ctas, group_m):
     """Every tile width (one or two MMAs per step, one or two accumulator buffers), shallow pipelines and a
-    single persistent CTA walking all tiles (many barrier phase wraps) give the same answer."""
-    M, N, K = 300, 528, 320
+    single persistent CTA (or CTA pair) walking all tiles (many barrier phase wraps) give the same answer."""
+    M, N, K = 600, 528, 320
     if stages:
-        stages = min(stages, mb.plan(M, N, K, variant="mma", block_n=block_n)["stages"])  # wide tiles fit fewer
+        stages = min(stages, mb.plan(M, N, K, variant=variant, block_n=block_n)["stages"])  # wide tiles fit fewer
+    if variant == "mma":
+        max_ctas //= 2
     x, w = make_inputs(M, K, N, seed=block_n)
-    y = mb.gemm_swiglu_out(x.cuda(), w.cuda(), variant="mma", block_n=block_n, stages=stages, max_ctas=max_ctas,
+    y = mb.gemm_swiglu_out(x.cuda(), w.cuda(), variant=variant, block_n=block_n, stages=stages, max_ctas=max_ctas,
                            group_m=group_m)
     base = mb.gemm_swiglu_out(x.cuda(), w.cuda(), variant="mma")
     assert_parity(y, swiglu_gold(x, w, want_eager=False)["gold"], f"bn={block_n}")
@@ -174,6 +177,7 @@ def test_decode_shapes_full_size(M):
     y = mb.gemm_swiglu(xd, wd)
     assert_parity(y, gold_fp32_gpu(xd, wd), f"decode M={M}")
     assert torch.equal(y, mb.gemm_swiglu_out(xd, wd, variant="mma")), "both schedules accumulate in the same order"
+    assert torch.equal(y, mb.gemm_swiglu_out(xd, wd, variant="mma2"))
 
 
 def test_llama_ffn_full_size_properties():
@@ -184,6 +188,8 @@ def test_llama_ffn_full_size_properties():
     y = mb.gemm_swiglu(xd, wd)
     rows = torch.randperm(M, generator=torch.Generator().manual_seed(1))[:384].cuda()
     assert_parity(y[rows], gold_fp32_gpu(xd[rows], wd), "llama ffn sample")
+    for variant in ("mma", "mma2"):  # one CTA per tile and CTA pairs: same K order per output, same bits
+        assert torch.equal(mb.gemm_swiglu_out(xd, wd, variant=variant), y), variant
     # (1) doubling the up weights doubles every output exactly (power-of-two scaling commutes with rounding)
     w2 = wd.clone()
     w2[N:] *= 2
@@ -205,4 +211,5 @@ def test_video_dit_ffn_sampled():
     rows = torch.cat([torch.arange(M - 130, M), torch.randperm(M - 130, generator=torch.Generator().manual_seed(3))[:254]]).cuda()
     assert_parity(y[rows], gold_fp32_gpu(xd[rows], wd), "video dit sample")
     shard = mb.shard_gate_up(wd, 7, 8)  # 1728 columns: 13.5 tiles of 128
-    assert torch.equal(mb.gemm_swiglu(xd, shard), y[:, 7 * 1728:])
+    for variant in ("mma", "mma2"):
+        assert torch.equal(mb.gemm_swiglu_out(xd, shard, variant=variant), y[:, 7 * 1728:]), variant

@@ -43,6 +43,12 @@ WORKLOADS = {
     "decode_m128": (128, 8192, 28672, "hbm", "decode-shaped weight streaming X[128,8192] W[2x28672,8192]"),
     "cpu_ref_case": (256, 1024, 2816, "tensor", "reference CPU-sized case X[256,1024] W[2x2816,1024]"),
 }
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu captures
+# summarised under profiles/ (bytes; key = workload@gpus).
+NCU_TRAFFIC = {
+    "llama3_8b_ffn@1": 833.9e6,  # profiles/swiglu_tc_kernel_pair_llama3_8b_ffn.md
+    "decode_m64@1": 945.1e6,     # profiles/swiglu_tc_kernel_stream_decode_m64.md
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 L2_FLUSH_BYTES = 256 << 20
 
@@ -278,6 +284,7 @@ def main():
         dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
     total_ms = float(total_ms.item())
     ms_per_step = total_ms / args.steps
+    kclk = mb.kernel_clock(local_rank)  # SM clock of the last timed kernel, measured inside the kernel
     status = mb.device_status(local_rank)
     if status["code"] != 0:
         raise SystemExit(f"kernel watchdog fired: {status}")
@@ -350,14 +357,8 @@ def main():
         e2e_scale = flops
     roof["kernel"] = "swiglu_tc_kernel"
     roof["kernel_ms"] = rank0_ms
-    traffic_file = ROOT / "profiles" / "traffic.json"
-    if traffic_file.exists():
-        try:
-            t = json.loads(traffic_file.read_text()).get(f"{args.workload}@{world}")
-            if t:
-                roof["traffic"] = t
-        except Exception:
-            pass
+    roof["traffic"] = NCU_TRAFFIC.get(f"{args.workload}@{world}")
+    roof["algorithmic_bytes"] = bytes_rank
 
     line = {
         "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -371,6 +372,13 @@ def main():
         "gpu_launches": args.steps,
         "clocks": clocks,
     }
+    if clocks is not None:
+        # nvidia-smi samples every 50 ms and mostly sees the gaps between millisecond kernels; the kernel's own
+        # cycle counter / wall timer ratio is the clock it really ran at (lower under the power cap)
+        line["clocks"]["kernel_sm_mhz"] = kclk["sm_mhz"]
+        if bound == "tensor" and kclk["sm_mhz"] > 0:
+            n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
+            line["roofline"]["tensor_pipe_frac_at_kernel_clock"] = achieved / (8192 * n_sm * kclk["sm_mhz"] * 1e6 / 1e12)
     if e2e is not None:
         ms, h2d, d2h, chunks = e2e
         line["e2e"] = {"value": e2e_scale / (ms * 1e-3) / (1e9 if bound == "hbm" else 1e12), "unit": unit,

@@ -502,18 +502,25 @@ static int make_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
   if (ctas < pair) return fail(MAGI_SWIGLU_ERR_VARIANT, "max_ctas=%d leaves no room for a CTA pair", max_ctas);
   if (block_n == 0) {
     if (variant == MAGI_SWIGLU_VARIANT_MMA2) {
-      // Widest tile that tensor memory holds (gate + up = 512 fp32 columns): fewest operand bytes per
-      // FLOP.  Among widths that waste no more columns than 256 does, take the widest.
-      int best = 256;
-      double best_waste = 1e30;
-      for (int bn = 256; bn >= 128; bn -= 16) {
-        const double waste = (double)((N + bn - 1) / bn * bn) / (double)N;
-        if (waste < best_waste - 0.02) {
-          best_waste = waste;
-          best = bn;
+      // Wide tiles move the fewest operand bytes per FLOP (256 columns fill tensor memory: gate + up = 512
+      // fp32 columns), but the persistent grid runs whole waves of tiles.  Measured on B200, one tile of
+      // width bn costs about (bn + 146) units of time (fixed part: epilogue, pipeline refill and the
+      // narrower tiles' lower operand reuse), so pick the width with the cheapest total of waves x tile cost.
+      if (N < 128) {
+        block_n = round_up((int)N, 16);
+      } else {
+        const int64_t units = ctas / 2;
+        const int64_t m_units = (M + 2 * kBM - 1) / (2 * kBM);
+        int64_t best_cost = -1;
+        for (int bn = 256; bn >= 128; bn -= 16) {
+          const int64_t tiles = m_units * ((N + bn - 1) / bn);
+          const int64_t cost = ((tiles + units - 1) / units) * (bn + 146);
+          if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            block_n = bn;
+          }
         }
       }
-      block_n = (N >= 128) ? best : round_up((int)N, 16);
     } else if (variant == MAGI_SWIGLU_VARIANT_MMA) {
       block_n = (N >= 128) ? 128 : round_up((int)N, 16);
     } else {

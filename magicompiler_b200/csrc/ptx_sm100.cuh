@@ -146,6 +146,12 @@ __device__ __forceinline__ uint64_t l2_policy_evict_normal() {
   asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
   return p;
 }
+// 256-bit store (32-byte aligned address): one full 32-byte sector per thread
+__device__ __forceinline__ void st_global_v8_hint(void* ptr, uint4 lo, uint4 hi, uint64_t policy) {
+  asm volatile("st.global.L2::cache_hint.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8}, %9;" ::"l"(ptr), "r"(lo.x),
+               "r"(lo.y), "r"(lo.z), "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w), "l"(policy)
+               : "memory");
+}
 __device__ __forceinline__ void st_global_v4_hint(void* ptr, uint4 v, uint64_t policy) {
   asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(ptr), "r"(v.x), "r"(v.y), "r"(v.z),
                "r"(v.w), "l"(policy)

@@ -78,6 +78,7 @@ struct KArgs {
   int n_mma;          // 1: one MMA of N = 2*block_n covers gate|up;  2: one MMA each
   uint32_t b_second;  // byte offset of the second MMA's weight rows inside a stage's weight tile
   int acc_bufs;       // tensor-memory accumulator buffers (2 = epilogue overlaps next tile)
+  int wide_store;     // y base and row pitch are 32-byte aligned: 256-bit stores (one full sector per thread)
   int x_hint, w_hint, y_hint;  // L2 eviction priority of X tiles, W tiles and Y stores: 0 normal, 1 first, 2 last
 };
 
@@ -128,7 +129,7 @@ __device__ __forceinline__ uint64_t l2_policy(int hint) {
   return hint == 1 ? l2_policy_evict_first() : (hint == 2 ? l2_policy_evict_last() : l2_policy_evict_normal());
 }
 
-__device__ __forceinline__ void store8(__nv_bfloat16* dst, const uint32_t* g, const uint32_t* u, uint64_t policy) {
+__device__ __forceinline__ uint4 swiglu_pack8(const uint32_t* g, const uint32_t* u) {
   uint4 v;
   __nv_bfloat162 p;
   p = __floats2bfloat162_rn(silu_mul(__uint_as_float(g[0]), __uint_as_float(u[0])),
@@ -143,11 +144,31 @@ __device__ __forceinline__ void store8(__nv_bfloat16* dst, const uint32_t* g, co
   p = __floats2bfloat162_rn(silu_mul(__uint_as_float(g[6]), __uint_as_float(u[6])),
                             silu_mul(__uint_as_float(g[7]), __uint_as_float(u[7])));
   v.w = *reinterpret_cast<uint32_t*>(&p);
+  return v;
+}
+
+// n (8, 16, 24 or 32 ...) consecutive outputs of one row starting at dst; `wide` = dst is 32-byte aligned
+template <int kCols>
+__device__ __forceinline__ void store_cols(__nv_bfloat16* dst, const uint32_t* g, const uint32_t* u, int cols_valid,
+                                           bool wide, uint64_t policy) {
 #ifdef MAGI_EXP_NOSTORE  // tuning experiment: epilogue without (almost all of) its global stores
-  if (v.x == 0x7fc07fc1u) st_global_v4_hint(dst, v, policy);
-#else
-  st_global_v4_hint(dst, v, policy);
+  if (g[0] != 0x7fc01234u) return;
 #endif
+#pragma unroll
+  for (int j = 0; j < kCols / 16; ++j) {
+    if (16 * j + 16 <= cols_valid) {
+      const uint4 lo = swiglu_pack8(g + 16 * j, u + 16 * j);
+      const uint4 hi = swiglu_pack8(g + 16 * j + 8, u + 16 * j + 8);
+      if (wide) {
+        st_global_v8_hint(dst + 16 * j, lo, hi, policy);
+      } else {
+        st_global_v4_hint(dst + 16 * j, lo, policy);
+        st_global_v4_hint(dst + 16 * j + 8, hi, policy);
+      }
+    } else if (16 * j + 8 <= cols_valid) {
+      st_global_v4_hint(dst + 16 * j, swiglu_pack8(g + 16 * j, u + 16 * j), policy);
+    }
+  }
 }
 
 template <int kCtas>
@@ -314,6 +335,7 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       const uint32_t t_gate = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * acc_cols);
       const uint32_t t_up = t_gate + (uint32_t)a.block_n;
       __nv_bfloat16* yrow = a.y + (long long)row * a.ldy + col0;
+      const bool wide = a.wide_store != 0;  // every 16-column group of every row starts on a 32-byte boundary
 
       // 32-column chunks alternate between the two warps of this lane quarter; a 16-column remainder
       // (block_n % 32 == 16) goes to whichever warp is next in turn
@@ -324,22 +346,14 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         tmem_ld_x32(t_gate + c, g);
         tmem_ld_x32(t_up + c, u);
         tmem_ld_wait();
-        if (row_ok) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            if (c + 8 * j + 8 <= valid) store8(yrow + c + 8 * j, g + 8 * j, u + 8 * j, y_policy);
-        }
+        if (row_ok) store_cols<32>(yrow + c, g, u, valid - c, wide, y_policy);
       }
       if (c + 16 == a.block_n && c < valid) {
         uint32_t g[16], u[16];
         tmem_ld_x16(t_gate + c, g);
         tmem_ld_x16(t_up + c, u);
         tmem_ld_wait();
-        if (row_ok) {
-#pragma unroll
-          for (int j = 0; j < 2; ++j)
-            if (c + 8 * j + 8 <= valid) store8(yrow + c + 8 * j, g + 8 * j, u + 8 * j, y_policy);
-        }
+        if (row_ok) store_cols<16>(yrow + c, g, u, valid - c, wide, y_policy);
       }
       MAGI_TRACE(6, it == 1 && warp == 4 && lane == 0);   // warp 4 drained its columns
       MAGI_TRACE(7, it == 1 && warp == 11 && lane == 0);  // warp 11 drained its columns
@@ -704,6 +718,7 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   a.n_mma = p.n_mma;
   a.b_second = p.b_second;
   a.acc_bufs = p.acc_bufs;
+  a.wide_store = (((uintptr_t)y & 31u) == 0 && ldy % 16 == 0) ? 1 : 0;
   // default L2 priorities: a band of X rows is re-read by every column tile -> keep; W tiles and Y are streamed
   a.x_hint = 2;
   a.w_hint = 1;

@@ -1,0 +1,188 @@
+"""Full-graph rewrite pass: ``silu(linear(x, Wg)) * linear(x, Wu)``  ->  ``gemm_swiglu(x, pack(Wg, Wu))``.
+
+This is the fusion pass MagiCompiler's ``PassConfig`` lists as a TODO (``magi_compiler/config.py:62``).  It has the
+shape of the reference's own full-graph passes (``passes/full_graph/replace_sage_atten.py:21-36``: a class with
+``is_applicable(graph)`` and ``__call__(graph)`` that retargets ``call_function`` nodes of the Dynamo graph) and is
+meant to run where ``ReplaceSageAttentionPass`` runs, before the graph is split
+(``passes/full_graph/full_graph_pass_mgr.py:27-38``), so that the new op becomes a split point.
+
+The two ``[N,K]`` weights have to become one ``[2N,K]`` tensor.  Concatenating on every call would copy the whole
+weight, so the pass routes them through ``magi_swiglu::pack_gate_up_cached``, a small op that packs once and returns
+the same buffer again for as long as the same two parameter objects are passed unmodified.
+"""
+from __future__ import annotations
+
+import operator
+import weakref
+
+import torch
+import torch.nn.functional as F
+
+from .register import magi_register_custom_op
+
+try:  # the reference's pass base class (uuid by source hash), when MagiCompiler is installed
+    from magi_compiler.passes.pass_base import MagiInductorPass as _PassBase  # type: ignore
+except Exception:  # pragma: no cover - depends on the environment
+    class _PassBase:  # same duck type: is_applicable(graph) / __call__(graph)
+        def is_applicable(self, graph, shape=None) -> bool:
+            return True
+
+
+PACK_OP_NAME = "magi_swiglu::pack_gate_up_cached"
+_pack_cache: dict[tuple[int, int], tuple] = {}
+
+
+def _pack_meta(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    return w_gate.new_empty((w_gate.shape[0] + w_up.shape[0], w_gate.shape[1]))
+
+
+@magi_register_custom_op(name=PACK_OP_NAME, mutates_args=(), infer_output_meta_fn=_pack_meta)
+def pack_gate_up_cached(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """``cat([w_gate, w_up])``, memoised on the identity, version counter and address of both arguments.
+
+    The cache entry dies with either argument (weak references).  A weight that is updated in place (optimizer
+    step) bumps its version counter and is packed again; tensors that are new objects on every call (a weight
+    offloaded to the host and brought back per iteration) are packed on every call.
+    """
+    if w_gate.dim() != 2 or w_gate.shape != w_up.shape or w_gate.dtype != w_up.dtype or w_gate.device != w_up.device:
+        raise ValueError(f"gate {tuple(w_gate.shape)}/{w_gate.dtype} and up {tuple(w_up.shape)}/{w_up.dtype} differ")
+    key = (id(w_gate), id(w_up))
+    stamp = (w_gate._version, w_up._version, w_gate.data_ptr(), w_up.data_ptr())
+    hit = _pack_cache.get(key)
+    if hit is not None:
+        ref_g, ref_u, old_stamp, packed = hit
+        if ref_g() is w_gate and ref_u() is w_up and old_stamp == stamp:
+            return packed
+    packed = torch.cat([w_gate, w_up], dim=0)
+
+    def _drop(_ref, key=key):
+        _pack_cache.pop(key, None)
+
+    try:
+        _pack_cache[key] = (weakref.ref(w_gate, _drop), weakref.ref(w_up, _drop), stamp, packed)
+    except TypeError:  # fake / functional tensors during tracing cannot be weakly referenced: do not cache
+        pass
+    return packed
+
+
+def clear_pack_cache() -> None:
+    _pack_cache.clear()
+
+
+_LINEAR_TARGETS = {F.linear, torch._C._nn.linear}
+_SILU_TARGETS = {F.silu, torch.ops.aten.silu.default, torch.ops.aten.silu}
+_MUL_TARGETS = {operator.mul, torch.mul, torch.ops.aten.mul.Tensor}
+
+
+def _is_linear_without_bias(node: torch.fx.Node) -> bool:
+    if node.op != "call_function" or node.target not in _LINEAR_TARGETS:
+        return False
+    bias = node.args[2] if len(node.args) > 2 else node.kwargs.get("bias")
+    return bias is None and len(node.args) >= 2
+
+
+def _example(node: torch.fx.Node):
+    return node.meta.get("example_value", node.meta.get("val"))
+
+
+def _is_bf16_on(devices: tuple[str, ...], *nodes: torch.fx.Node) -> bool:
+    """The op computes bf16 on CUDA only; skip a match that is known to be something else."""
+    for n in nodes:
+        ev = _example(n)
+        if isinstance(ev, torch.Tensor):
+            if ev.dtype != torch.bfloat16 or ev.device.type not in devices:
+                return False
+    return True
+
+
+class FuseSwiGLUPass(_PassBase):
+    """Rewrites every ``silu(linear(x, Wg)) * linear(x, Wu)`` (either operand order, bias-free linears that share
+    ``x``) of a Dynamo-level FX graph into ``gemm_swiglu(x, pack_gate_up_cached(Wg, Wu))``.
+
+    ``allowed_devices``: device types of the traced tensors for which the rewrite is made (the kernel exists for
+    CUDA; "meta" lets shape-only traces through; tests that stand a CPU function in for the kernel add "cpu")."""
+
+    def __init__(self, allowed_devices: tuple[str, ...] = ("cuda", "meta")):
+        self.allowed_devices = tuple(allowed_devices)
+
+    def _matches(self, graph: torch.fx.Graph):
+        found = []
+        for mul in graph.nodes:
+            is_mul = (mul.op == "call_function" and mul.target in _MUL_TARGETS) or \
+                     (mul.op == "call_method" and mul.target == "mul")
+            if not is_mul or len(mul.args) != 2 or not all(isinstance(a, torch.fx.Node) for a in mul.args):
+                continue
+            for act, up in (mul.args, mul.args[::-1]):
+                is_silu = (act.op == "call_function" and act.target in _SILU_TARGETS) or \
+                          (act.op == "call_method" and act.target == "silu")
+                if not is_silu or not act.args or not isinstance(act.args[0], torch.fx.Node):
+                    continue
+                gate = act.args[0]
+                if not (_is_linear_without_bias(gate) and _is_linear_without_bias(up)):
+                    continue
+                if gate.args[0] is not up.args[0] or gate is up:
+                    continue
+                if len(act.users) != 1 or len(gate.users) != 1 or len(up.users) != 1:
+                    continue  # an intermediate is used elsewhere: it must stay materialised
+                wg, wu = gate.args[1], up.args[1]
+                if not (isinstance(wg, torch.fx.Node) and isinstance(wu, torch.fx.Node)):
+                    continue
+                if not _is_bf16_on(self.allowed_devices, gate.args[0], wg, wu):
+                    continue
+                evg, evu = _example(wg), _example(wu)
+                if isinstance(evg, torch.Tensor) and isinstance(evu, torch.Tensor):
+                    if evg.dim() != 2 or evg.shape != evu.shape or evg.shape[0] % 8 or evg.shape[1] % 8:
+                        continue
+                found.append((mul, act, gate, up))
+                break
+        return found
+
+    def is_applicable(self, graph: torch.fx.Graph, shape: int | None = None) -> bool:
+        return bool(self._matches(graph))
+
+    def __call__(self, graph: torch.fx.Graph) -> int:
+        from .ops import gemm_swiglu  # registers the op
+
+        count = 0
+        for mul, act, gate, up in self._matches(graph):
+            x, wg, wu = gate.args[0], gate.args[1], up.args[1]
+            with graph.inserting_before(mul):
+                packed = graph.call_function(torch.ops.magi_swiglu.pack_gate_up_cached.default, (wg, wu))
+                fused = graph.call_function(torch.ops.magi_swiglu.gemm_swiglu.default, (x, packed))
+            for new, fn in ((packed, _pack_meta), (fused, None)):
+                try:  # carry shape metadata forward when the graph has it (fake tensors from Dynamo)
+                    if fn is not None:
+                        new.meta["example_value"] = fn(_example(wg), _example(wu))
+                    else:
+                        ex, ep = _example(x), packed.meta["example_value"]
+                        new.meta["example_value"] = ex.new_empty((*ex.shape[:-1], ep.shape[0] // 2))
+                except Exception:
+                    pass
+            mul.replace_all_uses_with(fused)
+            for dead in (mul, act, gate, up):
+                graph.erase_node(dead)
+            count += 1
+        if count:
+            graph.lint()
+        return count
+
+
+def install_into_magi_compiler(allowed_devices: tuple[str, ...] = ("cuda", "meta")) -> bool:
+    """Opt-in: make MagiCompiler's ``FullGraphPassManager`` run ``FuseSwiGLUPass`` first.  Returns False when
+    MagiCompiler is not importable.  (Upstream, the same effect is two lines in ``full_graph_pass_mgr.py``.)"""
+    try:
+        from magi_compiler.passes.full_graph import full_graph_pass_mgr as mgr  # type: ignore
+    except Exception:
+        return False
+    cls = mgr.FullGraphPassManager
+    if getattr(cls, "_magi_swiglu_installed", False):
+        return True
+    original_init = cls.__init__
+
+    def patched_init(self, pass_config):
+        original_init(self, pass_config)
+        self.passes.insert(0, FuseSwiGLUPass(allowed_devices))
+
+    cls.__init__ = patched_init
+    cls._magi_swiglu_installed = True
+    return True

@@ -63,3 +63,39 @@ def test_tensor_parallel_mlp_single_rank():
     got = mlp(x)
     ref = reference_mlp(x, w, wd)
     assert torch.allclose(got.float(), ref.float(), rtol=2e-2, atol=2e-2 * ref.float().abs().max().item())
+
+
+def test_rewrite_pass_on_gpu_matches_eager_module():
+    """An unmodified gate/up/down MLP (the reference's TransformerMLP structure) compiled with the rewrite pass runs
+    the fused kernel and matches its own eager execution; the packed weight is built once."""
+    import torch.nn.functional as F
+
+    from magicompiler_b200.passes import FuseSwiGLUPass, _pack_cache, clear_pack_cache
+
+    class MLP(torch.nn.Module):
+        def __init__(self, k=512, n=1024):
+            super().__init__()
+            self.gate_proj = torch.nn.Linear(k, n, bias=False, dtype=torch.bfloat16, device="cuda")
+            self.up_proj = torch.nn.Linear(k, n, bias=False, dtype=torch.bfloat16, device="cuda")
+            self.down_proj = torch.nn.Linear(n, k, bias=False, dtype=torch.bfloat16, device="cuda")
+
+        def forward(self, x):
+            return self.down_proj(F.silu(self.gate_proj(x)) * self.up_proj(x))
+
+    counts = []
+
+    def backend(gm, example_inputs):
+        counts.append(FuseSwiGLUPass()(gm.graph))
+        gm.recompile()
+        return gm.forward
+
+    torch.manual_seed(0)
+    clear_pack_cache()
+    torch._dynamo.reset()
+    m = MLP().requires_grad_(False)
+    cm = torch.compile(m, backend=backend, fullgraph=True, dynamic=True)
+    for rows in (300, 77):
+        x = torch.randn(rows, 512, device="cuda").to(torch.bfloat16)
+        got, ref = cm(x), m(x)
+        assert torch.allclose(got.float(), ref.float(), rtol=2e-2, atol=2e-2 * ref.float().abs().max().item())
+    assert counts == [1] and len(_pack_cache) == 1

@@ -90,7 +90,7 @@ int magi_swiglu_forward_bf16_ex(const void* x, const void* w_gate_up, void* y,
  * launching: out[0]=variant, out[1]=block_n, out[2]=stages, out[3]=grid CTAs,
  * out[4]=tiles, out[5]=dynamic shared memory bytes, out[6]=accumulator buffers,
  * out[7]=MMAs per K=16 step, out[8]=CTAs per tile (1 or 2), out[9]=row units per raster band,
- * out[10..11]=0 (reserved).  `sm_count` <= 0 means "query `device`".
+ * out[10]=1 if the tile is released to the MMA issuer in two halves, out[11]=0 (reserved).  `sm_count` <= 0 means "query `device`".
  * Needs no GPU when sm_count > 0.
  * Replaces: nothing in the reference. */
 int magi_swiglu_plan(int64_t M, int64_t N, int64_t K, int variant,
@@ -99,7 +99,7 @@ int magi_swiglu_plan(int64_t M, int64_t N, int64_t K, int variant,
 
 /* Reads (and clears) the device-side watchdog word of `device`.  Every wait in
  * the kernels is bounded; a wait that expires records
- * out[0]=code (0 = none; 1 = producer, 2 = mma issuer, 3 = epilogue),
+ * out[0]=code (0 = none; 1 = X producer, 2 = mma issuer, 3 = epilogue, 4 = W producer),
  * out[1]=block index, out[2]=pipeline stage or accumulator buffer, out[3]=phase.
  * This call SYNCHRONISES the device; it is for tests and debugging.
  * Replaces: nothing in the reference. */

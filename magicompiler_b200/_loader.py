@@ -123,7 +123,7 @@ def plan(M: int, N: int, K: int, variant: str | int = "auto", block_n: int = 0, 
     rc = lib.magi_swiglu_plan(M, N, K, v, block_n, stages, group_m, max_ctas, device, sm_count, out)
     if rc != 0:
         raise ValueError(f"magi_swiglu_plan failed ({rc}): {last_error()}")
-    keys = ["variant", "block_n", "stages", "grid", "tiles", "smem_bytes", "acc_bufs", "n_mma", "ctas", "group_m"]
+    keys = ["variant", "block_n", "stages", "grid", "tiles", "smem_bytes", "acc_bufs", "n_mma", "ctas", "group_m", "split"]
     return dict(zip(keys, list(out)))
 
 

@@ -16,8 +16,8 @@
 // pulls a third fewer bytes per FLOP through L2 and the ring is deeper.  The leader CTA (cluster rank 0)
 // issues the MMAs and owns the "stage full" barriers; both CTAs run their own producer and epilogue.
 //
-// Warp roles (384 threads): warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane),
-// warp 2 = tensor-memory allocator, warps 4..11 = epilogue (warp w reads TMEM lanes 32*(w%4)..+31;
+// Warp roles (384 threads): warps 0 and 3 = TMA producers (one lane each: X tiles, W tiles), warp 1 = MMA
+// issuer (one lane), warp 2 = tensor-memory allocator, warps 4..11 = epilogue (warp w reads TMEM lanes 32*(w%4)..+31;
 // the two warps of a lane quarter take alternate 32-column chunks of the tile).
 //
 // Every wait on an mbarrier is bounded: after kWaitLimitCycles the waiting role records itself in
@@ -56,8 +56,12 @@ __device__ unsigned long long g_clock_probe[2];
 // Tuning builds only: SM-cycle timestamps of block 0's second tile (MMA issuer and first epilogue warp).
 __device__ long long g_trace[16];
 #define MAGI_TRACE(slot, cond) do { if (blockIdx.x == 0 && (cond)) g_trace[slot] = clock64(); } while (0)
+#define MAGI_TRACE_T0() const long long trace_t0 = clock64()
+#define MAGI_TRACE_ADD(slot) do { if (blockIdx.x == 0) g_trace[slot] += clock64() - trace_t0; } while (0)
 #else
 #define MAGI_TRACE(slot, cond) do { } while (0)
+#define MAGI_TRACE_T0() do { } while (0)
+#define MAGI_TRACE_ADD(slot) do { } while (0)
 #endif
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
@@ -77,6 +81,8 @@ struct KArgs {
   uint32_t stage_bytes;
   int n_mma;          // 1: one MMA of N = 2*block_n covers gate|up;  2: one MMA each
   uint32_t b_second;  // byte offset of the second MMA's weight rows inside a stage's weight tile
+  int split;          // CTA pairs, two MMAs: tensor memory holds [gate_lo|up_lo|gate_hi|up_hi]; the low half of
+                      // the tile is handed back to the MMA issuer before the high half has been drained
   int acc_bufs;       // tensor-memory accumulator buffers (2 = epilogue overlaps next tile)
   int wide_store;     // y base and row pitch are 32-byte aligned: 256-bit stores (one full sector per thread)
   int x_hint, w_hint, y_hint;  // L2 eviction priority of X tiles, W tiles and Y stores: 0 normal, 1 first, 2 last
@@ -118,11 +124,7 @@ __device__ __forceinline__ void tile_coords(const KArgs& a, int t, int& mt, int&
 
 __device__ __forceinline__ float silu_mul(float g, float u) {
   // silu(g) = g / (1 + exp(-g)); ex2.approx + div.approx are far below bf16 resolution
-#ifdef MAGI_EXP_NOSILU  // tuning experiment: epilogue without the two special-function operations
-  return g * u;
-#else
   return __fdividef(g, 1.0f + __expf(-g)) * u;
-#endif
 }
 
 __device__ __forceinline__ uint64_t l2_policy(int hint) {
@@ -151,9 +153,6 @@ __device__ __forceinline__ uint4 swiglu_pack8(const uint32_t* g, const uint32_t*
 template <int kCols>
 __device__ __forceinline__ void store_cols(__nv_bfloat16* dst, const uint32_t* g, const uint32_t* u, int cols_valid,
                                            bool wide, uint64_t policy) {
-#ifdef MAGI_EXP_NOSTORE  // tuning experiment: epilogue without (almost all of) its global stores
-  if (g[0] != 0x7fc01234u) return;
-#endif
 #pragma unroll
   for (int j = 0; j < kCols / 16; ++j) {
     if (16 * j + 16 <= cols_valid) {
@@ -217,7 +216,7 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   const uint32_t tmem_base = tmem_slot;
   long long probe_c0 = 0;
   unsigned long long probe_t0 = 0;
-  if (blockIdx.x == 0 && threadIdx.x == 96) {  // an otherwise idle thread of warp 3
+  if (blockIdx.x == 0 && threadIdx.x == 64) {  // lane 0 of the allocator warp, idle between set-up and teardown
     probe_c0 = clock64();
     probe_t0 = global_timer_ns();
   }
@@ -225,10 +224,13 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   const int num_tiles = a.num_m_tiles * a.num_n_tiles;
   const int acc_cols = 2 * a.block_n;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer (every CTA loads its own tiles)
+  if (warp == 0 || warp == 3) {
+    // ------------------------------------------------------------ TMA producers (every CTA loads its own tiles)
+    // Two issuing threads, because one thread cannot issue tensor copies fast enough for the narrow tiles:
+    // warp 0 arms the "stage full" barrier and brings the X tile, warp 3 brings the W tile.
     if (lane == 0) {
-      const uint64_t x_policy = l2_policy(a.x_hint), w_policy = l2_policy(a.w_hint);
+      const bool x_role = (warp == 0);
+      const uint64_t policy = l2_policy(x_role ? a.x_hint : a.w_hint);
       // CTA pairs: the bytes of both CTAs are counted on the leader's barrier
       const uint32_t full_remote0 = (kCtas == 2) ? map_to_cta(full_bar(0), 0) : 0u;
       int stage = 0;
@@ -239,24 +241,31 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         tile_coords(a, t, mt, nt);
         const int row0 = (mt * kCtas + (int)cta_rank) * kBM;
         for (int kb = 0; kb < a.num_k_blocks; ++kb) {
-          if (!wait_bounded(empty_bar(stage), phase ^ 1u, &abort_flag, 1u, stage)) {
-            ok = false;
-            break;
+          {
+            MAGI_TRACE_T0();
+            if (!wait_bounded(empty_bar(stage), phase ^ 1u, &abort_flag, x_role ? 1u : 4u, stage)) {
+              ok = false;
+              break;
+            }
+            MAGI_TRACE_ADD(x_role ? 12 : 13);  // producers: cycles spent waiting for a free stage
           }
-          const uint32_t sa = tiles_base + stage * a.stage_bytes;
+          if (x_role && (kCtas == 1 || cta_rank == 0)) mbar_arrive_expect_tx(full_bar(stage), kCtas * a.stage_bytes);
+          const uint32_t bar = (kCtas == 2) ? full_remote0 + 8u * stage : full_bar(stage);
+          const uint32_t st_a = tiles_base + stage * a.stage_bytes;  // X tile of this stage
+          const uint32_t st_b = st_a + kABytes;                     // W rows of this stage
+          const int k0 = kb * kBK;  // past the end of K the copy is zero-filled
           if constexpr (kCtas == 1) {
-            mbar_arrive_expect_tx(full_bar(stage), a.stage_bytes);
-            tma_load_2d_hint(sa, &tm_x, full_bar(stage), kb * kBK, row0, x_policy);
-            tma_load_3d_hint(sa + kABytes, &tm_w, full_bar(stage), kb * kBK, nt * a.block_n, 0, w_policy);
+            if (x_role)
+              tma_load_2d_hint(st_a, &tm_x, bar, k0, row0, policy);
+            else
+              tma_load_3d_hint(st_b, &tm_w, bar, k0, nt * a.block_n, 0, policy);
           } else {
-            if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2u * a.stage_bytes);
-            const uint32_t bar = full_remote0 + 8u * stage;
-            tma_load_2d_pair_hint(sa, &tm_x, bar, kb * kBK, row0, x_policy);
-            if (a.n_mma == 1)  // this CTA's half of the N = 2*block_n operand: rank 0 = gate rows, rank 1 = up rows
-              tma_load_3d_pair_hint(sa + kABytes, &tm_w, bar, kb * kBK, nt * a.block_n, (int)cta_rank, w_policy);
-            else               // half of the gate rows and the matching half of the up rows
-              tma_load_3d_pair_hint(sa + kABytes, &tm_w, bar, kb * kBK,
-                                    nt * a.block_n + (int)cta_rank * (a.block_n / 2), 0, w_policy);
+            if (x_role)
+              tma_load_2d_pair_hint(st_a, &tm_x, bar, k0, row0, policy);
+            else if (a.n_mma == 1 || a.split)  // rank 0 brings the tile's gate rows, rank 1 its up rows
+              tma_load_3d_pair_hint(st_b, &tm_w, bar, k0, nt * a.block_n, (int)cta_rank, policy);
+            else  // half of the gate rows and the matching half of the up rows
+              tma_load_3d_pair_hint(st_b, &tm_w, bar, k0, nt * a.block_n + (int)cta_rank * (a.block_n / 2), 0, policy);
           }
           if (++stage == a.stages) {
             stage = 0;
@@ -278,29 +287,86 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         const int buf = (a.acc_bufs == 2) ? (it & 1) : 0;
         const uint32_t acc_phase = (a.acc_bufs == 2) ? ((it >> 1) & 1) : (it & 1);
         MAGI_TRACE(0, it == 2);  // issuer starts waiting for the accumulator of tile 2
-        if (!wait_bounded(acc_empty_bar(buf), acc_phase ^ 1u, &abort_flag, 2u, 16 + buf)) break;
+        {
+          MAGI_TRACE_T0();
+          if (!wait_bounded(acc_empty_bar(buf), acc_phase ^ 1u, &abort_flag, 2u, 16 + buf)) break;
+          MAGI_TRACE_ADD(15);  // issuer: cycles spent waiting for a free accumulator
+        }
         MAGI_TRACE(1, it == 2);  // accumulator free
         tc_fence_after_sync();
         const uint32_t d_gate = tmem_base + (uint32_t)(buf * acc_cols);
-        for (int kb = 0; kb < a.num_k_blocks; ++kb) {
-          if (!wait_bounded(full_bar(stage), phase, &abort_flag, 2u, stage)) {
-            ok = false;
-            break;
+        int kb = 0;
+        if (kCtas == 2 && a.split) {
+          // The low half [gate_lo|up_lo] is free while the epilogue still drains the high half: run the
+          // first MMA of as many K-steps as the ring holds, then wait for the high half and catch up.
+          const int ahead = min(a.stages, a.num_k_blocks);
+          int s2 = stage;
+          uint32_t p2 = phase;
+          for (int j = 0; j < ahead && ok; ++j) {
+            if (!wait_bounded(full_bar(s2), p2, &abort_flag, 2u, s2)) {
+              ok = false;
+              break;
+            }
+            MAGI_TRACE(2, it == 2 && j == 0);
+            tc_fence_after_sync();
+            const uint32_t sa = tiles_base + s2 * a.stage_bytes;
+#pragma unroll
+            for (int k = 0; k < kBK / 16; ++k)
+              umma_bf16<kCtas>(d_gate, umma_desc_k_sw128(sa + k * 32), umma_desc_k_sw128(sa + kABytes + k * 32), idesc,
+                               (uint32_t)((j | k) != 0));
+            if (++s2 == a.stages) {
+              s2 = 0;
+              p2 ^= 1u;
+            }
+          }
+          if (!ok) break;
+          if (!wait_bounded(acc_empty_bar(1), acc_phase ^ 1u, &abort_flag, 2u, 17)) break;
+          tc_fence_after_sync();
+          for (int j = 0; j < ahead; ++j) {
+            const uint32_t sa = tiles_base + stage * a.stage_bytes;
+#pragma unroll
+            for (int k = 0; k < kBK / 16; ++k)
+              umma_bf16<kCtas>(d_gate + a.block_n, umma_desc_k_sw128(sa + k * 32),
+                               umma_desc_k_sw128(sa + kABytes + a.b_second + k * 32), idesc, (uint32_t)((j | k) != 0));
+            umma_commit<kCtas>(empty_bar(stage));
+            if (++stage == a.stages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+          kb = ahead;
+        }
+        for (; kb < a.num_k_blocks; ++kb) {
+          {
+            MAGI_TRACE_T0();
+            if (!wait_bounded(full_bar(stage), phase, &abort_flag, 2u, stage)) {
+              ok = false;
+              break;
+            }
+            MAGI_TRACE_ADD(14);  // issuer: cycles spent waiting for operands
           }
           MAGI_TRACE(2, it == 2 && kb == 0);                   // first stage of tile 2 available
           MAGI_TRACE(3, it == 1 && kb == a.num_k_blocks - 1);  // last stage of tile 1 available
           tc_fence_after_sync();
-          const uint32_t sa = tiles_base + stage * a.stage_bytes;
-          const uint32_t sb = sa + kABytes;
+          {
+            MAGI_TRACE_T0();
+            const uint32_t sa = tiles_base + stage * a.stage_bytes;
+            const uint32_t sb = sa + kABytes;
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k) {
-            const uint32_t acc = (kb | k) != 0;
-            const uint64_t ad = umma_desc_k_sw128(sa + k * 32);
-            umma_bf16<kCtas>(d_gate, ad, umma_desc_k_sw128(sb + k * 32), idesc, acc);
-            if (a.n_mma == 2)
-              umma_bf16<kCtas>(d_gate + a.block_n, ad, umma_desc_k_sw128(sb + a.b_second + k * 32), idesc, acc);
+            for (int k = 0; k < kBK / 16; ++k) {
+              const uint32_t acc = (kb | k) != 0;
+              const uint64_t ad = umma_desc_k_sw128(sa + k * 32);
+              umma_bf16<kCtas>(d_gate, ad, umma_desc_k_sw128(sb + k * 32), idesc, acc);
+              if (a.n_mma == 2)
+                umma_bf16<kCtas>(d_gate + a.block_n, ad, umma_desc_k_sw128(sb + a.b_second + k * 32), idesc, acc);
+            }
+            MAGI_TRACE_ADD(10);  // issuer: cycles spent issuing MMAs
           }
-          umma_commit<kCtas>(empty_bar(stage));  // frees the stage (in both CTAs) once these MMAs have read it
+          {
+            MAGI_TRACE_T0();
+            umma_commit<kCtas>(empty_bar(stage));  // frees the stage (in both CTAs) once these MMAs have read it
+            MAGI_TRACE_ADD(11);  // issuer: cycles spent in the commit
+          }
           if (++stage == a.stages) {
             stage = 0;
             phase ^= 1u;
@@ -331,39 +397,73 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       const int row = (mt * kCtas + (int)cta_rank) * kBM + q * 32 + lane;
       const bool row_ok = row < a.M;
       const int col0 = nt * a.block_n;
-      const int valid = min(a.block_n, a.N - col0);  // multiple of 8
-      const uint32_t t_gate = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * acc_cols);
-      const uint32_t t_up = t_gate + (uint32_t)a.block_n;
-      __nv_bfloat16* yrow = a.y + (long long)row * a.ldy + col0;
+      const int valid_tile = min(a.block_n, a.N - col0);  // multiple of 8
+      const uint32_t t_tile = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * acc_cols);
+      __nv_bfloat16* yrow_tile = a.y + (long long)row * a.ldy + col0;
       const bool wide = a.wide_store != 0;  // every 16-column group of every row starts on a 32-byte boundary
 
-      // 32-column chunks alternate between the two warps of this lane quarter; a 16-column remainder
-      // (block_n % 32 == 16) goes to whichever warp is next in turn
-      const int half = (warp - 4) >> 2;
-      int c = 32 * half;
-      for (; c + 32 <= a.block_n && c < valid; c += 64) {
+      // A tile is drained in one segment (gate columns [0,bn), up columns [bn,2bn)) or, in split mode, in two
+      // (low half then high half, each [gate|up] of bn/2 columns) that are released separately.
+      const int num_seg = (kCtas == 2 && a.split) ? 2 : 1;
+      const int seg_cols = a.block_n / num_seg;
+      for (int seg = 0; seg < num_seg; ++seg) {
+        const uint32_t t_gate = t_tile + (uint32_t)(seg * a.block_n);
+        const uint32_t t_up = t_gate + (uint32_t)seg_cols;
+        const int valid = max(0, min(seg_cols, valid_tile - seg * seg_cols));
+        __nv_bfloat16* yrow = yrow_tile + seg * seg_cols;
+        const int release_buf = (num_seg == 2) ? seg : buf;
+
+        // 32-column chunks alternate between the two warps of this lane quarter; a 16-column remainder goes to
+        // whichever warp is next in turn.  The accumulator segment is handed back to the MMA issuer as soon as
+        // this warp's LAST load from it has landed, so that chunk's arithmetic and stores overlap the next MMAs.
+        auto width_at = [&](int c) {
+          return (c < valid && c + 32 <= seg_cols) ? 32 : ((c < valid && c + 16 == seg_cols) ? 16 : 0);
+        };
+        auto load = [&](uint32_t (&g)[32], uint32_t (&u)[32], int c, int w) {
+          if (w == 32) {
+            tmem_ld_x32(t_gate + c, g);
+            tmem_ld_x32(t_up + c, u);
+          } else {
+            tmem_ld_x16_into32(t_gate + c, g);
+            tmem_ld_x16_into32(t_up + c, u);
+          }
+        };
+        auto process = [&](const uint32_t (&g)[32], const uint32_t (&u)[32], int c, int w) {
+          if (!row_ok) return;
+          if (w == 32)
+            store_cols<32>(yrow + c, g, u, valid - c, wide, y_policy);
+          else
+            store_cols<16>(yrow + c, g, u, valid - c, wide, y_policy);
+        };
+        auto release = [&]() {
+          MAGI_TRACE(6 + seg * 4, it == 1 && warp == 4 && lane == 0);  // warp 4 has read its last column
+          MAGI_TRACE(7 + seg * 4, it == 1 && warp == 11 && lane == 0);
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (kCtas == 1)
+              mbar_arrive(acc_empty_bar(release_buf));
+            else  // the leader's MMA issuer waits for both CTAs
+              mbar_arrive_cluster(acc_empty_remote0 + 8u * release_buf);
+          }
+        };
         uint32_t g[32], u[32];
-        tmem_ld_x32(t_gate + c, g);
-        tmem_ld_x32(t_up + c, u);
-        tmem_ld_wait();
-        if (row_ok) store_cols<32>(yrow + c, g, u, valid - c, wide, y_policy);
-      }
-      if (c + 16 == a.block_n && c < valid) {
-        uint32_t g[16], u[16];
-        tmem_ld_x16(t_gate + c, g);
-        tmem_ld_x16(t_up + c, u);
-        tmem_ld_wait();
-        if (row_ok) store_cols<16>(yrow + c, g, u, valid - c, wide, y_policy);
-      }
-      MAGI_TRACE(6, it == 1 && warp == 4 && lane == 0);   // warp 4 drained its columns
-      MAGI_TRACE(7, it == 1 && warp == 11 && lane == 0);  // warp 11 drained its columns
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) {
-        if constexpr (kCtas == 1)
-          mbar_arrive(acc_empty_bar(buf));
-        else
-          mbar_arrive_cluster(acc_empty_remote0 + 8u * buf);  // the leader's MMA issuer waits for both CTAs
+        int c = 32 * ((warp - 4) >> 2);
+        int w = width_at(c);
+        bool released = false;
+        while (w) {
+          load(g, u, c, w);
+          tmem_ld_wait();
+          const int c2 = c + 64, w2 = width_at(c2);
+          if (!w2) {  // that was this warp's last read of the segment
+            release();
+            released = true;
+          }
+          process(g, u, c, w);
+          c = c2;
+          w = w2;
+        }
+        if (!released) release();
       }
     }
   }
@@ -378,7 +478,7 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (blockIdx.x == 0 && threadIdx.x == 96) {
+  if (blockIdx.x == 0 && threadIdx.x == 64) {
     g_clock_probe[0] = (unsigned long long)(clock64() - probe_c0);
     g_clock_probe[1] = global_timer_ns() - probe_t0;
   }
@@ -483,6 +583,7 @@ struct Plan {
   int variant, block_n, stages, grid, tiles, smem_bytes, acc_bufs, n_mma;
   int num_m_tiles, num_n_tiles, num_k_blocks, group_m;
   int ctas;  // CTAs per tile: 1, or 2 for the CTA-pair schedule
+  int split; // CTA pairs with two MMAs per step and block_n % 32 == 0: two separately released half tiles
   uint32_t stage_bytes, b_second;
 };
 
@@ -526,7 +627,7 @@ static int make_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
         const int64_t units = ctas / 2;
         const int64_t m_units = (M + 2 * kBM - 1) / (2 * kBM);
         int64_t best_cost = -1;
-        for (int bn = 256; bn >= 128; bn -= 16) {
+        for (int bn = 256; bn >= 128; bn -= 32) {  // multiples of 32: both half tiles stay multiples of 16
           const int64_t tiles = m_units * ((N + bn - 1) / bn);
           const int64_t cost = ((tiles + units - 1) / units) * (bn + 146);
           if (best_cost < 0 || cost < best_cost) {
@@ -552,6 +653,7 @@ static int make_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
   // weight rows per CTA and stage: gate + up rows of the tile, split between the CTAs of a pair
   p->stage_bytes = kABytes + 2u * (uint32_t)block_n * 128u / (uint32_t)pair;
   p->b_second = (uint32_t)block_n * 128u / (uint32_t)pair;
+  p->split = (pair == 2 && p->n_mma == 2 && block_n % 32 == 0 && !getenv("MAGI_SWIGLU_NO_SPLIT")) ? 1 : 0;
   const int fit = (kSmemLimit - 1024) / (int)p->stage_bytes;
   int max_stages = fit < kMaxStages ? fit : kMaxStages;
   if (stages == 0) stages = max_stages;
@@ -591,16 +693,16 @@ static int encode_maps(const void* x, const void* w, int64_t M, int64_t N, int64
     if (r != CUDA_SUCCESS) return fail(MAGI_SWIGLU_ERR_DRIVER, "tensor map for X rejected by the driver (CUresult %d)", (int)r);
   }
   {
-    // W viewed as [2][N][K]: one box brings block_n gate rows and the matching block_n up rows
-    const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)N, 2};
-    const cuuint64_t strides[2] = {(cuuint64_t)ldw * 2, (cuuint64_t)N * (cuuint64_t)ldw * 2};
-    // one CTA per tile: block_n gate rows + block_n up rows.  CTA pair: each CTA brings half of the MMA's
-    // weight rows — all gate rows or all up rows when one MMA covers gate|up, else half of each.
+    // W viewed as [2][N][K].  One CTA per tile: one box brings block_n gate rows and the matching block_n up
+    // rows.  CTA pair: each CTA brings half of the MMA's weight rows — all gate rows or all up rows when one
+    // MMA covers gate|up or the tile is split in halves, else half of each.
     cuuint32_t box_rows = (cuuint32_t)p.block_n, box_halves = 2;
     if (p.ctas == 2) {
-      if (p.n_mma == 1) box_halves = 1;
+      if (p.n_mma == 1 || p.split) box_halves = 1;  // rank 0 loads gate rows, rank 1 up rows
       else box_rows = (cuuint32_t)p.block_n / 2;
     }
+    const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)N, 2};
+    const cuuint64_t strides[2] = {(cuuint64_t)ldw * 2, (cuuint64_t)N * (cuuint64_t)ldw * 2};
     const cuuint32_t box[3] = {(cuuint32_t)kBK, box_rows, box_halves};
     const cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = enc(tm_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(w), dims, strides, box, estr,
@@ -717,6 +819,7 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   a.stage_bytes = p.stage_bytes;
   a.n_mma = p.n_mma;
   a.b_second = p.b_second;
+  a.split = p.split;
   a.acc_bufs = p.acc_bufs;
   a.wide_store = (((uintptr_t)y & 31u) == 0 && ldy % 16 == 0) ? 1 : 0;
   // default L2 priorities: a band of X rows is re-read by every column tile -> keep; W tiles and Y are streamed
@@ -801,7 +904,7 @@ int magi_swiglu_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
   out[7] = p.n_mma;
   out[8] = p.ctas;
   out[9] = p.group_m;
-  out[10] = 0;
+  out[10] = p.split;
   out[11] = 0;
   return 0;
 }
@@ -828,9 +931,12 @@ int magi_swiglu_device_status(int device, int32_t out[4]) {
 }
 
 #ifdef MAGI_SWIGLU_TRACE
-int magi_swiglu_trace(long long out[16]) {
+int magi_swiglu_trace(long long out[16]) {  // reads the trace and clears its accumulating slots
   cudaDeviceSynchronize();
-  return (int)cudaMemcpyFromSymbol(out, magi::g_trace, sizeof(long long) * 16);
+  int rc = (int)cudaMemcpyFromSymbol(out, magi::g_trace, sizeof(long long) * 16);
+  long long zero[16] = {0};
+  cudaMemcpyToSymbol(magi::g_trace, zero, sizeof(zero));
+  return rc;
 }
 #endif
 

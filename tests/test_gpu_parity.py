@@ -93,7 +93,7 @@ def test_ragged_shapes(shape, variant):
     assert_parity(y, swiglu_gold(x, w, want_eager=False)["gold"], f"{shape} {variant}")
 
 
-@pytest.mark.parametrize("block_n", [16, 32, 48, 64, 96, 112, 128, 144, 208, 256])
+@pytest.mark.parametrize("block_n", [16, 32, 48, 64, 96, 112, 128, 144, 160, 192, 208, 224, 256])
 @pytest.mark.parametrize("stages,max_ctas,group_m", [(0, 0, 0), (2, 2, 1), (3, 6, 2)])
 @pytest.mark.parametrize("variant", ["mma", "mma2"])
 def test_schedule_knobs(variant, block_n, stages, max_ctas, group_m):

@@ -42,6 +42,8 @@ WORKLOADS = {
     "decode_m64": (64, 8192, 28672, "hbm", "decode-shaped weight streaming X[64,8192] W[2x28672,8192]"),
     "decode_m128": (128, 8192, 28672, "hbm", "decode-shaped weight streaming X[128,8192] W[2x28672,8192]"),
     "cpu_ref_case": (256, 1024, 2816, "tensor", "reference CPU-sized case X[256,1024] W[2x2816,1024]"),
+    # full SwiGLU MLP: fused column-parallel gate/up, row-parallel down projection, NCCL all-reduce (see run_mlp_block)
+    "mlp_block": (16384, 8192, 28672, "tensor", "SwiGLU MLP block X[16384,8192], gate/up [2x28672,8192], down [8192,28672]"),
 }
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (bytes; key = workload@gpus).
@@ -190,6 +192,63 @@ def run_reference_arm(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_mlp_block(args, rank, world, local_rank):
+    """Config 5: gate/up column-parallel through the fused op, down projection row-parallel (library GEMM), one
+    all-reduce over NVLink, optionally chunked so the reduce of chunk i overlaps the GEMMs of chunk i+1."""
+    import torch.distributed as dist
+
+    import magicompiler_b200 as mb
+    from oracle import make_inputs
+
+    dev = torch.device("cuda", local_rank)
+    M, K, N, _, desc = WORKLOADS["mlp_block"]
+    x_cpu, w_cpu, wd_cpu = make_inputs(M, K, N, seed=0, with_down=True)
+    mlp = mb.TensorParallelSwiGLUMLP(w_cpu, wd_cpu, rank, world, chunks=args.chunks).to(dev)
+    del w_cpu, wd_cpu
+    x = x_cpu.to(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(args.warmup):
+        mlp(x)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        out = mlp(x)
+    e1.record()
+    barrier()
+    ms = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms.item())
+    status = mb.device_status(local_rank)
+    if status["code"] != 0:
+        raise SystemExit(f"kernel watchdog fired: {status}")
+    if rank == 0:
+        flops = 2.0 * M * K * 2 * N + 2.0 * M * N * K
+        peaks, kind = measured_peaks()
+        value = flops / (ms * 1e-3) / 1e12
+        per_gpu = value / world
+        print(json.dumps({
+            "metric": "SwiGLU MLP block TFLOP/s (fused gate/up + down projection + all-reduce)", "value": value,
+            "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (CPU generator seed 0, X~N(0,1), W~N(0,0.02), bf16)",
+            "config": {"workload": "mlp_block", "shape": desc, "chunks": args.chunks,
+                       "parallelism": f"tp{world}: column-parallel gate/up, row-parallel down, NCCL all-reduce of "
+                                      f"[{M},{K}] bf16", "l2": "inputs (1.7 GB) larger than L2, back-to-back steps"},
+            "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": float(peaks["bf16_tflops_sustained"]),
+                         "unit": "TFLOP/s", "frac": per_gpu / float(peaks["bf16_tflops_sustained"]), "traffic": None,
+                         "peak_kind": f"{kind} cuBLAS bf16 sustained (kernels timed inside a long step)"},
+            "gpu_launches": args.steps * args.chunks}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -201,6 +260,7 @@ def main():
     ap.add_argument("--block-n", type=int, default=0)
     ap.add_argument("--stages", type=int, default=0)
     ap.add_argument("--group-m", type=int, default=0)
+    ap.add_argument("--chunks", type=int, default=1, help="mlp_block: row chunks whose all-reduce overlaps the next chunk")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-flush", action="store_true", help="profiling runs only: skip the L2 flush kernels")
@@ -230,6 +290,9 @@ def main():
     if lib.magi_swiglu_supported(local_rank) != 1:
         raise SystemExit("this benchmark needs a B200 (sm_100)")
 
+    if args.workload == "mlp_block":
+        run_mlp_block(args, rank, world, local_rank)
+        return
     M, K, N, bound, desc = WORKLOADS[args.workload]
     x_cpu, w_cpu = make_inputs(M, K, N, seed=0)
     w_local_cpu = mb.shard_gate_up(w_cpu, rank, world) if world > 1 else w_cpu

@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define MAGI_SWIGLU_ABI_VERSION 2
+#define MAGI_SWIGLU_ABI_VERSION 3
 
 /* variant selector of magi_swiglu_forward_bf16 */
 #define MAGI_SWIGLU_VARIANT_AUTO   0  /* M <= 128 -> STREAM, else MMA2           */
@@ -86,11 +86,33 @@ int magi_swiglu_forward_bf16_ex(const void* x, const void* w_gate_up, void* y,
                                 int device, void* cuda_stream, int variant,
                                 int block_n, int stages, int group_m, int max_ctas);
 
-/* Describes the schedule magi_swiglu_forward_bf16_ex would use, without
+/* Same as magi_swiglu_forward_bf16_ex, with caller-owned scratch memory.  Narrow weights with M <= 128 (a
+ * column shard of a decode GEMM) run faster when several CTAs share a slab of W and split K between them; their
+ * fp32 partial sums live in `workspace` (device memory, 256-byte aligned, `workspace_bytes` long) and a second,
+ * small kernel on the same stream adds them in a fixed order and writes Y.  magi_swiglu_workspace_bytes() tells
+ * how much the best schedule wants; with less (or NULL) a schedule that fits is used.  The workspace needs no
+ * initialisation and holds nothing between calls.  Two launches that may overlap on the GPU must not share a
+ * workspace.  The library itself allocates nothing.
+ * Replaces: nothing in the reference. */
+int magi_swiglu_forward_bf16_ws(const void* x, const void* w_gate_up, void* y,
+                                int64_t M, int64_t N, int64_t K,
+                                int64_t ldx, int64_t ldw, int64_t ldy,
+                                int device, void* cuda_stream, int variant,
+                                int block_n, int stages, int group_m, int max_ctas,
+                                void* workspace, int64_t workspace_bytes);
+
+/* Scratch bytes the preferred schedule of magi_swiglu_forward_bf16_ws wants for this problem (0 = none needed;
+ * negative = argument error).  Needs no GPU when sm_count > 0.
+ * Replaces: nothing in the reference. */
+int64_t magi_swiglu_workspace_bytes(int64_t M, int64_t N, int64_t K, int variant,
+                                    int block_n, int stages, int group_m, int max_ctas,
+                                    int device, int sm_count);
+
+/* Describes the schedule magi_swiglu_forward_bf16_ws would use when given all the scratch it asks for, without
  * launching: out[0]=variant, out[1]=block_n, out[2]=stages, out[3]=grid CTAs,
  * out[4]=tiles, out[5]=dynamic shared memory bytes, out[6]=accumulator buffers,
  * out[7]=MMAs per K=16 step, out[8]=CTAs per tile (1 or 2), out[9]=row units per raster band,
- * out[10]=1 if the tile is released to the MMA issuer in two halves, out[11]=0 (reserved).  `sm_count` <= 0 means "query `device`".
+ * out[10]=1 if the tile is released to the MMA issuer in two halves, out[11]=CTAs that split K for one tile.  `sm_count` <= 0 means "query `device`".
  * Needs no GPU when sm_count > 0.
  * Replaces: nothing in the reference. */
 int magi_swiglu_plan(int64_t M, int64_t N, int64_t K, int variant,

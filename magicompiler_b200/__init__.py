@@ -5,7 +5,7 @@ before a model is decorated with ``magi_compile`` so the op is a graph split poi
 before ahead-of-time artifacts that mention the op are deserialised.
 """
 from ._loader import (MagiSwigluLibraryError, build_library, device_status, kernel_clock, load_library,  # noqa: F401
-                      plan)
+                      plan, workspace_bytes)
 from .ops import OP_NAME, gemm_swiglu, gemm_swiglu_out  # noqa: F401
 from .passes import FuseSwiGLUPass, install_into_magi_compiler, pack_gate_up_cached  # noqa: F401
 from .register import COMPUTE_SENSITIVE_OPS, SPLITTING_OPS, magi_register_custom_op  # noqa: F401
@@ -22,5 +22,5 @@ __all__ = [
     "gemm_swiglu", "gemm_swiglu_out", "OP_NAME", "pack_gate_up", "shard_gate_up", "shard_down", "shard_bounds",
     "ColumnParallelSwiGLU", "TensorParallelSwiGLUMLP", "FuseSwiGLUPass", "install_into_magi_compiler",
     "pack_gate_up_cached", "magi_register_custom_op", "SPLITTING_OPS",
-    "COMPUTE_SENSITIVE_OPS", "build_library", "load_library", "plan", "device_status", "kernel_clock", "MagiSwigluLibraryError",
+    "COMPUTE_SENSITIVE_OPS", "build_library", "load_library", "plan", "workspace_bytes", "device_status", "kernel_clock", "MagiSwigluLibraryError",
 ]

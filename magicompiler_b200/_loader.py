@@ -25,7 +25,7 @@ NVCC_FLAGS = [
     "-shared", "-Xcompiler", "-fPIC",
 ]
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 VARIANT_AUTO, VARIANT_MMA, VARIANT_STREAM, VARIANT_SIMT, VARIANT_MMA2 = 0, 1, 2, 3, 4
 VARIANTS = {"auto": VARIANT_AUTO, "mma": VARIANT_MMA, "stream": VARIANT_STREAM, "simt": VARIANT_SIMT,
             "mma2": VARIANT_MMA2}
@@ -76,6 +76,11 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.magi_swiglu_forward_bf16_ex.restype = i32
     lib.magi_swiglu_forward_bf16_ex.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, vp, i32,
                                                 i32, i32, i32, i32]
+    lib.magi_swiglu_forward_bf16_ws.restype = i32
+    lib.magi_swiglu_forward_bf16_ws.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, vp, i32,
+                                                i32, i32, i32, i32, vp, i64]
+    lib.magi_swiglu_workspace_bytes.restype = i64
+    lib.magi_swiglu_workspace_bytes.argtypes = [i64, i64, i64, i32, i32, i32, i32, i32, i32, i32]
     lib.magi_swiglu_plan.restype = i32
     lib.magi_swiglu_plan.argtypes = [i64, i64, i64, i32, i32, i32, i32, i32, i32, i32, ctypes.POINTER(ctypes.c_int32)]
     lib.magi_swiglu_device_status.restype = i32
@@ -123,8 +128,19 @@ def plan(M: int, N: int, K: int, variant: str | int = "auto", block_n: int = 0, 
     rc = lib.magi_swiglu_plan(M, N, K, v, block_n, stages, group_m, max_ctas, device, sm_count, out)
     if rc != 0:
         raise ValueError(f"magi_swiglu_plan failed ({rc}): {last_error()}")
-    keys = ["variant", "block_n", "stages", "grid", "tiles", "smem_bytes", "acc_bufs", "n_mma", "ctas", "group_m", "split"]
+    keys = ["variant", "block_n", "stages", "grid", "tiles", "smem_bytes", "acc_bufs", "n_mma", "ctas", "group_m", "split", "k_splits"]
     return dict(zip(keys, list(out)))
+
+
+def workspace_bytes(M: int, N: int, K: int, variant: str | int = "auto", block_n: int = 0, stages: int = 0,
+                    group_m: int = 0, max_ctas: int = 0, device: int = 0, sm_count: int = 0) -> int:
+    """Scratch bytes the preferred schedule wants (0 = none)."""
+    lib = load_library()
+    v = VARIANTS[variant] if isinstance(variant, str) else int(variant)
+    n = lib.magi_swiglu_workspace_bytes(M, N, K, v, block_n, stages, group_m, max_ctas, device, sm_count)
+    if n < 0:
+        raise ValueError(f"magi_swiglu_workspace_bytes failed ({n}): {last_error()}")
+    return int(n)
 
 
 def device_status(device: int = 0) -> dict:

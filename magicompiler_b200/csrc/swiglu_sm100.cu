@@ -86,6 +86,11 @@ struct KArgs {
   int acc_bufs;       // tensor-memory accumulator buffers (2 = epilogue overlaps next tile)
   int wide_store;     // y base and row pitch are 32-byte aligned: 256-bit stores (one full sector per thread)
   int x_hint, w_hint, y_hint;  // L2 eviction priority of X tiles, W tiles and Y stores: 0 normal, 1 first, 2 last
+  // Split-K (STREAM schedule on narrow weights): k_splits CTAs share one tile, each sums kb_per_split K-steps and
+  // parks its fp32 partial sums in `ws`; swiglu_splitk_reduce_kernel adds them in split order and writes Y.
+  // k_splits == 1: no scratch is touched.
+  int k_splits, kb_per_split;
+  float* ws;  // [tile][split][M rows][2*block_n] fp32
 };
 
 __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned role,
@@ -221,7 +226,7 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     probe_t0 = global_timer_ns();
   }
 
-  const int num_tiles = a.num_m_tiles * a.num_n_tiles;
+  const int num_items = a.num_m_tiles * a.num_n_tiles * a.k_splits;  // (tile, K split) work items
   const int acc_cols = 2 * a.block_n;
 
   if (warp == 0 || warp == 3) {
@@ -236,11 +241,14 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = unit; t < num_tiles && ok; t += units) {
+      for (int item = unit; item < num_items && ok; item += units) {
+        const int t = item / a.k_splits;
+        const int kb0 = (item - t * a.k_splits) * a.kb_per_split;
+        const int kb1 = min(a.num_k_blocks, kb0 + a.kb_per_split);
         int mt, nt;
         tile_coords(a, t, mt, nt);
         const int row0 = (mt * kCtas + (int)cta_rank) * kBM;
-        for (int kb = 0; kb < a.num_k_blocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           {
             MAGI_TRACE_T0();
             if (!wait_bounded(empty_bar(stage), phase ^ 1u, &abort_flag, x_role ? 1u : 4u, stage)) {
@@ -283,7 +291,9 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = unit; t < num_tiles && ok; t += units, ++it) {
+      for (int item = unit; item < num_items && ok; item += units, ++it) {
+        const int kb0 = (item % a.k_splits) * a.kb_per_split;  // split-K is never combined with CTA pairs
+        const int kb1 = min(a.num_k_blocks, kb0 + a.kb_per_split);
         const int buf = (a.acc_bufs == 2) ? (it & 1) : 0;
         const uint32_t acc_phase = (a.acc_bufs == 2) ? ((it >> 1) & 1) : (it & 1);
         MAGI_TRACE(0, it == 2);  // issuer starts waiting for the accumulator of tile 2
@@ -295,7 +305,7 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         MAGI_TRACE(1, it == 2);  // accumulator free
         tc_fence_after_sync();
         const uint32_t d_gate = tmem_base + (uint32_t)(buf * acc_cols);
-        int kb = 0;
+        int kb = kb0;
         if (kCtas == 2 && a.split) {
           // The low half [gate_lo|up_lo] is free while the epilogue still drains the high half: run the
           // first MMA of as many K-steps as the ring holds, then wait for the high half and catch up.
@@ -336,7 +346,7 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
           }
           kb = ahead;
         }
-        for (; kb < a.num_k_blocks; ++kb) {
+        for (; kb < kb1; ++kb) {
           {
             MAGI_TRACE_T0();
             if (!wait_bounded(full_bar(stage), phase, &abort_flag, 2u, stage)) {
@@ -346,7 +356,7 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
             MAGI_TRACE_ADD(14);  // issuer: cycles spent waiting for operands
           }
           MAGI_TRACE(2, it == 2 && kb == 0);                   // first stage of tile 2 available
-          MAGI_TRACE(3, it == 1 && kb == a.num_k_blocks - 1);  // last stage of tile 1 available
+          MAGI_TRACE(3, it == 1 && kb == kb1 - 1);  // last stage of tile 1 available
           tc_fence_after_sync();
           {
             MAGI_TRACE_T0();
@@ -354,7 +364,7 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
             const uint32_t sb = sa + kABytes;
 #pragma unroll
             for (int k = 0; k < kBK / 16; ++k) {
-              const uint32_t acc = (kb | k) != 0;
+              const uint32_t acc = ((kb - kb0) | k) != 0;
               const uint64_t ad = umma_desc_k_sw128(sa + k * 32);
               umma_bf16<kCtas>(d_gate, ad, umma_desc_k_sw128(sb + k * 32), idesc, acc);
               if (a.n_mma == 2)
@@ -383,7 +393,9 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     const uint64_t y_policy = l2_policy(a.y_hint);
     const uint32_t acc_empty_remote0 = (kCtas == 2) ? map_to_cta(acc_empty_bar(0), 0) : 0u;
     int it = 0;
-    for (int t = unit; t < num_tiles; t += units, ++it) {
+    for (int item = unit; item < num_items; item += units, ++it) {
+      const int t = item / a.k_splits;
+      const int zsplit = item - t * a.k_splits;
       const int buf = (a.acc_bufs == 2) ? (it & 1) : 0;
       const uint32_t acc_phase = (a.acc_bufs == 2) ? ((it >> 1) & 1) : (it & 1);
       int mt, nt;
@@ -401,6 +413,49 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       const uint32_t t_tile = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * acc_cols);
       __nv_bfloat16* yrow_tile = a.y + (long long)row * a.ldy + col0;
       const bool wide = a.wide_store != 0;  // every 16-column group of every row starts on a 32-byte boundary
+
+      if (kCtas == 1 && a.k_splits > 1) {
+        // ---- split-K: park this CTA's fp32 partial sums; swiglu_splitk_reduce_kernel finishes the tile
+        const int slot = warp - 4;
+        const int ws_ld = 2 * a.block_n;
+        const int r_loc = q * 32 + lane;
+        float* part = a.ws + ((size_t)(t * a.k_splits + zsplit) * a.M + r_loc) * ws_ld;
+        auto chunk_w = [&](int c) { return (c + 32 <= a.block_n) ? 32 : ((c + 16 == a.block_n) ? 16 : 0); };
+        uint32_t g[32], u[32];
+        bool released = false;
+        for (int c = 32 * (slot >> 2), w = chunk_w(c); w; c += 64, w = chunk_w(c)) {
+          if (w == 32) {
+            tmem_ld_x32(t_tile + c, g);
+            tmem_ld_x32(t_tile + a.block_n + c, u);
+          } else {
+            tmem_ld_x16_into32(t_tile + c, g);
+            tmem_ld_x16_into32(t_tile + a.block_n + c, u);
+          }
+          tmem_ld_wait();
+          if (!chunk_w(c + 64)) {  // last read of the accumulator: hand it back before the stores
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+            released = true;
+          }
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (4 * j < w) {
+                *reinterpret_cast<uint4*>(part + c + 4 * j) = make_uint4(g[4 * j], g[4 * j + 1], g[4 * j + 2], g[4 * j + 3]);
+                *reinterpret_cast<uint4*>(part + a.block_n + c + 4 * j) =
+                    make_uint4(u[4 * j], u[4 * j + 1], u[4 * j + 2], u[4 * j + 3]);
+              }
+            }
+          }
+        }
+        if (!released) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+        }
+        continue;
+      }
 
       // A tile is drained in one segment (gate columns [0,bn), up columns [bn,2bn)) or, in split mode, in two
       // (low half then high half, each [gate|up] of bn/2 columns) that are released separately.
@@ -487,6 +542,40 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   if (warp == 2) {
     tc_fence_after_sync();
     tmem_dealloc<kCtas>(tmem_base, kTmemCols);
+  }
+}
+
+// Second step of a split-K launch: Y[row, tile columns] = silu(sum_z g_z) * (sum_z u_z), partial sums added in
+// split order (bit-identical from run to run).  One thread per 8 output columns, coalesced along a row.
+__global__ void __launch_bounds__(256)
+swiglu_splitk_reduce_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ y, int M, int N, long long ldy,
+                            int block_n, int num_n_tiles, int k_splits) {
+  const int groups = block_n / 8;
+  const long long total = (long long)num_n_tiles * M * groups;
+  const uint64_t policy = l2_policy_evict_first();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int cg = (int)(i % groups);
+    const int row = (int)((i / groups) % M);
+    const int t = (int)(i / ((long long)groups * M));
+    const int col = t * block_n + cg * 8;
+    if (col >= N) continue;  // N is a multiple of 8: a group is inside or outside as a whole
+    const float* p = ws + (((size_t)t * k_splits) * M + row) * (2 * block_n) + cg * 8;
+    float g[8] = {0, 0, 0, 0, 0, 0, 0, 0}, u[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int z = 0; z < k_splits; ++z, p += (size_t)M * 2 * block_n) {
+      const float4 g0 = __ldcg(reinterpret_cast<const float4*>(p)), g1 = __ldcg(reinterpret_cast<const float4*>(p + 4));
+      const float4 u0 = __ldcg(reinterpret_cast<const float4*>(p + block_n));
+      const float4 u1 = __ldcg(reinterpret_cast<const float4*>(p + block_n + 4));
+      g[0] += g0.x; g[1] += g0.y; g[2] += g0.z; g[3] += g0.w; g[4] += g1.x; g[5] += g1.y; g[6] += g1.z; g[7] += g1.w;
+      u[0] += u0.x; u[1] += u0.y; u[2] += u0.z; u[3] += u0.w; u[4] += u1.x; u[5] += u1.y; u[6] += u1.z; u[7] += u1.w;
+    }
+    uint32_t gb[8], ub[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      gb[j] = __float_as_uint(g[j]);
+      ub[j] = __float_as_uint(u[j]);
+    }
+    st_global_v4_hint(y + (long long)row * ldy + col, swiglu_pack8(gb, ub), policy);
   }
 }
 
@@ -584,13 +673,32 @@ struct Plan {
   int num_m_tiles, num_n_tiles, num_k_blocks, group_m;
   int ctas;  // CTAs per tile: 1, or 2 for the CTA-pair schedule
   int split; // CTA pairs with two MMAs per step and block_n % 32 == 0: two separately released half tiles
+  int k_splits, kb_per_split;          // split-K of the STREAM schedule (1 = off)
+  int64_t ws_bytes;                    // fp32 partial sums of a split-K plan (0 = none)
   uint32_t stage_bytes, b_second;
 };
 
 static inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
+constexpr int64_t kWorkspaceCap = 64LL << 20;  // never plan for more scratch than this
+
+// Scratch bytes of a split-K plan: per tile k_splits x M x 2*block_n fp32 partial sums.
+static inline int64_t splitk_bytes(int64_t tiles, int64_t z, int64_t M, int64_t bn) { return tiles * z * M * 2 * bn * 4; }
+
+// Estimated time (ns) of the STREAM schedule: every CTA runs kb_per_split K-steps; a K-step costs at least
+// ~530 ns of MMA issue (measured) and otherwise its share of HBM bandwidth; split-K adds a reduction.
+static inline double stream_cost_ns(int64_t N, int64_t num_kb, int bn, int z, int ctas) {
+  const int64_t slabs = (N + bn - 1) / bn;
+  const int64_t items = slabs * z;
+  const int64_t waves = (items + ctas - 1) / ctas;
+  const int64_t active = items < ctas ? items : ctas;
+  const int64_t kpz = (num_kb + z - 1) / z;
+  const double step_ns = 256.0 * bn * (double)active / 6200.0;  // 2*bn rows x 128 B per K-step over ~6.2 TB/s
+  return (double)waves * ((double)kpz * (step_ns > 533.0 ? step_ns : 533.0) + 1500.0 + 6.0 * bn + (z > 1 ? 2500.0 : 0.0));
+}
+
 static int make_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, int stages, int group_m, int max_ctas,
-                     int sm_count, Plan* p) {
+                     int sm_count, int64_t ws_limit, Plan* p) {
   if (M < 0 || N <= 0 || K <= 0 || M > 0x7fffff00LL || N > 0x3fffff00LL || K > 0x7fffff00LL)
     return fail(MAGI_SWIGLU_ERR_SHAPE, "shape out of range: M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
   if (N % 8 != 0 || K % 8 != 0)
@@ -611,6 +719,7 @@ static int make_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
   if (variant == MAGI_SWIGLU_VARIANT_STREAM && M > kBM)
     return fail(MAGI_SWIGLU_ERR_VARIANT, "STREAM variant needs M <= %d (got %lld)", kBM, (long long)M);
   const int pair = (variant == MAGI_SWIGLU_VARIANT_MMA2) ? 2 : 1;
+  int stream_auto_width = 0;
   p->ctas = pair;
   int ctas = (max_ctas > 0 && max_ctas < sm_count) ? max_ctas : sm_count;
   if (pair == 2) ctas = ctas / 2 * 2;
@@ -643,6 +752,32 @@ static int make_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
       int64_t per = (N + ctas - 1) / ctas;
       block_n = round_up((int)(per < 16 ? 16 : per), 16);
       if (block_n > 256) block_n = 256;
+      stream_auto_width = 1;
+    }
+  }
+  int k_splits = 1;
+  if (variant == MAGI_SWIGLU_VARIANT_STREAM && M > 0) {
+    // Narrow weights (a column shard of a decode GEMM) leave each SM too little W per K-step to hide the MMA
+    // issue time; with scratch available, several CTAs share a slab and split K between them.
+    const int64_t num_kb = (K + kBK - 1) / kBK;
+    if (ws_limit > kWorkspaceCap) ws_limit = kWorkspaceCap;
+    int forced = 0;
+    if (const char* env = getenv("MAGI_SWIGLU_K_SPLITS")) forced = atoi(env);  // tuning aid
+    double best = stream_cost_ns(N, num_kb, block_n, 1, ctas);
+    const int bn_lo = stream_auto_width ? 32 : block_n, bn_hi = stream_auto_width ? 256 : block_n;
+    for (int bn = bn_lo; bn <= bn_hi; bn += 16) {
+      for (int z = 1; z <= 8; ++z) {
+        if (forced > 0 && z != forced) continue;
+        if (z > 1 && ((num_kb + z - 1) / z < 4 || (int64_t)((num_kb + z - 1) / z) * (z - 1) >= num_kb)) continue;
+        const int64_t slabs = (N + bn - 1) / bn;
+        if (z > 1 && splitk_bytes(slabs, z, M, bn) > ws_limit) continue;
+        const double c = stream_cost_ns(N, num_kb, bn, z, ctas);
+        if (c < best * 0.97 || (forced > 0 && z == forced && k_splits != forced)) {  // 3 %: prefer the simpler plan
+          best = c;
+          block_n = bn;
+          k_splits = z;
+        }
+      }
     }
   }
   if (block_n < 16 || block_n > 256 || block_n % 16 != 0)
@@ -674,7 +809,11 @@ static int make_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
     group_m = (int)(g < 4 ? 4 : (g > 64 ? 64 : g));
   }
   p->group_m = group_m;
-  p->grid = (p->tiles * pair < ctas) ? p->tiles * pair : ctas;
+  p->k_splits = k_splits;
+  p->kb_per_split = (p->num_k_blocks + k_splits - 1) / k_splits;
+  if (k_splits > 1) p->ws_bytes = splitk_bytes(p->tiles, k_splits, M, block_n);
+  const int64_t items = (int64_t)p->tiles * pair * k_splits;
+  p->grid = (items < ctas) ? (int)items : ctas;
   return 0;
 }
 
@@ -732,7 +871,7 @@ struct DeviceGuard {
 
 static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int64_t ldx,
                         int64_t ldw, int64_t ldy, int device, void* stream_v, int variant, int block_n, int stages,
-                        int group_m, int max_ctas) {
+                        int group_m, int max_ctas, void* workspace, int64_t workspace_bytes) {
   g_err[0] = 0;
   if (M == 0 && N > 0 && K > 0) return 0;
   if (!x || !w || !y) return fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
@@ -748,7 +887,10 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
     return fail(MAGI_SWIGLU_ERR_DEVICE, "device %d is sm_%d%d; this library runs on sm_100 (B200) only", device,
                 di->cc_major, di->cc_minor);
   Plan p;
-  int rc = make_plan(M, N, K, variant, block_n, stages, group_m, max_ctas, di->sm_count, &p);
+  if (workspace && (((uintptr_t)workspace & 255u) || workspace_bytes < 0))
+    return fail(MAGI_SWIGLU_ERR_ALIGN, "workspace must be 256-byte aligned");
+  int rc = make_plan(M, N, K, variant, block_n, stages, group_m, max_ctas, di->sm_count,
+                     workspace ? workspace_bytes : 0, &p);
   if (rc) return rc;
 
   DeviceGuard guard;
@@ -822,6 +964,9 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   a.split = p.split;
   a.acc_bufs = p.acc_bufs;
   a.wide_store = (((uintptr_t)y & 31u) == 0 && ldy % 16 == 0) ? 1 : 0;
+  a.k_splits = p.k_splits;
+  a.kb_per_split = p.kb_per_split;
+  a.ws = p.k_splits > 1 ? static_cast<float*>(workspace) : nullptr;
   // default L2 priorities: a band of X rows is re-read by every column tile -> keep; W tiles and Y are streamed
   a.x_hint = 2;
   a.w_hint = 1;
@@ -837,7 +982,16 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   if (p.ctas == 1) {
     swiglu_tc_kernel<1><<<p.grid, kThreads, p.smem_bytes, stream>>>(tm_x, tm_w, a);
     e = cudaGetLastError();
-    return e == cudaSuccess ? 0 : fail_cuda(e, "launch of swiglu_tc_kernel<1>");
+    if (e != cudaSuccess) return fail_cuda(e, "launch of swiglu_tc_kernel<1>");
+    if (p.k_splits > 1) {
+      const long long work = (long long)p.num_n_tiles * M * (p.block_n / 8);
+      const int blocks = (int)((work + 255) / 256 < 4LL * di->sm_count ? (work + 255) / 256 : 4LL * di->sm_count);
+      swiglu_splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(a.ws, a.y, a.M, a.N, a.ldy, p.block_n, p.num_n_tiles,
+                                                             p.k_splits);
+      e = cudaGetLastError();
+      if (e != cudaSuccess) return fail_cuda(e, "launch of swiglu_splitk_reduce_kernel");
+    }
+    return 0;
   }
   if (pair_clusters <= 0) return fail(MAGI_SWIGLU_ERR_VARIANT, "this device cannot co-schedule 2-CTA clusters of the pair kernel");
   int grid = p.grid;
@@ -872,14 +1026,37 @@ int magi_swiglu_supported(int device) {
 
 int magi_swiglu_forward_bf16(const void* x, const void* w_gate_up, void* y, int64_t M, int64_t N, int64_t K,
                              int64_t ldx, int64_t ldw, int64_t ldy, int device, void* cuda_stream, int variant) {
-  return magi::forward_impl(x, w_gate_up, y, M, N, K, ldx, ldw, ldy, device, cuda_stream, variant, 0, 0, 0, 0);
+  return magi::forward_impl(x, w_gate_up, y, M, N, K, ldx, ldw, ldy, device, cuda_stream, variant, 0, 0, 0, 0,
+                            nullptr, 0);
 }
 
 int magi_swiglu_forward_bf16_ex(const void* x, const void* w_gate_up, void* y, int64_t M, int64_t N, int64_t K,
                                 int64_t ldx, int64_t ldw, int64_t ldy, int device, void* cuda_stream, int variant,
                                 int block_n, int stages, int group_m, int max_ctas) {
   return magi::forward_impl(x, w_gate_up, y, M, N, K, ldx, ldw, ldy, device, cuda_stream, variant, block_n, stages,
-                            group_m, max_ctas);
+                            group_m, max_ctas, nullptr, 0);
+}
+
+int magi_swiglu_forward_bf16_ws(const void* x, const void* w_gate_up, void* y, int64_t M, int64_t N, int64_t K,
+                                int64_t ldx, int64_t ldw, int64_t ldy, int device, void* cuda_stream, int variant,
+                                int block_n, int stages, int group_m, int max_ctas, void* workspace,
+                                int64_t workspace_bytes) {
+  return magi::forward_impl(x, w_gate_up, y, M, N, K, ldx, ldw, ldy, device, cuda_stream, variant, block_n, stages,
+                            group_m, max_ctas, workspace, workspace_bytes);
+}
+
+int64_t magi_swiglu_workspace_bytes(int64_t M, int64_t N, int64_t K, int variant, int block_n, int stages, int group_m,
+                                    int max_ctas, int device, int sm_count) {
+  magi::g_err[0] = 0;
+  if (sm_count <= 0) {
+    const magi::DeviceInfo* di = magi::device_info(device);
+    if (!di) return magi::fail(MAGI_SWIGLU_ERR_DEVICE, "device %d is not available", device);
+    sm_count = di->sm_count;
+  }
+  if (M == 0) return 0;
+  magi::Plan p;
+  int rc = magi::make_plan(M, N, K, variant, block_n, stages, group_m, max_ctas, sm_count, magi::kWorkspaceCap, &p);
+  return rc ? (int64_t)rc : p.ws_bytes;
 }
 
 int magi_swiglu_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, int stages, int group_m, int max_ctas,
@@ -892,7 +1069,7 @@ int magi_swiglu_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
     sm_count = di->sm_count;
   }
   magi::Plan p;
-  int rc = magi::make_plan(M, N, K, variant, block_n, stages, group_m, max_ctas, sm_count, &p);
+  int rc = magi::make_plan(M, N, K, variant, block_n, stages, group_m, max_ctas, sm_count, magi::kWorkspaceCap, &p);
   if (rc) return rc;
   out[0] = p.variant;
   out[1] = p.block_n;
@@ -905,7 +1082,7 @@ int magi_swiglu_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
   out[8] = p.ctas;
   out[9] = p.group_m;
   out[10] = p.split;
-  out[11] = 0;
+  out[11] = p.k_splits;
   return 0;
 }
 

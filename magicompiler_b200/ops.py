@@ -63,6 +63,20 @@ def _rows_view(t: torch.Tensor, cols: int) -> torch.Tensor:
     return t2 if ok else t2.contiguous()
 
 
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def _workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
+    """Scratch for split-K schedules, one per (device, stream) so launches that may overlap never share one.
+    It comes from torch's caching allocator (capture-aware); the library itself allocates nothing."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
 def gemm_swiglu_out(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor | None = None, *,
                     variant: str | int = "auto", block_n: int = 0, stages: int = 0, group_m: int = 0,
                     max_ctas: int = 0) -> torch.Tensor:
@@ -90,8 +104,15 @@ def gemm_swiglu_out(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor 
     dev = x.device.index if x.device.index is not None else torch.cuda.current_device()
     stream = torch.cuda.current_stream(x.device).cuda_stream
     ldx = x2.stride(0) if M > 1 else K
-    rc = lib.magi_swiglu_forward_bf16_ex(x2.data_ptr(), w2.data_ptr(), y.data_ptr(), M, N, K, ldx, w2.stride(0),
-                                         y.stride(0), dev, stream, v, block_n, stages, group_m, max_ctas)
+    ws_ptr, ws_len = None, 0
+    if M <= 128:  # only the small-M schedules ever split K
+        need = lib.magi_swiglu_workspace_bytes(M, N, K, v, block_n, stages, group_m, max_ctas, dev, 0)
+        if need > 0:
+            ws = _workspace(x.device, stream, need)
+            ws_ptr, ws_len = ws.data_ptr(), ws.numel()
+    rc = lib.magi_swiglu_forward_bf16_ws(x2.data_ptr(), w2.data_ptr(), y.data_ptr(), M, N, K, ldx, w2.stride(0),
+                                         y.stride(0), dev, stream, v, block_n, stages, group_m, max_ctas,
+                                         ws_ptr, ws_len)
     if rc != 0:
         msg = f"magi_swiglu_forward_bf16 failed ({rc}): {_loader.last_error()}"
         raise (ValueError(msg) if rc < 0 else RuntimeError(msg))

@@ -26,7 +26,8 @@ def _declared_functions():
 def test_every_declared_symbol_is_exported(lib):
     names = _declared_functions()
     assert {"magi_swiglu_version", "magi_swiglu_supported", "magi_swiglu_forward_bf16", "magi_swiglu_forward_bf16_ex",
-            "magi_swiglu_plan", "magi_swiglu_device_status", "magi_swiglu_kernel_clock", "magi_swiglu_last_error"} <= set(names)
+            "magi_swiglu_plan", "magi_swiglu_device_status", "magi_swiglu_kernel_clock", "magi_swiglu_last_error",
+            "magi_swiglu_forward_bf16_ws", "magi_swiglu_workspace_bytes"} <= set(names)
     for n in names:
         assert hasattr(lib, n), n
 
@@ -34,7 +35,7 @@ def test_every_declared_symbol_is_exported(lib):
 def test_every_declaration_cites_what_it_replaces():
     text = HEADER.read_text()
     for n in _declared_functions():
-        decl = re.search(r"^(?:int|const char\*)\s+" + n + r"\(", text, re.M).start()
+        decl = re.search(r"^(?:int|int64_t|const char\*)\s+" + n + r"\(", text, re.M).start()
         comment = text[:decl].rsplit("/*", 1)[1]
         assert "Replaces:" in comment or "no counterpart in the reference" in comment, n
 
@@ -131,3 +132,20 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.delenv("MAGI_SWIGLU_AUTOBUILD", raising=False)
     with pytest.raises(_loader.MagiSwigluLibraryError):
         _loader.load_library()
+
+
+def test_split_k_plans_and_workspace_sizes():
+    # the full decode weight keeps one slab per SM and needs no scratch ...
+    assert _loader.plan(64, 28672, 8192, sm_count=148)["k_splits"] == 1
+    assert _loader.workspace_bytes(64, 28672, 8192, sm_count=148) == 0
+    # ... its 8-GPU column shard is too narrow for that: CTAs share slabs and split K
+    p = _loader.plan(64, 3584, 8192, sm_count=148)
+    assert p["k_splits"] >= 2 and p["tiles"] * p["k_splits"] <= 148 and p["grid"] == p["tiles"] * p["k_splits"]
+    need = _loader.workspace_bytes(64, 3584, 8192, sm_count=148)
+    assert need == p["tiles"] * p["k_splits"] * 64 * 2 * p["block_n"] * 4  # fp32 partial sums, nothing else
+    assert need <= 64 << 20
+    # large-M schedules never ask for scratch
+    assert _loader.workspace_bytes(8192, 14336, 4096, sm_count=148) == 0
+    assert _loader.workspace_bytes(0, 64, 64, sm_count=148) == 0
+    with pytest.raises(ValueError):
+        _loader.workspace_bytes(16, 100, 64, sm_count=148)

@@ -213,3 +213,69 @@ def test_video_dit_ffn_sampled():
     shard = mb.shard_gate_up(wd, 7, 8)  # 1728 columns: 13.5 tiles of 128
     for variant in ("mma", "mma2"):
         assert torch.equal(mb.gemm_swiglu_out(xd, shard, variant=variant), y[:, 7 * 1728:]), variant
+
+
+# ---------------------------------------------------------------- split-K (narrow weights, M <= 128)
+@pytest.mark.parametrize("M", [16, 64, 128])
+@pytest.mark.parametrize("n_shard", [3584, 7168])
+def test_decode_column_shards_split_k(M, n_shard):
+    """A 1/8 or 1/4 column shard of the decode weight: several CTAs share a slab and split K through scratch memory.
+    Checked against the fp32 gold; repeated launches reuse the scratch and agree bit for bit."""
+    plan = mb.plan(M, n_shard, 8192)
+    assert plan["k_splits"] > 1 and mb.workspace_bytes(M, n_shard, 8192) > 0
+    x, w = make_inputs(M, 8192, n_shard, seed=n_shard + M)
+    xd, wd = x.cuda(), w.cuda()
+    y1 = mb.gemm_swiglu(xd, wd)
+    assert_parity(y1, gold_fp32_gpu(xd, wd), f"shard M={M} N={n_shard}")
+    for _ in range(3):
+        assert torch.equal(mb.gemm_swiglu(xd, wd), y1)
+    # the same problem without scratch (plain C entry point) runs unsplit and agrees within rounding of the sums
+    lib = _loader.load_library()
+    y0 = torch.empty_like(y1)
+    rc = lib.magi_swiglu_forward_bf16(xd.data_ptr(), wd.data_ptr(), y0.data_ptr(), M, n_shard, 8192, 8192, 8192, n_shard,
+                                      0, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), 0)
+    assert rc == 0, _loader.last_error()
+    assert_parity(y0, gold_fp32_gpu(xd, wd), "unsplit")
+    assert error_metrics(y1, y0.float())["max_norm"] < 8e-3  # at most one bf16 step apart
+
+
+@pytest.mark.parametrize("splits", [2, 3, 5, 8])
+@pytest.mark.parametrize("shape", [(1, 264, 2048), (37, 72, 4096), (128, 528, 2304), (100, 2816, 1024)])
+def test_forced_k_splits_ragged(monkeypatch, splits, shape):
+    M, N, K = shape
+    monkeypatch.setenv("MAGI_SWIGLU_K_SPLITS", str(splits))
+    x, w = make_inputs(M, K, N, seed=splits + M)
+    y = mb.gemm_swiglu_out(x.cuda(), w.cuda(), variant="stream")
+    y2 = mb.gemm_swiglu_out(x.cuda(), w.cuda(), variant="stream")
+    assert_parity(y, swiglu_gold(x, w, want_eager=False)["gold"], f"{shape} z={splits}")
+    assert torch.equal(y, y2)
+
+
+def test_workspace_entry_point_contract():
+    """Through the C ABI with a caller-owned workspace: too small a workspace falls back to an unsplit schedule,
+    a misaligned one is rejected on the host, and the workspace needs no initialisation (it starts as NaNs here)."""
+    lib = _loader.load_library()
+    M, N, K = 64, 3584, 4096
+    x, w = make_inputs(M, K, N, seed=3)
+    xd, wd = x.cuda(), w.cuda()
+    need = mb.workspace_bytes(M, N, K)
+    assert need > 0
+    ws = torch.full(((need + 256) // 2,), float("nan"), dtype=torch.bfloat16, device="cuda").view(torch.uint8)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    gold = gold_fp32_gpu(xd, wd)
+
+    def call(ws_ptr, ws_len):
+        y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        rc = lib.magi_swiglu_forward_bf16_ws(xd.data_ptr(), wd.data_ptr(), y.data_ptr(), M, N, K, K, K, N, 0, stream, 0,
+                                             0, 0, 0, 0, ws_ptr, ws_len)
+        return rc, y
+
+    rc, y = call(ws.data_ptr(), need)
+    assert rc == 0, _loader.last_error()
+    assert_parity(y, gold, "full workspace")
+    rc, y_small = call(ws.data_ptr(), 4096)  # cannot hold the partial sums: unsplit schedule, still correct
+    assert rc == 0 and assert_parity(y_small, gold, "small workspace")
+    rc, _ = call(ws.data_ptr() + 16, need)
+    assert rc == -3 and "aligned" in _loader.last_error()
+    rc, y_null = call(None, 0)
+    assert rc == 0 and torch.equal(y_null, y_small)

@@ -101,6 +101,25 @@ int magi_swiglu_forward_bf16_ws(const void* x, const void* w_gate_up, void* y,
                                 int block_n, int stages, int group_m, int max_ctas,
                                 void* workspace, int64_t workspace_bytes);
 
+/* magi_swiglu_forward_bf16_ws without a workspace argument: the split-K partial sums go into an 8 MiB array that
+ * is built into the library (a file-scope __device__ array; every GPU that loads the library holds it until the
+ * process exits).  This entry point has no counterpart in the reference.
+ * It is for callers that have no way to get device memory at the point of the call: a ctypes/C caller with no
+ * allocator of its own, a serving process whose memory pool already owns the whole GPU, code running where a
+ * cudaMalloc would be refused or would stall the device.  It calls no cudaMalloc/cudaFree and no allocating library
+ * routine; the caller still passes x, w_gate_up and y.
+ *  - The FIRST call on each device looks the array's device address up (cudaGetSymbolAddress); make that first call
+ *    outside any stream capture.
+ *  - A problem whose preferred schedule wants more than 8 MiB of scratch (magi_swiglu_workspace_bytes tells) is
+ *    rejected with MAGI_SWIGLU_ERR_SHAPE and nothing is launched.  Problems that need no scratch run as usual.
+ *  - All calls on a device share the one array.  It keeps the previous call's contents, which is harmless: every
+ *    partial sum is written before it is read, nothing has to start at zero.  Calls that may overlap on the GPU
+ *    (different streams) race on it: serialise them, or use magi_swiglu_forward_bf16_ws with separate workspaces. */
+int magi_swiglu_forward_bf16_static(const void* x, const void* w_gate_up, void* y,
+                                    int64_t M, int64_t N, int64_t K,
+                                    int64_t ldx, int64_t ldw, int64_t ldy,
+                                    int device, void* cuda_stream);
+
 /* Scratch bytes the preferred schedule of magi_swiglu_forward_bf16_ws wants for this problem (0 = none needed;
  * negative = argument error).  Needs no GPU when sm_count > 0.
  * Replaces: nothing in the reference. */

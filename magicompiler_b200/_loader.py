@@ -79,6 +79,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.magi_swiglu_forward_bf16_ws.restype = i32
     lib.magi_swiglu_forward_bf16_ws.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, vp, i32,
                                                 i32, i32, i32, i32, vp, i64]
+    lib.magi_swiglu_forward_bf16_static.restype = i32
+    lib.magi_swiglu_forward_bf16_static.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, vp]
     lib.magi_swiglu_workspace_bytes.restype = i64
     lib.magi_swiglu_workspace_bytes.argtypes = [i64, i64, i64, i32, i32, i32, i32, i32, i32, i32]
     lib.magi_swiglu_plan.restype = i32

@@ -1012,6 +1012,29 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   return e == cudaSuccess ? 0 : fail_cuda(e, "launch of swiglu_tc_kernel<2>");
 }
 
+// ------------------------------------------------------------------ built-in scratch (no allocation anywhere)
+// Scratch for magi_swiglu_forward_bf16_static.  It is part of the loaded module: every GPU that loads the
+// library carries these bytes until the process exits.  In host code the name below is only a handle for the
+// symbol, not a device pointer; the device address is looked up once per device with cudaGetSymbolAddress.
+constexpr int64_t kStaticScratchBytes = 8LL << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+static void* g_static_scratch_addr[kMaxDevices];  // device address of g_static_scratch, per device (nullptr = not set up)
+
+// Looks the scratch array's device address up on first use for `device` (which must be the current device).
+static int static_scratch_address(int device, void** out) {
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  if (!g_static_scratch_addr[device]) {
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaGetSymbolAddress(g_static_scratch)");
+    if (!ptr) return fail(MAGI_SWIGLU_ERR_DRIVER, "cudaGetSymbolAddress returned a null address for the built-in scratch");
+    g_static_scratch_addr[device] = ptr;
+  }
+  *out = g_static_scratch_addr[device];
+  return 0;
+}
+
 }  // namespace magi
 
 // ================================================================== C ABI
@@ -1043,6 +1066,34 @@ int magi_swiglu_forward_bf16_ws(const void* x, const void* w_gate_up, void* y, i
                                 int64_t workspace_bytes) {
   return magi::forward_impl(x, w_gate_up, y, M, N, K, ldx, ldw, ldy, device, cuda_stream, variant, block_n, stages,
                             group_m, max_ctas, workspace, workspace_bytes);
+}
+
+int magi_swiglu_forward_bf16_static(const void* x, const void* w_gate_up, void* y, int64_t M, int64_t N, int64_t K,
+                                    int64_t ldx, int64_t ldw, int64_t ldy, int device, void* cuda_stream) {
+  magi::g_err[0] = 0;
+  if (M == 0 && N > 0 && K > 0) return 0;
+  const magi::DeviceInfo* di = magi::device_info(device);
+  if (!di) return magi::fail(MAGI_SWIGLU_ERR_DEVICE, "device %d is not available", device);
+  // the schedule the scratch-taking entry point prefers for this problem, and the scratch it wants
+  magi::Plan p;
+  int rc = magi::make_plan(M, N, K, MAGI_SWIGLU_VARIANT_AUTO, 0, 0, 0, 0, di->sm_count, magi::kWorkspaceCap, &p);
+  if (rc) return rc;
+  if (p.ws_bytes > magi::kStaticScratchBytes)
+    return magi::fail(MAGI_SWIGLU_ERR_SHAPE,
+                      "M=%lld N=%lld K=%lld needs %lld bytes of scratch; the built-in scratch of "
+                      "magi_swiglu_forward_bf16_static holds %lld (use magi_swiglu_forward_bf16_ws with your own)",
+                      (long long)M, (long long)N, (long long)K, (long long)p.ws_bytes,
+                      (long long)magi::kStaticScratchBytes);
+  void* scratch = nullptr;
+  {
+    magi::DeviceGuard guard;  // the symbol's address is per device: look it up with `device` current
+    cudaError_t e = guard.set(device);
+    if (e != cudaSuccess) return magi::fail_cuda(e, "cudaSetDevice");
+    rc = magi::static_scratch_address(device, &scratch);
+    if (rc) return rc;
+  }
+  return magi::forward_impl(x, w_gate_up, y, M, N, K, ldx, ldw, ldy, device, cuda_stream, MAGI_SWIGLU_VARIANT_AUTO, 0, 0,
+                            0, 0, scratch, magi::kStaticScratchBytes);
 }
 
 int64_t magi_swiglu_workspace_bytes(int64_t M, int64_t N, int64_t K, int variant, int block_n, int stages, int group_m,

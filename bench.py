@@ -48,8 +48,9 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (bytes; key = workload@gpus).
 NCU_TRAFFIC = {
-    "llama3_8b_ffn@1": 833.9e6,  # profiles/swiglu_tc_kernel_pair_llama3_8b_ffn.md
-    "decode_m64@1": 945.1e6,     # profiles/swiglu_tc_kernel_stream_decode_m64.md
+    "llama3_8b_ffn@1": 1218.2e6,  # profiles/swiglu_tc_kernel_pair_llama3_8b_ffn.md
+    "video_dit_ffn@1": 13406.3e6,
+    "decode_m64@1": 946.7e6,     # profiles/swiglu_tc_kernel_stream_decode_m64.md
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 L2_FLUSH_BYTES = 256 << 20
@@ -432,7 +433,8 @@ def main():
                    "l2": "flushed before every timed step (256 MiB written, then 256 MiB read)" if not args.no_flush else "not flushed",
                    "plan": plan, "wall_s_timed_region": wall},
         "roofline": roof,
-        "gpu_launches": args.steps,
+        # one tile kernel per step, plus the ordered-reduce kernel when the plan splits K
+        "gpu_launches": args.steps * (2 if plan.get("k_splits", 1) > 1 else 1),
         "clocks": clocks,
     }
     if clocks is not None:

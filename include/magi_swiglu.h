@@ -120,6 +120,17 @@ int magi_swiglu_forward_bf16_static(const void* x, const void* w_gate_up, void* 
                                     int64_t ldx, int64_t ldw, int64_t ldy,
                                     int device, void* cuda_stream);
 
+/* Backward of the activation.  h is [M, 2N] = [G | U], the pre-activations X·Wg^T and X·Wu^T (bf16, row stride ldh),
+ * dy is [M, N]; writes dh = [dG | dU] ([M, 2N], row stride lddh) with dG = dY*U*s*(1 + G*(1-s)), dU = dY*G*s,
+ * s = sigmoid(G); fp32 arithmetic, one rounding.  The GEMMs around it (recomputing h, dX = dH·W, dW = dH^T·X) are
+ * plain library GEMMs on the host side.  N % 8 == 0, strides % 8 == 0, 16-byte aligned pointers.
+ * Replaces: the autograd of F.silu(gate_proj(x)) * up_proj(x) (tests/model_definition.py:337-339) that the
+ * reference gets from PyTorch; wired up through the setup_context_fn/backward_fn arguments of
+ * magi_compiler/_magi_register_custom_op.py:198-200. */
+int magi_swiglu_backward_act_bf16(const void* h, const void* dy, void* dh,
+                                  int64_t M, int64_t N, int64_t ldh, int64_t lddy, int64_t lddh,
+                                  int device, void* cuda_stream);
+
 /* Scratch bytes the preferred schedule of magi_swiglu_forward_bf16_ws wants for this problem (0 = none needed;
  * negative = argument error).  Needs no GPU when sm_count > 0.
  * Replaces: nothing in the reference. */

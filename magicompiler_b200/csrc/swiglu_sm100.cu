@@ -579,6 +579,41 @@ swiglu_splitk_reduce_kernel(const float* __restrict__ ws, __nv_bfloat16* __restr
   }
 }
 
+// Backward of the activation: from the recomputed pre-activations H = [G | U] (bf16, [M, 2N]) and dY ([M, N]):
+//   dG = dY * U * s * (1 + G * (1 - s)),   dU = dY * G * s,   s = sigmoid(G)
+// written as dH = [dG | dU] (bf16).  Element-wise, HBM-bound (10 bytes per output element); 8 columns per thread
+// with 16-byte accesses, fp32 arithmetic, one rounding per result.
+__global__ void __launch_bounds__(256)
+swiglu_bwd_act_kernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ dy,
+                      __nv_bfloat16* __restrict__ dh, int M, int N, long long ldh, long long lddy, long long lddh) {
+  const int groups = N / 8;
+  const long long total = (long long)M * groups;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / groups;
+    const int col = (int)(i - row * groups) * 8;
+    const uint4 gv = *reinterpret_cast<const uint4*>(h + row * ldh + col);
+    const uint4 uv = *reinterpret_cast<const uint4*>(h + row * ldh + N + col);
+    const uint4 dv = *reinterpret_cast<const uint4*>(dy + row * lddy + col);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+    const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&dv);
+    uint4 og, ou;
+    __nv_bfloat162* og2 = reinterpret_cast<__nv_bfloat162*>(&og);
+    __nv_bfloat162* ou2 = reinterpret_cast<__nv_bfloat162*>(&ou);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]), d = __bfloat1622float2(d2[j]);
+      const float sx = __fdividef(1.0f, 1.0f + __expf(-g.x)), sy = __fdividef(1.0f, 1.0f + __expf(-g.y));
+      og2[j] = __floats2bfloat162_rn(d.x * u.x * sx * (1.0f + g.x * (1.0f - sx)),
+                                     d.y * u.y * sy * (1.0f + g.y * (1.0f - sy)));
+      ou2[j] = __floats2bfloat162_rn(d.x * g.x * sx, d.y * g.y * sy);
+    }
+    *reinterpret_cast<uint4*>(dh + row * lddh + col) = og;
+    *reinterpret_cast<uint4*>(dh + row * lddh + N + col) = ou;
+  }
+}
+
 // Plain CUDA-core kernel: one thread per output, 16x16 outputs per block, K staged through shared
 // memory in slices of 32.  Same arithmetic contract (fp32 accumulate, one rounding).  Validation only.
 __global__ void __launch_bounds__(256)
@@ -1094,6 +1129,34 @@ int magi_swiglu_forward_bf16_static(const void* x, const void* w_gate_up, void* 
   }
   return magi::forward_impl(x, w_gate_up, y, M, N, K, ldx, ldw, ldy, device, cuda_stream, MAGI_SWIGLU_VARIANT_AUTO, 0, 0,
                             0, 0, scratch, magi::kStaticScratchBytes);
+}
+
+int magi_swiglu_backward_act_bf16(const void* h, const void* dy, void* dh, int64_t M, int64_t N, int64_t ldh,
+                                  int64_t lddy, int64_t lddh, int device, void* cuda_stream) {
+  magi::g_err[0] = 0;
+  if (M == 0 && N > 0) return 0;
+  if (!h || !dy || !dh) return magi::fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
+  if (M < 0 || N <= 0 || N % 8 != 0 || M > 0x7fffff00LL || N > 0x3fffff00LL)
+    return magi::fail(MAGI_SWIGLU_ERR_SHAPE, "bad shape M=%lld N=%lld (N must be a positive multiple of 8)", (long long)M,
+                      (long long)N);
+  if (ldh < 2 * N || lddh < 2 * N || lddy < N) return magi::fail(MAGI_SWIGLU_ERR_SHAPE, "row strides too small");
+  if (ldh % 8 || lddh % 8 || lddy % 8 || (((uintptr_t)h | (uintptr_t)dy | (uintptr_t)dh) & 15u))
+    return magi::fail(MAGI_SWIGLU_ERR_ALIGN, "pointers must be 16-byte aligned and row strides multiples of 8 elements");
+  const magi::DeviceInfo* di = magi::device_info(device);
+  if (!di) return magi::fail(MAGI_SWIGLU_ERR_DEVICE, "device %d is not available", device);
+  if (di->cc_major != 10 || di->cc_minor != 0)
+    return magi::fail(MAGI_SWIGLU_ERR_DEVICE, "device %d is not sm_100 (B200)", device);
+  magi::DeviceGuard guard;
+  cudaError_t e = guard.set(device);
+  if (e != cudaSuccess) return magi::fail_cuda(e, "cudaSetDevice");
+  const long long work = M * (N / 8);
+  const long long want = (work + 255) / 256;
+  const int blocks = (int)(want < 16LL * di->sm_count ? want : 16LL * di->sm_count);
+  magi::swiglu_bwd_act_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(dy), static_cast<__nv_bfloat16*>(dh),
+      (int)M, (int)N, ldh, lddy, lddh);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : magi::fail_cuda(e, "launch of swiglu_bwd_act_kernel");
 }
 
 int64_t magi_swiglu_workspace_bytes(int64_t M, int64_t N, int64_t K, int variant, int block_n, int stages, int group_m,

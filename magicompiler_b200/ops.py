@@ -119,6 +119,54 @@ def gemm_swiglu_out(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor 
     return y.view(out_shape)
 
 
+BWD_ACT_OP_NAME = "magi_swiglu::swiglu_backward_act"
+
+
+@magi_register_custom_op(name=BWD_ACT_OP_NAME, mutates_args=(),
+                         infer_output_meta_fn=lambda h, dy: torch.empty_like(h))
+def swiglu_backward_act(h: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
+    """``dH = [dG | dU]`` from the pre-activations ``H = [G | U]`` (``[M, 2N]`` bf16) and ``dY`` (``[M, N]`` bf16):
+    one element-wise CUDA kernel (``magi_swiglu_backward_act_bf16``)."""
+    if h.dtype != torch.bfloat16 or dy.dtype != torch.bfloat16:
+        raise TypeError("swiglu_backward_act computes in bf16 only")
+    if not (h.is_cuda and dy.is_cuda) or h.device != dy.device:
+        raise TypeError("swiglu_backward_act runs on CUDA tensors of one device")
+    if h.dim() != 2 or dy.dim() != 2 or h.shape[0] != dy.shape[0] or h.shape[1] != 2 * dy.shape[1] or dy.shape[1] % 8:
+        raise ValueError(f"shapes do not match: h {tuple(h.shape)}, dy {tuple(dy.shape)} (need [M,2N], [M,N], N % 8 == 0)")
+    lib = _loader.load_library()
+    h2, dy2 = _rows_view(h, h.shape[1]), _rows_view(dy, dy.shape[1])
+    dh = torch.empty((h.shape[0], h.shape[1]), dtype=torch.bfloat16, device=h.device)
+    if h.shape[0] == 0:
+        return dh
+    dev = h.device.index if h.device.index is not None else torch.cuda.current_device()
+    rc = lib.magi_swiglu_backward_act_bf16(h2.data_ptr(), dy2.data_ptr(), dh.data_ptr(), h.shape[0], dy.shape[1],
+                                           h2.stride(0) if h.shape[0] > 1 else h.shape[1],
+                                           dy2.stride(0) if h.shape[0] > 1 else dy.shape[1], dh.stride(0), dev,
+                                           torch.cuda.current_stream(h.device).cuda_stream)
+    if rc != 0:
+        msg = f"magi_swiglu_backward_act_bf16 failed ({rc}): {_loader.last_error()}"
+        raise (ValueError(msg) if rc < 0 else RuntimeError(msg))
+    return dh
+
+
+def _gemm_swiglu_setup_context(ctx, inputs, output):
+    x, w_gate_up = inputs
+    ctx.save_for_backward(x, w_gate_up)  # the 2N-wide pre-activations are never stored: backward recomputes them
+
+
+def _gemm_swiglu_backward(ctx, grad_out):
+    """dX = dH · W and dW = dH^T · X with dH = [dG | dU]; H = X · W^T is recomputed by one library GEMM."""
+    x, w = ctx.saved_tensors
+    k = x.shape[-1]
+    x2 = x.reshape(-1, k)
+    dy2 = grad_out.reshape(-1, grad_out.shape[-1]).contiguous()
+    h = torch.matmul(x2, w.t())
+    dh = torch.ops.magi_swiglu.swiglu_backward_act(h, dy2)
+    dx = torch.matmul(dh, w).view(x.shape) if ctx.needs_input_grad[0] else None
+    dw = torch.matmul(dh.t(), x2) if ctx.needs_input_grad[1] else None
+    return dx, dw
+
+
 def _gemm_swiglu_meta(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     # shape/dtype/device only; works with a symbolic leading dimension
     return x.new_empty((*x.shape[:-1], w_gate_up.shape[0] // 2))
@@ -128,6 +176,8 @@ def _gemm_swiglu_meta(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     name=OP_NAME,
     mutates_args=(),
     infer_output_meta_fn=_gemm_swiglu_meta,
+    setup_context_fn=_gemm_swiglu_setup_context,
+    backward_fn=_gemm_swiglu_backward,
     is_compute_sensitive=True,
     is_subgraph_boundary=True,
 )

@@ -18,6 +18,7 @@ from .swiglu_oracle import (  # noqa: F401
     build,
     error_metrics,
     make_inputs,
+    swiglu_backward_gold,
     swiglu_gold,
     swiglu_gold_numpy,
     swiglu_ref_eager,

@@ -127,3 +127,17 @@ def error_metrics(y: torch.Tensor, gold: torch.Tensor) -> dict:
         "frob": (diff.norm().item() / gf.norm().item()) if gmax > 0 else diff.norm().item(),
         "gold_absmax": gmax,
     }
+
+
+def swiglu_backward_gold(x: torch.Tensor, w: torch.Tensor, dy: torch.Tensor):
+    """fp32 gold of the backward of ``silu(x·Wg^T) * (x·Wu^T)`` (the autograd PyTorch derives for the reference's
+    expression, tests/model_definition.py:337-339), written out: returns (dx [M,K], dw [2N,K]) in fp32."""
+    n = w.shape[0] // 2
+    xf, wf, dyf = x.float(), w.float(), dy.float()
+    h = xf @ wf.t()
+    g, u = h[:, :n], h[:, n:]
+    s = torch.sigmoid(g)
+    dg = dyf * u * s * (1.0 + g * (1.0 - s))
+    du = dyf * g * s
+    dh = torch.cat([dg, du], dim=1)
+    return dh @ wf, dh.t() @ xf

@@ -1,0 +1,43 @@
+"""Backward of the op without a GPU: the oracle's written-out gradient equals PyTorch autograd of the reference's
+eager expression, the backward ops are registered with working fake impls, and the mirror wires autograd up."""
+import torch
+import torch.nn.functional as F
+from torch._subclasses.fake_tensor import FakeTensorMode
+
+import magicompiler_b200 as mb
+from oracle import make_inputs, swiglu_backward_gold
+
+
+def test_oracle_backward_equals_autograd_of_reference_expression():
+    x, w = make_inputs(24, 64, 40, seed=3)
+    dy = torch.randn(24, 40, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16)
+    xf = x.float().requires_grad_(True)
+    wf = w.float().requires_grad_(True)
+    y = F.silu(F.linear(xf, wf[:40])) * F.linear(xf, wf[40:])  # the reference's expression, in fp32
+    y.backward(dy.float())
+    dx, dw = swiglu_backward_gold(x, w, dy)
+    assert torch.allclose(dx, xf.grad, rtol=1e-4, atol=1e-5)
+    assert torch.allclose(dw, wf.grad, rtol=1e-4, atol=1e-5)
+
+
+def test_backward_op_schema_and_fake_impl():
+    op = torch.ops.magi_swiglu.swiglu_backward_act.default
+    assert str(op._schema) == "magi_swiglu::swiglu_backward_act(Tensor h, Tensor dy) -> Tensor"
+    with FakeTensorMode():
+        h = torch.empty(10, 96, dtype=torch.bfloat16, device="cuda")
+        dy = torch.empty(10, 48, dtype=torch.bfloat16, device="cuda")
+        dh = mb.swiglu_backward_act(h, dy)
+        assert dh.shape == (10, 96) and dh.dtype == torch.bfloat16
+
+
+def test_autograd_graph_through_fake_tensors():
+    """The forward op carries an autograd formula built from library GEMMs and the backward op: gradients of the
+    right shapes come back for x and for the packed weight (meta tensors: nothing runs on a device)."""
+    x = torch.empty(4, 6, 64, dtype=torch.bfloat16, device="meta", requires_grad=True)
+    w = torch.empty(80, 64, dtype=torch.bfloat16, device="meta", requires_grad=True)
+    y = mb.gemm_swiglu(x, w)
+    assert y.requires_grad and y.shape == (4, 6, 40)
+    gx, gw = torch.autograd.grad(y, (x, w), torch.empty_like(y))
+    assert gx.shape == x.shape and gw.shape == w.shape and gx.dtype == torch.bfloat16
+    (gx_only,) = torch.autograd.grad(mb.gemm_swiglu(x, w.detach()), (x,), torch.empty_like(y))
+    assert gx_only.shape == x.shape

@@ -99,3 +99,69 @@ def test_rewrite_pass_on_gpu_matches_eager_module():
         got, ref = cm(x), m(x)
         assert torch.allclose(got.float(), ref.float(), rtol=2e-2, atol=2e-2 * ref.float().abs().max().item())
     assert counts == [1] and len(_pack_cache) == 1
+
+
+# ---------------------------------------------------------------- backward (training)
+def _grad_errors(got, gold):
+    from oracle import error_metrics
+
+    return error_metrics(got, gold)
+
+
+@pytest.mark.parametrize("shape", [(256, 512, 384), (300, 328, 520), (64, 1024, 2816), (4096, 1024, 2048)])
+def test_backward_against_fp32_gold_and_reference_autograd(shape):
+    """dX and dW of the op against the fp32 gradient of the reference's expression.  Tolerance (bf16 gradients, one
+    recomputed bf16 intermediate): max|d-gold|/max|gold| <= 2e-2 and Frobenius-relative <= 1e-2; and the op's error
+    stays within 1.5x of what PyTorch's own bf16 autograd of the eager expression makes on the same inputs."""
+    import torch.nn.functional as F
+
+    from oracle import swiglu_backward_gold
+
+    M, K, N = shape
+    x, w = make_inputs(M, K, N, seed=M)
+    dy = torch.randn(M, N, generator=torch.Generator().manual_seed(7)).to(torch.bfloat16)
+    xd = x.cuda().requires_grad_(True)
+    wd = w.cuda().requires_grad_(True)
+    y = mb.gemm_swiglu(xd, wd)
+    y.backward(dy.cuda())
+    dx_gold, dw_gold = swiglu_backward_gold(x.cuda(), w.cuda(), dy.cuda())
+    xe = x.cuda().requires_grad_(True)
+    we = w.cuda().requires_grad_(True)
+    (F.silu(F.linear(xe, we[:N])) * F.linear(xe, we[N:])).backward(dy.cuda())  # the reference's eager path, bf16
+    for name, got, ref, gold in (("dx", xd.grad, xe.grad, dx_gold), ("dw", wd.grad, we.grad, dw_gold)):
+        assert got.dtype == torch.bfloat16 and got.shape == gold.shape
+        m, mref = _grad_errors(got, gold), _grad_errors(ref, gold)
+        assert m["max_norm"] <= 2e-2 and m["frob"] <= 1e-2, (name, m)
+        assert m["frob"] <= 1.5 * mref["frob"] + 1e-4, (name, m, mref)
+
+
+def test_backward_act_kernel_special_cases():
+    h = torch.zeros(16, 32, dtype=torch.bfloat16, device="cuda")
+    h[:, :16] = torch.linspace(-60, 60, 16).to(torch.bfloat16)  # gate pre-activations
+    h[:, 16:] = 2.0
+    dy = torch.ones(16, 16, dtype=torch.bfloat16, device="cuda")
+    dh = mb.swiglu_backward_act(h, dy).float()
+    g = h[:, :16].float()
+    s = torch.sigmoid(g)
+    assert torch.isfinite(dh).all()
+    assert torch.allclose(dh[:, :16], 2.0 * s * (1 + g * (1 - s)), rtol=1e-2, atol=1e-3)
+    assert torch.allclose(dh[:, 16:], g * s, rtol=1e-2, atol=1e-3)
+    assert mb.swiglu_backward_act(h[:0], dy[:0]).shape == (0, 32)
+    with pytest.raises(ValueError):
+        mb.swiglu_backward_act(h, dy[:, :8])
+
+
+def test_training_step_through_torch_compile():
+    """The op inside a compiled training step (AOTAutograd traces its backward formula): gradients match eager."""
+    torch._dynamo.reset()
+    x, w = make_inputs(192, 256, 384, seed=4)
+    xd = x.cuda()
+    w1 = w.cuda().requires_grad_(True)
+    w2 = w.cuda().requires_grad_(True)
+
+    def loss_fn(x, w):
+        return (mb.gemm_swiglu(x, w).float() ** 2).mean()
+
+    loss_fn(xd, w1).backward()
+    torch.compile(loss_fn, backend="aot_eager", fullgraph=True)(xd, w2).backward()
+    assert torch.allclose(w1.grad.float(), w2.grad.float(), rtol=1e-2, atol=1e-6)

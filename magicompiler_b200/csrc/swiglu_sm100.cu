@@ -219,6 +219,9 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   if constexpr (kCtas == 2) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
+  // A kernel launched behind this one with programmatic stream serialisation (the split-K reduce) may be scheduled
+  // now; it still waits for this grid to complete before it reads anything (griddepcontrol.wait on its side).
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   long long probe_c0 = 0;
   unsigned long long probe_t0 = 0;
   if (blockIdx.x == 0 && threadIdx.x == 64) {  // lane 0 of the allocator warp, idle between set-up and teardown
@@ -553,6 +556,7 @@ swiglu_splitk_reduce_kernel(const float* __restrict__ ws, __nv_bfloat16* __restr
   const int groups = block_n / 8;
   const long long total = (long long)num_n_tiles * M * groups;
   const uint64_t policy = l2_policy_evict_first();
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // the partial sums of the tile kernel are complete and visible
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     const int cg = (int)(i % groups);
@@ -1021,9 +1025,18 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
     if (p.k_splits > 1) {
       const long long work = (long long)p.num_n_tiles * M * (p.block_n / 8);
       const int blocks = (int)((work + 255) / 256 < 4LL * di->sm_count ? (work + 255) / 256 : 4LL * di->sm_count);
-      swiglu_splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(a.ws, a.y, a.M, a.N, a.ldy, p.block_n, p.num_n_tiles,
-                                                             p.k_splits);
-      e = cudaGetLastError();
+      // scheduled while the tile kernel drains (programmatic dependent launch); it waits for that grid itself
+      cudaLaunchConfig_t rc_cfg = {};
+      cudaLaunchAttribute rc_attr[1];
+      rc_attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      rc_attr[0].val.programmaticStreamSerializationAllowed = 1;
+      rc_cfg.gridDim = dim3((unsigned)blocks);
+      rc_cfg.blockDim = dim3(256);
+      rc_cfg.stream = stream;
+      rc_cfg.attrs = rc_attr;
+      rc_cfg.numAttrs = 1;
+      e = cudaLaunchKernelEx(&rc_cfg, swiglu_splitk_reduce_kernel, (const float*)a.ws, a.y, a.M, a.N, a.ldy, p.block_n,
+                             p.num_n_tiles, p.k_splits);
       if (e != cudaSuccess) return fail_cuda(e, "launch of swiglu_splitk_reduce_kernel");
     }
     return 0;

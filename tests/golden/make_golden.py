@@ -59,7 +59,8 @@ def import_reference(ref_root: Path):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=str(HERE.parent.parent.parent / "reference"),
+                    help="MagiCompiler checkout (default: a directory \"reference\" next to this repository)")
     args = ap.parse_args()
     from oracle import make_inputs, to_bits
 

@@ -133,7 +133,8 @@ def test_mirror_autograd_and_flags():
 
 
 # ---- integration with a real MagiCompiler checkout (CPU, eager backend) --------------------------------
-_REF = Path(os.environ.get("MAGI_COMPILER_ROOT", "/root/reference"))
+# a MagiCompiler checkout: $MAGI_COMPILER_ROOT, else a directory "reference" next to this repository
+_REF = Path(os.environ.get("MAGI_COMPILER_ROOT", ROOT.parent / "reference"))
 
 _SCRIPT = textwrap.dedent('''
     import json, os, sys, tempfile

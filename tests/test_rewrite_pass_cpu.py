@@ -114,7 +114,8 @@ def test_cached_packer_packs_once_and_tracks_updates():
         pack_gate_up_cached(torch.zeros(4, 8), torch.zeros(6, 8))
 
 
-_REF = Path(os.environ.get("MAGI_COMPILER_ROOT", "/root/reference"))
+# a MagiCompiler checkout: $MAGI_COMPILER_ROOT, else a directory "reference" next to this repository
+_REF = Path(os.environ.get("MAGI_COMPILER_ROOT", ROOT.parent / "reference"))
 _SCRIPT = textwrap.dedent('''
     import json, os, sys, tempfile
     stub = tempfile.mkdtemp(); open(os.path.join(stub, "graphviz.py"), "w").write("class Digraph:\\n    pass\\n")

@@ -141,12 +141,15 @@ def cpu_eager_tflops(M, K, N, x, w, target_s=12.0, max_rows=None):
     rows2 = max(16, rows2 // 16 * 16) if M >= 16 else M
     xs = x[:rows2].contiguous()
     times = []
-    for _ in range(3):
+    reps = 3
+    while len(times) < reps:
         t0 = time.perf_counter()
         swiglu_ref_eager(xs, w)
         times.append(time.perf_counter() - t0)
+        if len(times) == 3:  # about target_s of CPU work in total, at most 40 repetitions
+            reps = int(min(40, max(3, target_s / max(statistics.median(times), 1e-6))))
     t = statistics.median(times)
-    return flops_of(rows2, K, N) / t / 1e12, rows2, threads, t
+    return flops_of(rows2, K, N) / t / 1e12, rows2, threads, t, len(times)
 
 
 def run_reference_arm(args, rank, world):
@@ -450,13 +453,13 @@ def main():
                        "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms,
                        "how": f"pinned X -> device, op, Y -> pinned host, {chunks} row chunk(s) pipelined on side streams"}
     if world == 1 and not args.no_cpu_baseline:
-        v, rows, threads, t = cpu_eager_tflops(M, K, N, x_cpu, w_cpu)
+        v, rows, threads, t, reps = cpu_eager_tflops(M, K, N, x_cpu, w_cpu)
         if bound == "hbm":
             v = bytes_of(rows, K, N) / t / 1e9
         line["cpu_baseline"] = {
             "value": v, "unit": unit, "cores": threads, "kind": "port",
             "sample": f"reference eager expression (torch CPU, bf16) on the first {rows} of {M} rows with the full W, "
-                      f"median of 3 runs of {t:.2f} s"}
+                      f"median of {reps} runs of {t:.2f} s"}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -36,7 +36,17 @@ def _pack_meta(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
     return w_gate.new_empty((w_gate.shape[0] + w_up.shape[0], w_gate.shape[1]))
 
 
-@magi_register_custom_op(name=PACK_OP_NAME, mutates_args=(), infer_output_meta_fn=_pack_meta)
+def _pack_setup_context(ctx, inputs, output):
+    ctx.gate_rows = inputs[0].shape[0]
+
+
+def _pack_backward(ctx, grad):
+    # the packed weight is cat([gate, up]): its gradient splits back into the two halves (training through the pass)
+    return grad[: ctx.gate_rows], grad[ctx.gate_rows:]
+
+
+@magi_register_custom_op(name=PACK_OP_NAME, mutates_args=(), infer_output_meta_fn=_pack_meta,
+                         setup_context_fn=_pack_setup_context, backward_fn=_pack_backward)
 def pack_gate_up_cached(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
     """``cat([w_gate, w_up])``, memoised on the identity, version counter and address of both arguments.
 

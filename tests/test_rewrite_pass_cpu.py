@@ -115,6 +115,16 @@ def test_cached_packer_packs_once_and_tracks_updates():
 
 
 # a MagiCompiler checkout: $MAGI_COMPILER_ROOT, else a directory "reference" next to this repository
+def test_cached_packer_passes_gradients_to_both_weights():
+    clear_pack_cache()
+    wg = torch.nn.Parameter(torch.randn(8, 16))
+    wu = torch.nn.Parameter(torch.randn(8, 16))
+    packed = pack_gate_up_cached(wg, wu)
+    (packed * torch.arange(16.0).view(16, 1)).sum().backward()
+    assert torch.equal(wg.grad, torch.arange(8.0).view(8, 1).expand(8, 16))
+    assert torch.equal(wu.grad, torch.arange(8.0, 16.0).view(8, 1).expand(8, 16))
+
+
 _REF = Path(os.environ.get("MAGI_COMPILER_ROOT", ROOT.parent / "reference"))
 _SCRIPT = textwrap.dedent('''
     import json, os, sys, tempfile

@@ -45,7 +45,7 @@ constexpr int kTmemCols = 512;       // whole tensor memory of the SM (one CTA p
 constexpr uint32_t kABytes = kBM * kBK * 2;
 constexpr int kSmemLimit = 232448 - 1024;  // dynamic part of the 227 KB opt-in maximum (static barriers take the rest)
 constexpr int kSmemFloor = 120 * 1024;  // keeps a second CTA off the SM (it would block in tcgen05.alloc)
-constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
+constexpr long long kWaitLimitCycles = 6000000000LL;  // three to four seconds of SM cycles
 
 __device__ unsigned int g_watchdog[4];  // {role that gave up, block, stage/buffer, parity}
 // {SM cycles, nanoseconds} block 0 of the most recent tile kernel spent between set-up and teardown: the

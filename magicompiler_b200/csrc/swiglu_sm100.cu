@@ -1006,9 +1006,12 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   a.k_splits = p.k_splits;
   a.kb_per_split = p.kb_per_split;
   a.ws = p.k_splits > 1 ? static_cast<float*>(workspace) : nullptr;
-  // default L2 priorities: a band of X rows is re-read by every column tile -> keep; W tiles and Y are streamed
+  // Default L2 priorities (ncu, DRAM bytes per launch).  X: a band of X rows is re-read by every column tile ->
+  // keep.  Y: written once -> evict first.  W: in the tile schedules a W tile is shared by all row units of the band
+  // that run at the same time, and marking it evict-first makes late CTAs miss it (+25..70 % DRAM reads) -> normal;
+  // in the STREAM schedule every W byte is read exactly once -> evict first.
   a.x_hint = 2;
-  a.w_hint = 1;
+  a.w_hint = (p.variant == MAGI_SWIGLU_VARIANT_STREAM) ? 1 : 0;
   a.y_hint = 1;
   if (const char* env = getenv("MAGI_SWIGLU_L2_HINTS")) {  // three digits "xwy", each 0/1/2 (tuning aid)
     if (strlen(env) == 3) {

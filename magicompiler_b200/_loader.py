@@ -17,7 +17,7 @@ CSRC = _PKG / "csrc"
 INCLUDE = _PKG.parent / "include"
 LIB_PATH = _PKG / "_lib" / "libmagi_swiglu.so"
 SOURCES = [CSRC / "swiglu_sm100.cu"]
-HEADERS = [CSRC / "ptx_sm100.cuh", INCLUDE / "magi_swiglu.h"]
+HEADERS = [CSRC / "ptx_sm100.cuh", CSRC / "swiglu_kernels.cuh", CSRC / "swiglu_plan.hpp", INCLUDE / "magi_swiglu.h"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

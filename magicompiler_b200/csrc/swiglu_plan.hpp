@@ -1,0 +1,178 @@
+// Host-side schedule selection for the SwiGLU kernels: which variant, tile width, ring depth, raster band, CTA
+// count and (for narrow small-M problems) how many CTAs split K, plus the error-text helpers of the C ABI.
+// Pure host arithmetic: nothing here touches a GPU.
+#pragma once
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "../../include/magi_swiglu.h"
+#include "swiglu_kernels.cuh"
+
+namespace magi {
+
+thread_local char g_err[512] = "";
+
+static int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+static int fail_cuda(cudaError_t e, const char* what) {
+  snprintf(g_err, sizeof(g_err), "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+  return e == cudaSuccess ? 1 : (int)e;
+}
+
+struct Plan {
+  int variant, block_n, stages, grid, tiles, smem_bytes, acc_bufs, n_mma;
+  int num_m_tiles, num_n_tiles, num_k_blocks, group_m;
+  int ctas;  // CTAs per tile: 1, or 2 for the CTA-pair schedule
+  int split; // CTA pairs with two MMAs per step and block_n % 32 == 0: two separately released half tiles
+  int k_splits, kb_per_split;          // split-K of the STREAM schedule (1 = off)
+  int64_t ws_bytes;                    // fp32 partial sums of a split-K plan (0 = none)
+  uint32_t stage_bytes, b_second;
+};
+
+static inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+constexpr int64_t kWorkspaceCap = 64LL << 20;  // never plan for more scratch than this
+
+// Scratch bytes of a split-K plan: per tile k_splits x M x 2*block_n fp32 partial sums.
+static inline int64_t splitk_bytes(int64_t tiles, int64_t z, int64_t M, int64_t bn) { return tiles * z * M * 2 * bn * 4; }
+
+// Estimated time (ns) of the STREAM schedule: every CTA runs kb_per_split K-steps; a K-step costs at least
+// ~530 ns of MMA issue (measured) and otherwise its share of HBM bandwidth; split-K adds a reduction.
+static inline double stream_cost_ns(int64_t N, int64_t num_kb, int bn, int z, int ctas) {
+  const int64_t slabs = (N + bn - 1) / bn;
+  const int64_t items = slabs * z;
+  const int64_t waves = (items + ctas - 1) / ctas;
+  const int64_t active = items < ctas ? items : ctas;
+  const int64_t kpz = (num_kb + z - 1) / z;
+  const double step_ns = 256.0 * bn * (double)active / 6200.0;  // 2*bn rows x 128 B per K-step over ~6.2 TB/s
+  return (double)waves * ((double)kpz * (step_ns > 533.0 ? step_ns : 533.0) + 1500.0 + 6.0 * bn + (z > 1 ? 2500.0 : 0.0));
+}
+
+static int make_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, int stages, int group_m, int max_ctas,
+                     int sm_count, int64_t ws_limit, Plan* p) {
+  if (M < 0 || N <= 0 || K <= 0 || M > 0x7fffff00LL || N > 0x3fffff00LL || K > 0x7fffff00LL)
+    return fail(MAGI_SWIGLU_ERR_SHAPE, "shape out of range: M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
+  if (N % 8 != 0 || K % 8 != 0)
+    return fail(MAGI_SWIGLU_ERR_SHAPE, "N (%lld) and K (%lld) must be multiples of 8", (long long)N, (long long)K);
+  if (variant == MAGI_SWIGLU_VARIANT_AUTO) variant = (M <= 128) ? MAGI_SWIGLU_VARIANT_STREAM : MAGI_SWIGLU_VARIANT_MMA2;
+  if (variant != MAGI_SWIGLU_VARIANT_MMA && variant != MAGI_SWIGLU_VARIANT_STREAM &&
+      variant != MAGI_SWIGLU_VARIANT_SIMT && variant != MAGI_SWIGLU_VARIANT_MMA2)
+    return fail(MAGI_SWIGLU_ERR_VARIANT, "unknown variant %d", variant);
+  if (sm_count <= 0) return fail(MAGI_SWIGLU_ERR_DEVICE, "sm_count must be positive");
+  memset(p, 0, sizeof(*p));
+  p->variant = variant;
+  if (variant == MAGI_SWIGLU_VARIANT_SIMT) {
+    p->block_n = 16;
+    p->tiles = (int)(((M + 15) / 16) * ((N + 15) / 16));
+    p->grid = p->tiles;
+    return 0;
+  }
+  if (variant == MAGI_SWIGLU_VARIANT_STREAM && M > kBM)
+    return fail(MAGI_SWIGLU_ERR_VARIANT, "STREAM variant needs M <= %d (got %lld)", kBM, (long long)M);
+  const int pair = (variant == MAGI_SWIGLU_VARIANT_MMA2) ? 2 : 1;
+  int stream_auto_width = 0;
+  p->ctas = pair;
+  int ctas = (max_ctas > 0 && max_ctas < sm_count) ? max_ctas : sm_count;
+  if (pair == 2) ctas = ctas / 2 * 2;
+  if (ctas < pair) return fail(MAGI_SWIGLU_ERR_VARIANT, "max_ctas=%d leaves no room for a CTA pair", max_ctas);
+  if (block_n == 0) {
+    if (variant == MAGI_SWIGLU_VARIANT_MMA2) {
+      // Wide tiles move the fewest operand bytes per FLOP (256 columns fill tensor memory: gate + up = 512
+      // fp32 columns), but the persistent grid runs whole waves of tiles.  Measured on B200, one tile of
+      // width bn costs about (bn + 146) units of time (fixed part: epilogue, pipeline refill and the
+      // narrower tiles' lower operand reuse), so pick the width with the cheapest total of waves x tile cost.
+      if (N < 128) {
+        block_n = round_up((int)N, 16);
+      } else {
+        const int64_t units = ctas / 2;
+        const int64_t m_units = (M + 2 * kBM - 1) / (2 * kBM);
+        int64_t best_cost = -1;
+        for (int bn = 256; bn >= 128; bn -= 32) {  // multiples of 32: both half tiles stay multiples of 16
+          const int64_t tiles = m_units * ((N + bn - 1) / bn);
+          const int64_t cost = ((tiles + units - 1) / units) * (bn + 146);
+          if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            block_n = bn;
+          }
+        }
+      }
+    } else if (variant == MAGI_SWIGLU_VARIANT_MMA) {
+      block_n = (N >= 128) ? 128 : round_up((int)N, 16);
+    } else {
+      // one slab per SM if it fits in tensor memory (gate + up <= 512 fp32 columns)
+      int64_t per = (N + ctas - 1) / ctas;
+      block_n = round_up((int)(per < 16 ? 16 : per), 16);
+      if (block_n > 256) block_n = 256;
+      stream_auto_width = 1;
+    }
+  }
+  int k_splits = 1;
+  if (variant == MAGI_SWIGLU_VARIANT_STREAM && M > 0) {
+    // Narrow weights (a column shard of a decode GEMM) leave each SM too little W per K-step to hide the MMA
+    // issue time; with scratch available, several CTAs share a slab and split K between them.
+    const int64_t num_kb = (K + kBK - 1) / kBK;
+    if (ws_limit > kWorkspaceCap) ws_limit = kWorkspaceCap;
+    int forced = 0;
+    if (const char* env = getenv("MAGI_SWIGLU_K_SPLITS")) forced = atoi(env);  // tuning aid
+    double best = stream_cost_ns(N, num_kb, block_n, 1, ctas);
+    const int bn_lo = stream_auto_width ? 32 : block_n, bn_hi = stream_auto_width ? 256 : block_n;
+    for (int bn = bn_lo; bn <= bn_hi; bn += 16) {
+      for (int z = 1; z <= 8; ++z) {
+        if (forced > 0 && z != forced) continue;
+        if (z > 1 && ((num_kb + z - 1) / z < 4 || (int64_t)((num_kb + z - 1) / z) * (z - 1) >= num_kb)) continue;
+        const int64_t slabs = (N + bn - 1) / bn;
+        if (z > 1 && splitk_bytes(slabs, z, M, bn) > ws_limit) continue;
+        const double c = stream_cost_ns(N, num_kb, bn, z, ctas);
+        if (c < best * 0.97 || (forced > 0 && z == forced && k_splits != forced)) {  // 3 %: prefer the simpler plan
+          best = c;
+          block_n = bn;
+          k_splits = z;
+        }
+      }
+    }
+  }
+  if (block_n < 16 || block_n > 256 || block_n % 16 != 0)
+    return fail(MAGI_SWIGLU_ERR_VARIANT, "block_n=%d must be a multiple of 16 in [16,256]", block_n);
+  p->block_n = block_n;
+  p->n_mma = (2 * block_n <= 256) ? 1 : 2;
+  p->acc_bufs = (4 * block_n <= kTmemCols) ? 2 : 1;
+  // weight rows per CTA and stage: gate + up rows of the tile, split between the CTAs of a pair
+  p->stage_bytes = kABytes + 2u * (uint32_t)block_n * 128u / (uint32_t)pair;
+  p->b_second = (uint32_t)block_n * 128u / (uint32_t)pair;
+  p->split = (pair == 2 && p->n_mma == 2 && block_n % 32 == 0 && !getenv("MAGI_SWIGLU_NO_SPLIT")) ? 1 : 0;
+  const int fit = (kSmemLimit - 1024) / (int)p->stage_bytes;
+  int max_stages = fit < kMaxStages ? fit : kMaxStages;
+  if (stages == 0) stages = max_stages;
+  if (stages < 2 || stages > max_stages)
+    return fail(MAGI_SWIGLU_ERR_VARIANT, "stages=%d out of range [2,%d] for block_n=%d", stages, max_stages, block_n);
+  p->stages = stages;
+  int smem = stages * (int)p->stage_bytes + 1024;
+  p->smem_bytes = smem < kSmemFloor ? kSmemFloor : smem;
+  p->num_m_tiles = (int)((M + kBM * pair - 1) / (kBM * pair));
+  p->num_n_tiles = (int)((N + block_n - 1) / block_n);
+  p->num_k_blocks = (int)((K + kBK - 1) / kBK);
+  if ((int64_t)p->num_m_tiles * p->num_n_tiles > 0x7fffffffLL) return fail(MAGI_SWIGLU_ERR_SHAPE, "too many tiles");
+  p->tiles = p->num_m_tiles * p->num_n_tiles;
+  if (group_m <= 0) {
+    // band height: keep one band of X rows (group_m units x K) around 32 MB so it stays in L2 while W streams by
+    const int64_t unit_bytes = (int64_t)kBM * pair * K * 2;
+    int64_t g = (32LL << 20) / (unit_bytes > 0 ? unit_bytes : 1);
+    group_m = (int)(g < 4 ? 4 : (g > 64 ? 64 : g));
+  }
+  p->group_m = group_m;
+  p->k_splits = k_splits;
+  p->kb_per_split = (p->num_k_blocks + k_splits - 1) / k_splits;
+  if (k_splits > 1) p->ws_bytes = splitk_bytes(p->tiles, k_splits, M, block_n);
+  const int64_t items = (int64_t)p->tiles * pair * k_splits;
+  p->grid = (items < ctas) ? (int)items : ctas;
+  return 0;
+}
+}  // namespace magi

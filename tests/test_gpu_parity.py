@@ -279,3 +279,26 @@ def test_workspace_entry_point_contract():
     assert rc == -3 and "aligned" in _loader.last_error()
     rc, y_null = call(None, 0)
     assert rc == 0 and torch.equal(y_null, y_small)
+
+
+def test_random_shapes_all_schedules():
+    """Seeded sweep of irregular shapes (any M, N and K multiples of 8) through every schedule that accepts them."""
+    import random
+
+    rng = random.Random(1234)
+    checked = 0
+    for _ in range(48):
+        M = rng.choice([1, 2, 7, 31, 100, 128, 129, 200, 257, 511, 640, 1000])
+        N = 8 * rng.randint(1, 180)
+        K = 8 * rng.randint(1, 160)
+        x, w = make_inputs(M, K, N, seed=checked)
+        xd, wd = x.cuda(), w.cuda()
+        gold = gold_fp32_gpu(xd, wd)
+        variants = ["auto", "mma", "mma2"] + (["stream"] if M <= 128 else [])
+        outs = {}
+        for v in variants:
+            outs[v] = mb.gemm_swiglu_out(xd, wd, variant=v)
+            assert_parity(outs[v], gold, f"M={M} N={N} K={K} {v}")
+            checked += 1
+        assert torch.equal(outs["mma"], outs["mma2"]), (M, N, K)
+    assert checked >= 150

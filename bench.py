@@ -207,7 +207,8 @@ def run_mlp_block(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
     M, K, N, _, desc = WORKLOADS["mlp_block"]
     x_cpu, w_cpu, wd_cpu = make_inputs(M, K, N, seed=0, with_down=True)
-    mlp = mb.TensorParallelSwiGLUMLP(w_cpu, wd_cpu, rank, world, chunks=args.chunks).to(dev)
+    mlp = mb.TensorParallelSwiGLUMLP(w_cpu, wd_cpu, rank, world, chunks=args.chunks,
+                                     down_fn=mb.gemm_nt if args.down == "own" else None).to(dev)
     del w_cpu, wd_cpu
     x = x_cpu.to(dev)
 
@@ -243,12 +244,14 @@ def run_mlp_block(args, rank, world, local_rank):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic (CPU generator seed 0, X~N(0,1), W~N(0,0.02), bf16)",
             "config": {"workload": "mlp_block", "shape": desc, "chunks": args.chunks,
+                       "down_projection": "magi_swiglu_gemm_nt_bf16 (own tile kernel)" if args.down == "own"
+                       else "torch.matmul (library GEMM)",
                        "parallelism": f"tp{world}: column-parallel gate/up, row-parallel down, NCCL all-reduce of "
                                       f"[{M},{K}] bf16", "l2": "inputs (1.7 GB) larger than L2, back-to-back steps"},
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": float(peaks["bf16_tflops_sustained"]),
                          "unit": "TFLOP/s", "frac": per_gpu / float(peaks["bf16_tflops_sustained"]), "traffic": None,
                          "peak_kind": f"{kind} cuBLAS bf16 sustained (kernels timed inside a long step)"},
-            "gpu_launches": args.steps * args.chunks}), flush=True)
+            "gpu_launches": args.steps * args.chunks * (2 if args.down == "own" else 1)}), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -265,6 +268,7 @@ def main():
     ap.add_argument("--stages", type=int, default=0)
     ap.add_argument("--group-m", type=int, default=0)
     ap.add_argument("--chunks", type=int, default=1, help="mlp_block: row chunks whose all-reduce overlaps the next chunk")
+    ap.add_argument("--down", default="own", choices=["own", "library"], help="mlp_block: kernel of the down projection")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-flush", action="store_true", help="profiling runs only: skip the L2 flush kernels")

@@ -120,6 +120,14 @@ int magi_swiglu_forward_bf16_static(const void* x, const void* w_gate_up, void* 
                                     int64_t ldx, int64_t ldw, int64_t ldy,
                                     int device, void* cuda_stream);
 
+/* Plain bf16 GEMM on the same tile kernels: C[M,N] = A[M,K] · B[N,K]^T (both operands row-major with the reduction
+ * dimension contiguous, i.e. y = F.linear(a, b)), fp32 accumulation, one rounding.  N % 16 == 0, K % 8 == 0, strides
+ * multiples of 8, 16-byte aligned pointers.  Used for the row-parallel down projection of the MLP block.
+ * Replaces: self.down_proj(...) of TransformerMLP.forward (tests/model_definition.py:339) and w2 of FeedForward
+ * (example/training/llama3.py:169,173), which the reference runs through a library GEMM. */
+int magi_swiglu_gemm_nt_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,
+                      int64_t lda, int64_t ldb, int64_t ldc, int device, void* cuda_stream);
+
 /* Backward of the activation.  h is [M, 2N] = [G | U], the pre-activations X·Wg^T and X·Wu^T (bf16, row stride ldh),
  * dy is [M, N]; writes dh = [dG | dU] ([M, 2N], row stride lddh) with dG = dY*U*s*(1 + G*(1-s)), dU = dY*G*s,
  * s = sigmoid(G); fp32 arithmetic, one rounding.  The GEMMs around it (recomputing h, dX = dH·W, dW = dH^T·X) are

@@ -79,6 +79,7 @@ struct KArgs {
                       // the tile is handed back to the MMA issuer before the high half has been drained
   int acc_bufs;       // tensor-memory accumulator buffers (2 = epilogue overlaps next tile)
   int wide_store;     // y base and row pitch are 32-byte aligned: 256-bit stores (one full sector per thread)
+  int plain;          // 1: plain GEMM C = A·B^T; B's first N rows fill output columns [0,N), its last N rows [N,2N)
   int x_hint, w_hint, y_hint;  // L2 eviction priority of X tiles, W tiles and Y stores: 0 normal, 1 first, 2 last
   // Split-K (STREAM schedule on narrow weights): k_splits CTAs share one tile, each sums kb_per_split K-steps and
   // parks its fp32 partial sums in `ws`; swiglu_splitk_reduce_kernel adds them in split order and writes Y.
@@ -146,6 +147,40 @@ __device__ __forceinline__ uint4 swiglu_pack8(const uint32_t* g, const uint32_t*
                             silu_mul(__uint_as_float(g[7]), __uint_as_float(u[7])));
   v.w = *reinterpret_cast<uint32_t*>(&p);
   return v;
+}
+
+// Plain-GEMM epilogue: eight fp32 accumulator values rounded to bf16, no activation.
+__device__ __forceinline__ uint4 plain_pack8(const uint32_t* v) {
+  uint4 o;
+  __nv_bfloat162 p;
+  p = __floats2bfloat162_rn(__uint_as_float(v[0]), __uint_as_float(v[1]));
+  o.x = *reinterpret_cast<uint32_t*>(&p);
+  p = __floats2bfloat162_rn(__uint_as_float(v[2]), __uint_as_float(v[3]));
+  o.y = *reinterpret_cast<uint32_t*>(&p);
+  p = __floats2bfloat162_rn(__uint_as_float(v[4]), __uint_as_float(v[5]));
+  o.z = *reinterpret_cast<uint32_t*>(&p);
+  p = __floats2bfloat162_rn(__uint_as_float(v[6]), __uint_as_float(v[7]));
+  o.w = *reinterpret_cast<uint32_t*>(&p);
+  return o;
+}
+
+template <int kCols>
+__device__ __forceinline__ void store_cols_plain(__nv_bfloat16* dst, const uint32_t* v, int cols_valid, bool wide,
+                                                 uint64_t policy) {
+#pragma unroll
+  for (int j = 0; j < kCols / 16; ++j) {
+    if (16 * j + 16 <= cols_valid) {
+      const uint4 lo = plain_pack8(v + 16 * j), hi = plain_pack8(v + 16 * j + 8);
+      if (wide) {
+        st_global_v8_hint(dst + 16 * j, lo, hi, policy);
+      } else {
+        st_global_v4_hint(dst + 16 * j, lo, policy);
+        st_global_v4_hint(dst + 16 * j + 8, hi, policy);
+      }
+    } else if (16 * j + 8 <= cols_valid) {
+      st_global_v4_hint(dst + 16 * j, plain_pack8(v + 16 * j), policy);
+    }
+  }
 }
 
 // n (8, 16, 24 or 32 ...) consecutive outputs of one row starting at dst; `wide` = dst is 32-byte aligned
@@ -482,10 +517,19 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         };
         auto process = [&](const uint32_t (&g)[32], const uint32_t (&u)[32], int c, int w) {
           if (!row_ok) return;
-          if (w == 32)
+          if (a.plain) {  // plain GEMM: the "gate" accumulator is output column n, the "up" accumulator column N + n
+            if (w == 32) {
+              store_cols_plain<32>(yrow + c, g, valid - c, wide, y_policy);
+              store_cols_plain<32>(yrow + a.N + c, u, valid - c, wide, y_policy);
+            } else {
+              store_cols_plain<16>(yrow + c, g, valid - c, wide, y_policy);
+              store_cols_plain<16>(yrow + a.N + c, u, valid - c, wide, y_policy);
+            }
+          } else if (w == 32) {
             store_cols<32>(yrow + c, g, u, valid - c, wide, y_policy);
-          else
+          } else {
             store_cols<16>(yrow + c, g, u, valid - c, wide, y_policy);
+          }
         };
         auto release = [&]() {
           MAGI_TRACE(6 + seg * 4, it == 1 && warp == 4 && lane == 0);  // warp 4 has read its last column

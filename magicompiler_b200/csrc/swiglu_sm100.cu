@@ -108,11 +108,11 @@ struct DeviceGuard {
 
 static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int64_t ldx,
                         int64_t ldw, int64_t ldy, int device, void* stream_v, int variant, int block_n, int stages,
-                        int group_m, int max_ctas, void* workspace, int64_t workspace_bytes) {
+                        int group_m, int max_ctas, void* workspace, int64_t workspace_bytes, int plain = 0) {
   g_err[0] = 0;
   if (M == 0 && N > 0 && K > 0) return 0;
   if (!x || !w || !y) return fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
-  if (ldx < K || ldw < K || ldy < N)
+  if (ldx < K || ldw < K || ldy < (plain ? 2 * N : N))
     return fail(MAGI_SWIGLU_ERR_SHAPE, "row strides too small: ldx=%lld ldw=%lld (K=%lld) ldy=%lld (N=%lld)",
                 (long long)ldx, (long long)ldw, (long long)K, (long long)ldy, (long long)N);
   if (ldx % 8 || ldw % 8 || ldy % 8) return fail(MAGI_SWIGLU_ERR_ALIGN, "row strides must be multiples of 8 elements");
@@ -200,7 +200,8 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   a.b_second = p.b_second;
   a.split = p.split;
   a.acc_bufs = p.acc_bufs;
-  a.wide_store = (((uintptr_t)y & 31u) == 0 && ldy % 16 == 0) ? 1 : 0;
+  a.wide_store = (((uintptr_t)y & 31u) == 0 && ldy % 16 == 0 && (!plain || N % 16 == 0)) ? 1 : 0;
+  a.plain = plain;
   a.k_splits = p.k_splits;
   a.kb_per_split = p.kb_per_split;
   a.ws = p.k_splits > 1 ? static_cast<float*>(workspace) : nullptr;
@@ -343,6 +344,18 @@ int magi_swiglu_forward_bf16_static(const void* x, const void* w_gate_up, void* 
   }
   return magi::forward_impl(x, w_gate_up, y, M, N, K, ldx, ldw, ldy, device, cuda_stream, MAGI_SWIGLU_VARIANT_AUTO, 0, 0,
                             0, 0, scratch, magi::kStaticScratchBytes);
+}
+
+int magi_swiglu_gemm_nt_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                      int64_t ldc, int device, void* cuda_stream) {
+  magi::g_err[0] = 0;
+  if (N <= 0 || N % 16 != 0)
+    return magi::fail(MAGI_SWIGLU_ERR_SHAPE, "magi_swiglu_gemm_nt_bf16 needs N (%lld) to be a positive multiple of 16", (long long)N);
+  // The tile kernels see B as a packed pair: rows [0, N/2) and rows [N/2, N) land in the two accumulator halves
+  // and the plain epilogue writes them to output columns n and N/2 + n.  M <= 128 runs the one-CTA tile schedule
+  // (the streaming schedule's split-K reduce applies the activation).
+  const int variant = (M <= 128) ? MAGI_SWIGLU_VARIANT_MMA : MAGI_SWIGLU_VARIANT_MMA2;
+  return magi::forward_impl(a, b, c, M, N / 2, K, lda, ldb, ldc, device, cuda_stream, variant, 0, 0, 0, 0, nullptr, 0, 1);
 }
 
 int magi_swiglu_backward_act_bf16(const void* h, const void* dy, void* dh, int64_t M, int64_t N, int64_t ldh,

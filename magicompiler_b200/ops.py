@@ -119,6 +119,36 @@ def gemm_swiglu_out(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor 
     return y.view(out_shape)
 
 
+GEMM_NT_OP_NAME = "magi_swiglu::gemm_nt"
+
+
+@magi_register_custom_op(name=GEMM_NT_OP_NAME, mutates_args=(),
+                         infer_output_meta_fn=lambda a, b: a.new_empty((*a.shape[:-1], b.shape[0])),
+                         is_compute_sensitive=True)
+def gemm_nt(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``a @ b.T`` (``F.linear(a, b)``) in bf16 on the tile kernels of the fused op (``magi_swiglu_gemm_nt_bf16``):
+    ``a`` is ``[..., K]``, ``b`` is ``[N, K]`` with N a multiple of 16; fp32 accumulation, one rounding."""
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise TypeError("gemm_nt computes in bf16 only")
+    if not (a.is_cuda and b.is_cuda) or a.device != b.device:
+        raise TypeError("gemm_nt runs on CUDA tensors of one device")
+    if b.dim() != 2 or a.dim() < 1 or a.shape[-1] != b.shape[1] or b.shape[0] % 16 or b.shape[1] % 8 or b.shape[1] == 0:
+        raise ValueError(f"shapes do not fit: a {tuple(a.shape)}, b {tuple(b.shape)} (need [..,K], [N,K], N % 16 == 0, K % 8 == 0)")
+    n, k = b.shape
+    a2, b2 = _rows_view(a, k), _rows_view(b, k)
+    m = a2.shape[0]
+    c = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
+    if m > 0:
+        dev = a.device.index if a.device.index is not None else torch.cuda.current_device()
+        rc = _loader.load_library().magi_swiglu_gemm_nt_bf16(
+            a2.data_ptr(), b2.data_ptr(), c.data_ptr(), m, n, k, a2.stride(0) if m > 1 else k, b2.stride(0), n, dev,
+            torch.cuda.current_stream(a.device).cuda_stream)
+        if rc != 0:
+            msg = f"magi_swiglu_gemm_nt_bf16 failed ({rc}): {_loader.last_error()}"
+            raise (ValueError(msg) if rc < 0 else RuntimeError(msg))
+    return c.view(*a.shape[:-1], n)
+
+
 BWD_ACT_OP_NAME = "magi_swiglu::swiglu_backward_act"
 
 

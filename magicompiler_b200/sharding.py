@@ -80,9 +80,10 @@ class TensorParallelSwiGLUMLP(torch.nn.Module):
     """
 
     def __init__(self, w_gate_up_full: torch.Tensor, w_down_full: torch.Tensor, rank: int = 0, world: int = 1,
-                 group=None, chunks: int = 1, swiglu_fn: Callable | None = None):
+                 group=None, chunks: int = 1, swiglu_fn: Callable | None = None, down_fn: Callable | None = None):
         super().__init__()
         self.rank, self.world, self.group, self.chunks = rank, world, group, max(1, int(chunks))
+        self._down = down_fn  # (h [m, N/P], w_down [K_out, N/P]) -> [m, K_out]; None = library GEMM (torch.matmul)
         self.gate_up = ColumnParallelSwiGLU(w_gate_up_full, rank, world, swiglu_fn)
         self.w_down = torch.nn.Parameter(shard_down(w_down_full, rank, world), requires_grad=False)
 
@@ -96,7 +97,10 @@ class TensorParallelSwiGLUMLP(torch.nn.Module):
         for lo in range(0, m, step or 1):
             hi = min(m, lo + step)
             h = self.gate_up(x2[lo:hi])
-            torch.matmul(h, self.w_down.t(), out=out[lo:hi])  # plain library GEMM: partial sums of this rank
+            if self._down is None:
+                torch.matmul(h, self.w_down.t(), out=out[lo:hi])  # plain library GEMM: partial sums of this rank
+            else:
+                out[lo:hi] = self._down(h, self.w_down)
             if self.world > 1:
                 works.append(dist.all_reduce(out[lo:hi], op=dist.ReduceOp.SUM, group=self.group, async_op=True))
         for wk in works:

@@ -165,3 +165,33 @@ def test_training_step_through_torch_compile():
     loss_fn(xd, w1).backward()
     torch.compile(loss_fn, backend="aot_eager", fullgraph=True)(xd, w2).backward()
     assert torch.allclose(w1.grad.float(), w2.grad.float(), rtol=1e-2, atol=1e-6)
+
+
+@pytest.mark.parametrize("shape", [(256, 512, 512), (300, 1056, 328), (64, 2048, 1024), (4096, 4096, 2048), (1, 16, 8)])
+def test_plain_gemm_on_the_tile_kernels(shape):
+    """gemm_nt = F.linear on the same kernels (identity epilogue) against an fp32 gold."""
+    M, N, K = shape
+    g = torch.Generator().manual_seed(M + N)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    b = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    c = mb.gemm_nt(a, b)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    gold = a.float() @ b.float().t()
+    torch.backends.cuda.matmul.allow_tf32 = prev
+    from oracle import error_metrics
+
+    m = error_metrics(c, gold)
+    assert c.shape == (M, N) and m["max_norm"] <= 1e-2 and m["frob"] <= 5e-3, m
+    lib = torch.nn.functional.linear(a, b)
+    assert error_metrics(c, lib.float())["max_norm"] <= 8e-3  # at most a bf16 step from the library GEMM
+    with pytest.raises(ValueError):
+        mb.gemm_nt(a, b[: N - 8] if N > 8 else b[:, :4])
+
+
+def test_mlp_with_own_down_projection():
+    x, w, wd = make_inputs(512, 256, 384, seed=2, with_down=True)
+    x, w, wd = x.cuda(), w.cuda(), wd.cuda()
+    got = mb.TensorParallelSwiGLUMLP(w, wd, chunks=2, down_fn=mb.gemm_nt)(x)
+    ref = reference_mlp(x, w, wd)
+    assert torch.allclose(got.float(), ref.float(), rtol=2e-2, atol=2e-2 * ref.float().abs().max().item())

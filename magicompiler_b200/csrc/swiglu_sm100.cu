@@ -95,10 +95,11 @@ struct DeviceGuard {
   cudaError_t set(int device) {
     cudaError_t e = cudaGetDevice(&prev);
     if (e != cudaSuccess) return e;
-    if (prev != device) {
-      e = cudaSetDevice(device);
-      changed = (e == cudaSuccess);
-    }
+    // Always set the device, even when it already is the current one: on a thread that has made no CUDA call yet
+    // (an autograd worker, say) this is what binds the device's primary context, which the driver-level
+    // tensor-map encoder needs.
+    e = cudaSetDevice(device);
+    changed = (e == cudaSuccess && prev != device);
     return e;
   }
   ~DeviceGuard() {

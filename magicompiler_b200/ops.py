@@ -185,12 +185,13 @@ def _gemm_swiglu_setup_context(ctx, inputs, output):
 
 
 def _gemm_swiglu_backward(ctx, grad_out):
-    """dX = dH · W and dW = dH^T · X with dH = [dG | dU]; H = X · W^T is recomputed by one library GEMM."""
+    """dX = dH · W and dW = dH^T · X with dH = [dG | dU]; H = X · W^T is recomputed on the op's own tile kernels
+    (gemm_nt); the two gradient GEMMs need transposed operands and go to the library."""
     x, w = ctx.saved_tensors
     k = x.shape[-1]
     x2 = x.reshape(-1, k)
     dy2 = grad_out.reshape(-1, grad_out.shape[-1]).contiguous()
-    h = torch.matmul(x2, w.t())
+    h = torch.ops.magi_swiglu.gemm_nt(x2, w)
     dh = torch.ops.magi_swiglu.swiglu_backward_act(h, dy2)
     dx = torch.matmul(dh, w).view(x.shape) if ctx.needs_input_grad[0] else None
     dw = torch.matmul(dh.t(), x2) if ctx.needs_input_grad[1] else None

@@ -195,3 +195,26 @@ def test_mlp_with_own_down_projection():
     got = mb.TensorParallelSwiGLUMLP(w, wd, chunks=2, down_fn=mb.gemm_nt)(x)
     ref = reference_mlp(x, w, wd)
     assert torch.allclose(got.float(), ref.float(), rtol=2e-2, atol=2e-2 * ref.float().abs().max().item())
+
+
+def test_call_from_a_fresh_thread():
+    """A thread that has never touched CUDA (like an autograd worker) can call the op: the library binds the
+    device's context itself before encoding tensor maps."""
+    import threading
+
+    x, w = _inputs(M=200)
+    expect = mb.gemm_swiglu(x, w)
+    out = {}
+
+    def work():
+        try:
+            out["y"] = mb.gemm_swiglu_out(x, w)
+        except Exception as exc:  # surfaced in the main thread below
+            out["err"] = exc
+
+    t = threading.Thread(target=work)
+    t.start()
+    t.join()
+    torch.cuda.synchronize()
+    assert "err" not in out, out.get("err")
+    assert torch.equal(out["y"], expect)

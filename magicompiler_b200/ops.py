@@ -20,6 +20,8 @@ the output is bf16 on that device.  There is no fp16/fp32 path, no CPU path and 
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _loader
@@ -77,36 +79,53 @@ def _workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
     return ws
 
 
+_ws_need: dict[tuple, int] = {}  # (M, N, K, schedule knobs, device) -> scratch bytes the preferred schedule wants
+
+
+def _raw_stream(device_index: int) -> int:
+    return torch._C._cuda_getCurrentRawStream(device_index)
+
+
 def gemm_swiglu_out(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor | None = None, *,
                     variant: str | int = "auto", block_n: int = 0, stages: int = 0, group_m: int = 0,
                     max_ctas: int = 0) -> torch.Tensor:
-    """The op's body with the schedule knobs of ``magi_swiglu_forward_bf16_ex`` exposed (tests, tuning)."""
+    """The op's body with the schedule knobs of ``magi_swiglu_forward_bf16_ws`` exposed (tests, tuning).
+
+    The host path is kept short (decode-sized calls finish on the GPU in 20-30 us): contiguous operands skip the
+    re-striding helper and the scratch size of a shape is asked from the library once."""
     M, N, K = _check(x, w_gate_up)
     lib = _loader.load_library()
-    x2 = _rows_view(x, K)
-    w2 = _rows_view(w_gate_up, K)
-    if w2.data_ptr() != w_gate_up.data_ptr() and w_gate_up.numel() > 0:
-        # a copy of the weight on every call would double the op's HBM traffic
-        raise ValueError("w_gate_up must have unit inner stride, a row stride that is a multiple of 8 and a "
-                         "16-byte-aligned base; pack it once with magicompiler_b200.pack_gate_up")
-    out_shape = (*x.shape[:-1], N)
+    x2 = x if (x.dim() == 2 and x.is_contiguous() and x.data_ptr() % 16 == 0) else _rows_view(x, K)
+    if w_gate_up.is_contiguous() and w_gate_up.data_ptr() % 16 == 0:
+        w2 = w_gate_up
+    else:
+        w2 = _rows_view(w_gate_up, K)
+        if w2.data_ptr() != w_gate_up.data_ptr() and w_gate_up.numel() > 0:
+            # a copy of the weight on every call would double the op's HBM traffic
+            raise ValueError("w_gate_up must have unit inner stride, a row stride that is a multiple of 8 and a "
+                             "16-byte-aligned base; pack it once with magicompiler_b200.pack_gate_up")
     if out is None:
         y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     else:
+        out_shape = (*x.shape[:-1], N)
         if out.dtype != torch.bfloat16 or out.device != x.device or tuple(out.shape) != tuple(out_shape):
             raise ValueError("out must be a bf16 tensor of the output shape on x's device")
         y = out.reshape(M, N)
         if y.data_ptr() != out.data_ptr() or y.stride(1) != 1 or y.stride(0) % 8 != 0 or y.data_ptr() % 16 != 0:
             raise ValueError("out must be row-contiguous with a 16-byte-aligned base")
     if M == 0:
-        return y.view(out_shape)
+        return y.view(*x.shape[:-1], N)
     v = _loader.VARIANTS[variant] if isinstance(variant, str) else int(variant)
     dev = x.device.index if x.device.index is not None else torch.cuda.current_device()
-    stream = torch.cuda.current_stream(x.device).cuda_stream
+    stream = _raw_stream(dev)
     ldx = x2.stride(0) if M > 1 else K
     ws_ptr, ws_len = None, 0
     if M <= 128:  # only the small-M schedules ever split K
-        need = lib.magi_swiglu_workspace_bytes(M, N, K, v, block_n, stages, group_m, max_ctas, dev, 0)
+        key = (M, N, K, v, block_n, stages, group_m, max_ctas, dev, _split_env())
+        need = _ws_need.get(key)
+        if need is None:
+            need = lib.magi_swiglu_workspace_bytes(M, N, K, v, block_n, stages, group_m, max_ctas, dev, 0)
+            _ws_need[key] = need
         if need > 0:
             ws = _workspace(x.device, stream, need)
             ws_ptr, ws_len = ws.data_ptr(), ws.numel()
@@ -116,7 +135,11 @@ def gemm_swiglu_out(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor 
     if rc != 0:
         msg = f"magi_swiglu_forward_bf16 failed ({rc}): {_loader.last_error()}"
         raise (ValueError(msg) if rc < 0 else RuntimeError(msg))
-    return y.view(out_shape)
+    return y if x.dim() == 2 else y.view(*x.shape[:-1], N)
+
+
+def _split_env() -> str | None:
+    return os.environ.get("MAGI_SWIGLU_K_SPLITS")  # tuning aid of the library; part of the cache key
 
 
 GEMM_NT_OP_NAME = "magi_swiglu::gemm_nt"

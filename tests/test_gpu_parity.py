@@ -302,3 +302,17 @@ def test_random_shapes_all_schedules():
             checked += 1
         assert torch.equal(outs["mma"], outs["mma2"]), (M, N, K)
     assert checked >= 150
+
+
+@pytest.mark.parametrize("shape", [(262144, 1024, 256), (256, 65536, 64), (100000, 264, 72), (3, 131072, 128)])
+def test_extreme_aspect_ratios(shape):
+    """Very tall, very wide and very thin problems: index arithmetic, raster bands and tails at their limits."""
+    M, N, K = shape
+    g = torch.Generator(device="cuda").manual_seed(M % 1000)
+    xd = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    wd = (torch.randn(2 * N, K, generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+    y = mb.gemm_swiglu(xd, wd)
+    rows = torch.unique(torch.cat([torch.arange(0, min(M, 64)), torch.arange(max(0, M - 300), M),
+                                   torch.randint(0, M, (256,))])).cuda()
+    assert_parity(y[rows], gold_fp32_gpu(xd[rows], wd), f"{shape}")
+    assert mb.device_status(0)["code"] == 0

@@ -120,6 +120,22 @@ int magi_swiglu_forward_bf16_static(const void* x, const void* w_gate_up, void* 
                                     int64_t ldx, int64_t ldw, int64_t ldy,
                                     int device, void* cuda_stream);
 
+/* Row scales of an RMSNorm: out[m] = rsqrt(mean_k x[m,k]^2 + eps) in fp32 (x bf16 [M,K], K % 8 == 0).
+ * Replaces: the variance/rsqrt part of RMSNorm.forward, tests/model_definition.py:53-54. */
+int magi_swiglu_row_rms_f32(const void* x, float* out, int64_t M, int64_t K, int64_t ldx, float eps,
+                            int device, void* cuda_stream);
+
+/* The fused op with a per-row scale applied to both accumulators before the activation:
+ *   y[m, n] = silu(s_m · x_m·Wg[n]) * (s_m · x_m·Wu[n]),   s = row_scale [M] fp32.
+ * With s from magi_swiglu_row_rms_f32 and the norm weight folded into W's columns this is RMSNorm followed by the
+ * SwiGLU projection without the normalised activations ever being written.  Same requirements and workspace rules as
+ * magi_swiglu_forward_bf16_ws (workspace may be NULL).
+ * Replaces: x = self.post_attention_layernorm(x) feeding self.mlp(x), tests/model_definition.py:360-361, gate/up part. */
+int magi_swiglu_forward_bf16_scaled(const void* x, const void* w_gate_up, void* y, const float* row_scale,
+                                    int64_t M, int64_t N, int64_t K,
+                                    int64_t ldx, int64_t ldw, int64_t ldy,
+                                    int device, void* cuda_stream, void* workspace, int64_t workspace_bytes);
+
 /* Plain bf16 GEMM on the same tile kernels: C[M,N] = A[M,K] · B[N,K]^T (both operands row-major with the reduction
  * dimension contiguous, i.e. y = F.linear(a, b)), fp32 accumulation, one rounding.  N % 16 == 0, K % 8 == 0, strides
  * multiples of 8, 16-byte aligned pointers.  Used for the row-parallel down projection of the MLP block.

@@ -79,6 +79,8 @@ struct KArgs {
                       // the tile is handed back to the MMA issuer before the high half has been drained
   int acc_bufs;       // tensor-memory accumulator buffers (2 = epilogue overlaps next tile)
   int wide_store;     // y base and row pitch are 32-byte aligned: 256-bit stores (one full sector per thread)
+  const float* row_scale;  // optional [M] fp32: accumulators of row m are multiplied by row_scale[m] before the
+                           // epilogue (a fused RMSNorm: 1/rms(x_m), the norm weight being folded into W); null = none
   int plain;          // 1: plain GEMM C = A·B^T; B's first N rows fill output columns [0,N), its last N rows [N,2N)
   int x_hint, w_hint, y_hint;  // L2 eviction priority of X tiles, W tiles and Y stores: 0 normal, 1 first, 2 last
   // Split-K (STREAM schedule on narrow weights): k_splits CTAs share one tile, each sums kb_per_split K-steps and
@@ -445,6 +447,7 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       const uint32_t t_tile = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * acc_cols);
       __nv_bfloat16* yrow_tile = a.y + (long long)row * a.ldy + col0;
       const bool wide = a.wide_store != 0;  // every 16-column group of every row starts on a 32-byte boundary
+      const float row_scale_m = (a.row_scale != nullptr && row_ok) ? __ldg(a.row_scale + row) : 1.0f;
 
       if (kCtas == 1 && a.k_splits > 1) {
         // ---- split-K: park this CTA's fp32 partial sums; swiglu_splitk_reduce_kernel finishes the tile
@@ -515,8 +518,15 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
             tmem_ld_x16_into32(t_up + c, u);
           }
         };
-        auto process = [&](const uint32_t (&g)[32], const uint32_t (&u)[32], int c, int w) {
+        auto process = [&](uint32_t (&g)[32], uint32_t (&u)[32], int c, int w) {
           if (!row_ok) return;
+          if (a.row_scale != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              g[j] = __float_as_uint(__uint_as_float(g[j]) * row_scale_m);
+              u[j] = __float_as_uint(__uint_as_float(u[j]) * row_scale_m);
+            }
+          }
           if (a.plain) {  // plain GEMM: the "gate" accumulator is output column n, the "up" accumulator column N + n
             if (w == 32) {
               store_cols_plain<32>(yrow + c, g, valid - c, wide, y_policy);
@@ -590,7 +600,7 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
 // split order (bit-identical from run to run).  One thread per 8 output columns, coalesced along a row.
 __global__ void __launch_bounds__(256)
 swiglu_splitk_reduce_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ y, int M, int N, long long ldy,
-                            int block_n, int num_n_tiles, int k_splits) {
+                            int block_n, int num_n_tiles, int k_splits, const float* __restrict__ row_scale) {
   const int groups = block_n / 8;
   const long long total = (long long)num_n_tiles * M * groups;
   const uint64_t policy = l2_policy_evict_first();
@@ -611,13 +621,39 @@ swiglu_splitk_reduce_kernel(const float* __restrict__ ws, __nv_bfloat16* __restr
       g[0] += g0.x; g[1] += g0.y; g[2] += g0.z; g[3] += g0.w; g[4] += g1.x; g[5] += g1.y; g[6] += g1.z; g[7] += g1.w;
       u[0] += u0.x; u[1] += u0.y; u[2] += u0.z; u[3] += u0.w; u[4] += u1.x; u[5] += u1.y; u[6] += u1.z; u[7] += u1.w;
     }
+    const float rs = row_scale != nullptr ? __ldg(row_scale + row) : 1.0f;
     uint32_t gb[8], ub[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      gb[j] = __float_as_uint(g[j]);
-      ub[j] = __float_as_uint(u[j]);
+      gb[j] = __float_as_uint(g[j] * rs);
+      ub[j] = __float_as_uint(u[j] * rs);
     }
     st_global_v4_hint(y + (long long)row * ldy + col, swiglu_pack8(gb, ub), policy);
+  }
+}
+
+// Row scales of a fused RMSNorm: out[m] = rsqrt(mean_k x[m,k]^2 + eps), one warp per row, fp32 sums, 16-byte loads.
+__global__ void __launch_bounds__(256)
+swiglu_row_rms_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, int M, int K, long long ldx,
+                      float eps) {
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < M; row += warps) {
+    const __nv_bfloat16* xr = x + (long long)row * ldx;
+    float acc = 0.f;
+    for (int k = lane * 8; k < K; k += 256) {  // K % 8 == 0
+      const uint4 v = *reinterpret_cast<const uint4*>(xr + k);
+      const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(v2[j]);
+        acc = fmaf(f.x, f.x, acc);
+        acc = fmaf(f.y, f.y, acc);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) out[row] = rsqrtf(acc / (float)K + eps);
   }
 }
 

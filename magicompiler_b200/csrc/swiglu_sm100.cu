@@ -109,7 +109,8 @@ struct DeviceGuard {
 
 static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int64_t ldx,
                         int64_t ldw, int64_t ldy, int device, void* stream_v, int variant, int block_n, int stages,
-                        int group_m, int max_ctas, void* workspace, int64_t workspace_bytes, int plain = 0) {
+                        int group_m, int max_ctas, void* workspace, int64_t workspace_bytes, int plain = 0,
+                        const float* row_scale = nullptr) {
   g_err[0] = 0;
   if (M == 0 && N > 0 && K > 0) return 0;
   if (!x || !w || !y) return fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
@@ -203,6 +204,7 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   a.acc_bufs = p.acc_bufs;
   a.wide_store = (((uintptr_t)y & 31u) == 0 && ldy % 16 == 0 && (!plain || N % 16 == 0)) ? 1 : 0;
   a.plain = plain;
+  a.row_scale = row_scale;
   a.k_splits = p.k_splits;
   a.kb_per_split = p.kb_per_split;
   a.ws = p.k_splits > 1 ? static_cast<float*>(workspace) : nullptr;
@@ -239,7 +241,7 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
       rc_cfg.attrs = rc_attr;
       rc_cfg.numAttrs = 1;
       e = cudaLaunchKernelEx(&rc_cfg, swiglu_splitk_reduce_kernel, (const float*)a.ws, a.y, a.M, a.N, a.ldy, p.block_n,
-                             p.num_n_tiles, p.k_splits);
+                             p.num_n_tiles, p.k_splits, row_scale);
       if (e != cudaSuccess) return fail_cuda(e, "launch of swiglu_splitk_reduce_kernel");
     }
     return 0;
@@ -345,6 +347,39 @@ int magi_swiglu_forward_bf16_static(const void* x, const void* w_gate_up, void* 
   }
   return magi::forward_impl(x, w_gate_up, y, M, N, K, ldx, ldw, ldy, device, cuda_stream, MAGI_SWIGLU_VARIANT_AUTO, 0, 0,
                             0, 0, scratch, magi::kStaticScratchBytes);
+}
+
+int magi_swiglu_row_rms_f32(const void* x, float* out, int64_t M, int64_t K, int64_t ldx, float eps, int device,
+                            void* cuda_stream) {
+  magi::g_err[0] = 0;
+  if (M == 0 && K > 0) return 0;
+  if (!x || !out) return magi::fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
+  if (M < 0 || K <= 0 || K % 8 != 0 || M > 0x7fffff00LL || K > 0x7fffff00LL || ldx < K || ldx % 8 != 0)
+    return magi::fail(MAGI_SWIGLU_ERR_SHAPE, "bad shape M=%lld K=%lld ldx=%lld (K and ldx multiples of 8)", (long long)M,
+                      (long long)K, (long long)ldx);
+  if (((uintptr_t)x & 15u) || ((uintptr_t)out & 3u)) return magi::fail(MAGI_SWIGLU_ERR_ALIGN, "x must be 16-byte aligned");
+  const magi::DeviceInfo* di = magi::device_info(device);
+  if (!di) return magi::fail(MAGI_SWIGLU_ERR_DEVICE, "device %d is not available", device);
+  magi::DeviceGuard guard;
+  cudaError_t e = guard.set(device);
+  if (e != cudaSuccess) return magi::fail_cuda(e, "cudaSetDevice");
+  const long long want = (M + 7) / 8;  // eight rows (warps) per block
+  const int blocks = (int)(want < 32LL * di->sm_count ? want : 32LL * di->sm_count);
+  magi::swiglu_row_rms_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), out, (int)M, (int)K, ldx, eps);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : magi::fail_cuda(e, "launch of swiglu_row_rms_kernel");
+}
+
+int magi_swiglu_forward_bf16_scaled(const void* x, const void* w_gate_up, void* y, const float* row_scale, int64_t M,
+                                    int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldy, int device,
+                                    void* cuda_stream, void* workspace, int64_t workspace_bytes) {
+  if (M > 0 && !row_scale) {
+    magi::g_err[0] = 0;
+    return magi::fail(MAGI_SWIGLU_ERR_NULL, "row_scale is null");
+  }
+  return magi::forward_impl(x, w_gate_up, y, M, N, K, ldx, ldw, ldy, device, cuda_stream, MAGI_SWIGLU_VARIANT_AUTO, 0, 0,
+                            0, 0, workspace, workspace_bytes, 0, row_scale);
 }
 
 int magi_swiglu_gemm_nt_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,

@@ -142,6 +142,54 @@ def _split_env() -> str | None:
     return os.environ.get("MAGI_SWIGLU_K_SPLITS")  # tuning aid of the library; part of the cache key
 
 
+RMS_OP_NAME = "magi_swiglu::rmsnorm_gemm_swiglu"
+
+
+def fold_rmsnorm_weight(w_gate_up: torch.Tensor, norm_weight: torch.Tensor) -> torch.Tensor:
+    """Fold an RMSNorm weight (``[K]``) into the packed gate/up weight (``[2N, K]``): ``W'[n, k] = W[n, k] * g[k]``
+    (computed in fp32, rounded once).  Do this once at load; ``rmsnorm_gemm_swiglu`` then needs only the row scales."""
+    if norm_weight.dim() != 1 or norm_weight.shape[0] != w_gate_up.shape[1]:
+        raise ValueError(f"norm weight {tuple(norm_weight.shape)} does not match K={w_gate_up.shape[1]}")
+    return (w_gate_up.float() * norm_weight.float().to(w_gate_up.device)).to(w_gate_up.dtype).contiguous()
+
+
+@magi_register_custom_op(name=RMS_OP_NAME, mutates_args=(),
+                         infer_output_meta_fn=lambda x, w_folded, eps: x.new_empty((*x.shape[:-1], w_folded.shape[0] // 2)),
+                         is_compute_sensitive=True, is_subgraph_boundary=True)
+def rmsnorm_gemm_swiglu(x: torch.Tensor, w_folded: torch.Tensor, eps: float) -> torch.Tensor:
+    """``gemm_swiglu(rmsnorm(x), w)`` in two launches and without materialising the normalised activations:
+    a row-scale kernel computes ``rsqrt(mean(x^2) + eps)`` and the fused kernel multiplies both accumulators of a
+    row by it before the activation.  ``w_folded`` = ``fold_rmsnorm_weight(w_gate_up, norm.weight)``.
+    Replaces ``self.mlp(self.post_attention_layernorm(x))`` up to the down projection
+    (MagiCompiler tests/model_definition.py:42-56, 360-361)."""
+    M, N, K = _check(x, w_folded)
+    lib = _loader.load_library()
+    x2 = x if (x.dim() == 2 and x.is_contiguous() and x.data_ptr() % 16 == 0) else _rows_view(x, K)
+    if not w_folded.is_contiguous() or w_folded.data_ptr() % 16:
+        raise ValueError("w_folded must be contiguous and 16-byte aligned")
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    if M == 0:
+        return y.view(*x.shape[:-1], N)
+    dev = x.device.index if x.device.index is not None else torch.cuda.current_device()
+    stream = _raw_stream(dev)
+    scale = torch.empty((M,), dtype=torch.float32, device=x.device)
+    ldx = x2.stride(0) if M > 1 else K
+    rc = lib.magi_swiglu_row_rms_f32(x2.data_ptr(), scale.data_ptr(), M, K, ldx, float(eps), dev, stream)
+    if rc == 0:
+        ws_ptr, ws_len = None, 0
+        if M <= 128:
+            need = lib.magi_swiglu_workspace_bytes(M, N, K, 0, 0, 0, 0, 0, dev, 0)
+            if need > 0:
+                ws = _workspace(x.device, stream, need)
+                ws_ptr, ws_len = ws.data_ptr(), ws.numel()
+        rc = lib.magi_swiglu_forward_bf16_scaled(x2.data_ptr(), w_folded.data_ptr(), y.data_ptr(), scale.data_ptr(), M, N,
+                                                 K, ldx, K, N, dev, stream, ws_ptr, ws_len)
+    if rc != 0:
+        msg = f"rmsnorm_gemm_swiglu failed ({rc}): {_loader.last_error()}"
+        raise (ValueError(msg) if rc < 0 else RuntimeError(msg))
+    return y if x.dim() == 2 else y.view(*x.shape[:-1], N)
+
+
 GEMM_NT_OP_NAME = "magi_swiglu::gemm_nt"
 
 

@@ -18,6 +18,8 @@ from .swiglu_oracle import (  # noqa: F401
     build,
     error_metrics,
     make_inputs,
+    rmsnorm_swiglu_gold,
+    rmsnorm_swiglu_ref_eager,
     swiglu_backward_gold,
     swiglu_gold,
     swiglu_gold_numpy,

@@ -141,3 +141,21 @@ def swiglu_backward_gold(x: torch.Tensor, w: torch.Tensor, dy: torch.Tensor):
     du = dyf * g * s
     dh = torch.cat([dg, du], dim=1)
     return dh @ wf, dh.t() @ xf
+
+
+def rmsnorm_swiglu_gold(x: torch.Tensor, norm_weight: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    """fp32 gold of RMSNorm followed by the SwiGLU projection, nothing rounded in between:
+    MagiCompiler's RMSNorm.forward (tests/model_definition.py:51-56) feeding TransformerMLP's gate/up part (:337-339)."""
+    n = w.shape[0] // 2
+    xf = x.float()
+    xn = xf * torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + eps) * norm_weight.float()
+    h = xn @ w.float().t()
+    return F.silu(h[:, :n]) * h[:, n:]
+
+
+def rmsnorm_swiglu_ref_eager(x: torch.Tensor, norm_weight: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    """The reference's eager chain, literally: RMSNorm.forward (fp32 inside, bf16 out), then the eager SwiGLU."""
+    variance = x.to(torch.float32).pow(2).mean(dim=-1, keepdim=True)
+    xn = x * torch.rsqrt(variance + eps)
+    xn = (xn.to(norm_weight.dtype) * norm_weight).to(x.dtype)
+    return swiglu_ref_eager(xn, w)

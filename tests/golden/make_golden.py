@@ -51,10 +51,10 @@ def import_reference(ref_root: Path):
     sys.path.insert(0, str(ref_root))
     argv, sys.argv = sys.argv, sys.argv[:1]  # the reference's config object parses sys.argv
     try:
-        from tests.model_definition import TransformerConfig, TransformerMLP
+        from tests.model_definition import RMSNorm, TransformerConfig, TransformerMLP
     finally:
         sys.argv = argv
-    return TransformerConfig, TransformerMLP
+    return TransformerConfig, TransformerMLP, RMSNorm
 
 
 def main():
@@ -64,7 +64,7 @@ def main():
     args = ap.parse_args()
     from oracle import make_inputs, to_bits
 
-    TransformerConfig, TransformerMLP = import_reference(Path(args.reference))
+    TransformerConfig, TransformerMLP, RMSNorm = import_reference(Path(args.reference))
     torch.set_num_threads(min(os.cpu_count() or 1, 8))
     out = {}
     for name, M, K, N, seed, store_inputs, row_step in CASES:
@@ -86,6 +86,28 @@ def main():
             out[f"{name}/x"] = to_bits(x)
             out[f"{name}/w"] = to_bits(w)
         print(name, "ok", y.float().abs().max().item())
+    # RMSNorm feeding the MLP's gate/up part, as in the reference's TransformerBlock.forward (lines 360-361)
+    name, M, K, N, seed, eps = "rms_96x256x136", 96, 256, 136, 4, 1e-6
+    x, w = make_inputs(M, K, N, seed=seed)
+    gamma = 1.0 + 0.1 * torch.randn(K, generator=torch.Generator().manual_seed(seed))
+    norm = RMSNorm(K, eps=eps)
+    cfg = TransformerConfig(vocab_size=8, hidden_size=K, intermediate_size=N, num_hidden_layers=1,
+                            num_attention_heads=1, num_key_value_heads=1, max_position_embeddings=8,
+                            params_dtype=torch.bfloat16)
+    mlp = TransformerMLP(cfg)
+    with torch.no_grad():
+        norm.weight.copy_(gamma)
+        mlp.gate_proj.weight.copy_(w[:N])
+        mlp.up_proj.weight.copy_(w[N:])
+        xn = norm(x).to(torch.bfloat16)
+        y = F.silu(mlp.gate_proj(xn)) * mlp.up_proj(xn)
+    out[f"{name}/shape"] = np.array([M, K, N, seed, 1], dtype=np.int64)
+    out[f"{name}/y_eager"] = to_bits(y)
+    out[f"{name}/x"] = to_bits(x)
+    out[f"{name}/w"] = to_bits(w)
+    out[f"{name}/gamma"] = gamma.numpy()
+    out[f"{name}/eps"] = np.array([eps])
+    print(name, "ok", y.float().abs().max().item())
     np.savez_compressed(HERE / "swiglu_reference_eager.npz", **out)
     print("wrote", HERE / "swiglu_reference_eager.npz", (HERE / "swiglu_reference_eager.npz").stat().st_size, "bytes")
 

@@ -218,3 +218,43 @@ def test_call_from_a_fresh_thread():
     torch.cuda.synchronize()
     assert "err" not in out, out.get("err")
     assert torch.equal(out["y"], expect)
+
+
+# ---------------------------------------------------------------- RMSNorm fused in front of the op
+def test_rmsnorm_fused_against_reference_fixture(golden):
+    from oracle import error_metrics, from_bits, rmsnorm_swiglu_gold
+
+    name = "rms_96x256x136"
+    x, w = from_bits(golden[name + "/x"]), from_bits(golden[name + "/w"])
+    gamma = torch.from_numpy(golden[name + "/gamma"])
+    eps = float(golden[name + "/eps"][0])
+    wf = mb.fold_rmsnorm_weight(w.cuda(), gamma)
+    y = mb.rmsnorm_gemm_swiglu(x.cuda(), wf, eps)
+    ref = from_bits(golden[name + "/y_eager"]).float()  # what the reference's RMSNorm + TransformerMLP produced
+    m = error_metrics(y, ref)
+    assert m["max_norm"] <= 1e-2 and m["frob"] <= 5e-3, m
+    m = error_metrics(y, rmsnorm_swiglu_gold(x, gamma, w, eps))
+    assert m["max_norm"] <= 1e-2 and m["frob"] <= 5e-3, m
+
+
+@pytest.mark.parametrize("shape", [(16, 3584, 2048), (128, 264, 520), (300, 528, 328), (4096, 2048, 1024)])
+def test_rmsnorm_fused_shapes(shape):
+    """Every schedule (split-K reduce, streaming, CTA pairs) applies the row scale; compared with the fp32 gold and
+    with the reference's eager chain on the GPU."""
+    from oracle import error_metrics, rmsnorm_swiglu_gold, rmsnorm_swiglu_ref_eager
+
+    M, N, K = shape
+    x, w = make_inputs(M, K, N, seed=N)
+    x = (x.float() * 3.0 + 0.5).to(torch.bfloat16)  # rows whose rms is far from 1
+    gamma = 1.0 + 0.2 * torch.randn(K, generator=torch.Generator().manual_seed(1))
+    eps = 1e-6
+    xd, wd = x.cuda(), w.cuda()
+    y = mb.rmsnorm_gemm_swiglu(xd, mb.fold_rmsnorm_weight(wd, gamma), eps)
+    gold = rmsnorm_swiglu_gold(xd, gamma.cuda(), wd, eps)
+    m = error_metrics(y, gold)
+    assert y.shape == (M, N) and m["max_norm"] <= 1e-2 and m["frob"] <= 5e-3, m
+    mref = error_metrics(rmsnorm_swiglu_ref_eager(xd, gamma.cuda(), wd, eps), gold)
+    assert m["frob"] <= mref["frob"] * 1.2 + 1e-4, (m, mref)
+    # the plain op on pre-normalised activations is the same computation up to the rounding of x_norm
+    with pytest.raises(ValueError):
+        mb.fold_rmsnorm_weight(wd, gamma[:-8])

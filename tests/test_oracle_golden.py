@@ -95,3 +95,19 @@ def test_oracle_edge_cases():
     wb = torch.cat([torch.full((8, 16), -100.0), torch.ones(8, 16)]).to(torch.bfloat16)
     o = swiglu_gold(xb, wb)
     assert torch.isfinite(o["gold"]).all() and (o["gold"].abs() == 0).all()
+
+
+def test_rmsnorm_oracle_matches_reference_fixture(golden):
+    """RMSNorm -> gate/up SwiGLU: the oracle's restatement of the reference's eager chain reproduces what the
+    reference's RMSNorm and TransformerMLP modules produced, and the fp32 gold sits within the path's tolerance."""
+    from oracle import rmsnorm_swiglu_gold, rmsnorm_swiglu_ref_eager
+
+    name = "rms_96x256x136"
+    x, w = from_bits(golden[name + "/x"]), from_bits(golden[name + "/w"])
+    gamma = torch.from_numpy(golden[name + "/gamma"])
+    eps = float(golden[name + "/eps"][0])
+    ref = from_bits(golden[name + "/y_eager"])
+    got = rmsnorm_swiglu_ref_eager(x, gamma, w, eps)
+    assert float((to_bits(got) != to_bits(ref)).mean()) <= 1e-3
+    m = error_metrics(ref, rmsnorm_swiglu_gold(x, gamma, w, eps))
+    assert m["max_norm"] <= TOL_MAX_NORM and m["frob"] <= TOL_FROB, m

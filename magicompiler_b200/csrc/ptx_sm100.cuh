@@ -230,6 +230,20 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// tcgen05.ld fills its destination registers asynchronously; they may be read only after tcgen05.wait::ld.  The
+// compiler sees the registers as outputs of the load statement, so nothing but statement order keeps it from
+// reading them early.  This empty statement, placed after the wait, claims to rewrite the registers: every later
+// use now depends on a statement that follows the wait.  It emits no instruction.
+__device__ __forceinline__ void tmem_regs_ready(uint32_t (&r)[32]) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 16)
+    asm volatile("" : "+r"(r[i]), "+r"(r[i + 1]), "+r"(r[i + 2]), "+r"(r[i + 3]), "+r"(r[i + 4]), "+r"(r[i + 5]),
+                      "+r"(r[i + 6]), "+r"(r[i + 7]), "+r"(r[i + 8]), "+r"(r[i + 9]), "+r"(r[i + 10]), "+r"(r[i + 11]),
+                      "+r"(r[i + 12]), "+r"(r[i + 13]), "+r"(r[i + 14]), "+r"(r[i + 15])
+                 :
+                 : "memory");
+}
+
 // Lane l of the warp receives 16 consecutive fp32 columns of tensor-memory lane (base lane + l).
 __device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(

@@ -467,6 +467,8 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
             tmem_ld_x16_into32(t_tile + a.block_n + c, u);
           }
           tmem_ld_wait();
+          tmem_regs_ready(g);
+          tmem_regs_ready(u);
           if (!chunk_w(c + 64)) {  // last read of the accumulator: hand it back before the stores
             tc_fence_before_sync();
             __syncwarp();
@@ -560,6 +562,8 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         while (w) {
           load(g, u, c, w);
           tmem_ld_wait();
+          tmem_regs_ready(g);
+          tmem_regs_ready(u);
           const int c2 = c + 64, w2 = width_at(c2);
           if (!w2) {  // that was this warp's last read of the segment
             release();

@@ -271,6 +271,7 @@ def main():
     ap.add_argument("--down", default="own", choices=["own", "library"], help="mlp_block: kernel of the down projection")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-incumbents", action="store_true", help="skip timing eager CUDA and the library GEMM")
     ap.add_argument("--no-flush", action="store_true", help="profiling runs only: skip the L2 flush kernels")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" and not args.no_flush else args.warmup
@@ -456,6 +457,36 @@ def main():
         line["e2e"] = {"value": e2e_scale / (ms * 1e-3) / (1e9 if bound == "hbm" else 1e12), "unit": unit,
                        "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms,
                        "how": f"pinned X -> device, op, Y -> pinned host, {chunks} row chunk(s) pipelined on side streams"}
+    if world == 1 and not args.no_incumbents:
+        # the paths this op replaces on the same GPU, timed the same way (L2 flush, CUDA events, median of 10):
+        # the reference's eager expression (two library GEMMs + silu + mul) and one library GEMM [M,K]x[K,2N] alone
+        import torch.nn.functional as F
+
+        def timed(fn):
+            for _ in range(3):
+                fn()
+            ts = []
+            for _ in range(10):
+                if not args.no_flush:
+                    flush_l2()
+                s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s0.record()
+                fn()
+                s1.record()
+                torch.cuda.synchronize(dev)
+                ts.append(s0.elapsed_time(s1))
+            return statistics.median(ts)
+
+        def as_metric(ms):
+            return (nbytes if bound == "hbm" else flops) / (ms * 1e-3) / (1e9 if bound == "hbm" else 1e12)
+
+        t_eager = timed(lambda: F.silu(F.linear(x, w[:N])) * F.linear(x, w[N:]))
+        t_gemm = timed(lambda: F.linear(x, w))
+        line["incumbents"] = {
+            "eager_cuda": {"ms": t_eager, "value": as_metric(t_eager), "unit": unit,
+                           "what": "F.silu(F.linear(x,Wg))*F.linear(x,Wu): 2 library GEMMs + 2 element-wise kernels"},
+            "library_gemm_only": {"ms": t_gemm, "value": as_metric(t_gemm), "unit": unit,
+                                  "what": "F.linear(x, W[2N,K]) alone, no activation"}}
     if world == 1 and not args.no_cpu_baseline:
         v, rows, threads, t, reps = cpu_eager_tflops(M, K, N, x_cpu, w_cpu)
         if bound == "hbm":

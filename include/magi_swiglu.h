@@ -136,6 +136,16 @@ int magi_swiglu_forward_bf16_scaled(const void* x, const void* w_gate_up, void* 
                                     int64_t ldx, int64_t ldw, int64_t ldy,
                                     int device, void* cuda_stream, void* workspace, int64_t workspace_bytes);
 
+/* The fused op with a statically scaled fp8 (e4m3, saturating) output: y[m,n] = fp8(silu(g)*u / *scale), one byte per
+ * element, row stride ldy in bytes.  `scale` points to ONE fp32 value in device memory (it is read by the kernel, not
+ * by the host).  N % 16 == 0, ldy % 16 == 0; other requirements as magi_swiglu_forward_bf16.
+ * Replaces: the merged gate/up linear followed by vLLM's silu_and_mul_quant(result, input, scale), the quantising
+ * activation op the reference's de-functionalisation pass handles (passes/piecewise_graph/fix_functionalization.py:110-112). */
+int magi_swiglu_forward_fp8_e4m3(const void* x, const void* w_gate_up, void* y_fp8, const float* scale,
+                                 int64_t M, int64_t N, int64_t K,
+                                 int64_t ldx, int64_t ldw, int64_t ldy,
+                                 int device, void* cuda_stream);
+
 /* Plain bf16 GEMM on the same tile kernels: C[M,N] = A[M,K] · B[N,K]^T (both operands row-major with the reduction
  * dimension contiguous, i.e. y = F.linear(a, b)), fp32 accumulation, one rounding.  N % 16 == 0, K % 8 == 0, strides
  * multiples of 8, 16-byte aligned pointers.  Used for the row-parallel down projection of the MLP block.

@@ -81,6 +81,7 @@ struct KArgs {
   int wide_store;     // y base and row pitch are 32-byte aligned: 256-bit stores (one full sector per thread)
   const float* row_scale;  // optional [M] fp32: accumulators of row m are multiplied by row_scale[m] before the
                            // epilogue (a fused RMSNorm: 1/rms(x_m), the norm weight being folded into W); null = none
+  const float* out_scale;  // non-null: Y is fp8 e4m3 (one byte per element), y = sat(silu(g)*u / *out_scale)
   int plain;          // 1: plain GEMM C = A·B^T; B's first N rows fill output columns [0,N), its last N rows [N,2N)
   int x_hint, w_hint, y_hint;  // L2 eviction priority of X tiles, W tiles and Y stores: 0 normal, 1 first, 2 last
   // Split-K (STREAM schedule on narrow weights): k_splits CTAs share one tile, each sums kb_per_split K-steps and
@@ -181,6 +182,31 @@ __device__ __forceinline__ void store_cols_plain(__nv_bfloat16* dst, const uint3
       }
     } else if (16 * j + 8 <= cols_valid) {
       st_global_v4_hint(dst + 16 * j, plain_pack8(v + 16 * j), policy);
+    }
+  }
+}
+
+// fp8 (e4m3, saturating) output: kCols consecutive outputs of one row, 16 per 16-byte store; N % 16 == 0.
+template <int kCols>
+__device__ __forceinline__ void store_cols_fp8(uint8_t* dst, const uint32_t* g, const uint32_t* u, int cols_valid,
+                                               float inv_scale, uint64_t policy) {
+#pragma unroll
+  for (int j = 0; j < kCols / 16; ++j) {
+    if (16 * j + 16 <= cols_valid) {
+      uint32_t w4[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int i = 16 * j + 4 * q;
+        const float v0 = silu_mul(__uint_as_float(g[i]), __uint_as_float(u[i])) * inv_scale;
+        const float v1 = silu_mul(__uint_as_float(g[i + 1]), __uint_as_float(u[i + 1])) * inv_scale;
+        const float v2 = silu_mul(__uint_as_float(g[i + 2]), __uint_as_float(u[i + 2])) * inv_scale;
+        const float v3 = silu_mul(__uint_as_float(g[i + 3]), __uint_as_float(u[i + 3])) * inv_scale;
+        uint16_t lo, hi;  // cvt packs its first source into the upper byte
+        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(v1), "f"(v0));
+        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(v3), "f"(v2));
+        w4[q] = (uint32_t)lo | ((uint32_t)hi << 16);
+      }
+      st_global_v4_hint(dst + 16 * j, make_uint4(w4[0], w4[1], w4[2], w4[3]), policy);
     }
   }
 }
@@ -448,6 +474,7 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       __nv_bfloat16* yrow_tile = a.y + (long long)row * a.ldy + col0;
       const bool wide = a.wide_store != 0;  // every 16-column group of every row starts on a 32-byte boundary
       const float row_scale_m = (a.row_scale != nullptr && row_ok) ? __ldg(a.row_scale + row) : 1.0f;
+      const float out_inv_scale = (a.out_scale != nullptr) ? 1.0f / __ldg(a.out_scale) : 1.0f;
 
       if (kCtas == 1 && a.k_splits > 1) {
         // ---- split-K: park this CTA's fp32 partial sums; swiglu_splitk_reduce_kernel finishes the tile
@@ -529,7 +556,13 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
               u[j] = __float_as_uint(__uint_as_float(u[j]) * row_scale_m);
             }
           }
-          if (a.plain) {  // plain GEMM: the "gate" accumulator is output column n, the "up" accumulator column N + n
+          if (a.out_scale != nullptr) {  // fp8 output: one byte per element
+            uint8_t* y8 = reinterpret_cast<uint8_t*>(a.y) + (long long)row * a.ldy + col0 + seg * seg_cols + c;
+            if (w == 32)
+              store_cols_fp8<32>(y8, g, u, valid - c, out_inv_scale, y_policy);
+            else
+              store_cols_fp8<16>(y8, g, u, valid - c, out_inv_scale, y_policy);
+          } else if (a.plain) {  // plain GEMM: the "gate" accumulator is output column n, the "up" accumulator column N + n
             if (w == 32) {
               store_cols_plain<32>(yrow + c, g, valid - c, wide, y_policy);
               store_cols_plain<32>(yrow + a.N + c, u, valid - c, wide, y_policy);

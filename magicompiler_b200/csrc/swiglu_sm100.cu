@@ -110,7 +110,7 @@ struct DeviceGuard {
 static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int64_t ldx,
                         int64_t ldw, int64_t ldy, int device, void* stream_v, int variant, int block_n, int stages,
                         int group_m, int max_ctas, void* workspace, int64_t workspace_bytes, int plain = 0,
-                        const float* row_scale = nullptr) {
+                        const float* row_scale = nullptr, const float* out_scale = nullptr) {
   g_err[0] = 0;
   if (M == 0 && N > 0 && K > 0) return 0;
   if (!x || !w || !y) return fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
@@ -205,6 +205,7 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   a.wide_store = (((uintptr_t)y & 31u) == 0 && ldy % 16 == 0 && (!plain || N % 16 == 0)) ? 1 : 0;
   a.plain = plain;
   a.row_scale = row_scale;
+  a.out_scale = out_scale;
   a.k_splits = p.k_splits;
   a.kb_per_split = p.kb_per_split;
   a.ws = p.k_splits > 1 ? static_cast<float*>(workspace) : nullptr;
@@ -380,6 +381,21 @@ int magi_swiglu_forward_bf16_scaled(const void* x, const void* w_gate_up, void* 
   }
   return magi::forward_impl(x, w_gate_up, y, M, N, K, ldx, ldw, ldy, device, cuda_stream, MAGI_SWIGLU_VARIANT_AUTO, 0, 0,
                             0, 0, workspace, workspace_bytes, 0, row_scale);
+}
+
+int magi_swiglu_forward_fp8_e4m3(const void* x, const void* w_gate_up, void* y_fp8, const float* scale, int64_t M,
+                                 int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldy, int device,
+                                 void* cuda_stream) {
+  magi::g_err[0] = 0;
+  if (M > 0 && !scale) return magi::fail(MAGI_SWIGLU_ERR_NULL, "scale is null");
+  if (N % 16 != 0 || ldy % 16 != 0)
+    return magi::fail(MAGI_SWIGLU_ERR_SHAPE, "fp8 output needs N (%lld) and ldy (%lld) to be multiples of 16", (long long)N,
+                      (long long)ldy);
+  // the one-byte output row is addressed in the kernel; the bf16 checks of the common path see ldy in elements.
+  // No scratch: the split-K reduce kernel writes bf16 only, so narrow problems run unsplit here.
+  const int variant = MAGI_SWIGLU_VARIANT_AUTO;
+  return magi::forward_impl(x, w_gate_up, y_fp8, M, N, K, ldx, ldw, ldy, device, cuda_stream, variant, 0, 0, 0, 0, nullptr,
+                            0, 0, nullptr, scale);
 }
 
 int magi_swiglu_gemm_nt_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,

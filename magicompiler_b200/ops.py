@@ -250,6 +250,42 @@ def swiglu_backward_act(h: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
     return dh
 
 
+FP8_OP_NAME = "magi_swiglu::gemm_swiglu_fp8"
+
+
+def _gemm_swiglu_fp8_meta(x: torch.Tensor, w_gate_up: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    return x.new_empty((*x.shape[:-1], w_gate_up.shape[0] // 2), dtype=torch.float8_e4m3fn)
+
+
+@magi_register_custom_op(name=FP8_OP_NAME, mutates_args=(), infer_output_meta_fn=_gemm_swiglu_fp8_meta,
+                         is_compute_sensitive=True)
+def gemm_swiglu_fp8(x: torch.Tensor, w_gate_up: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """The fused op with a statically scaled fp8 output: ``(silu(g) * u / scale).to(float8_e4m3fn)``, saturating,
+    rounded once from the fp32 accumulators (``magi_swiglu_forward_fp8_e4m3``).  ``scale`` is a one-element fp32
+    CUDA tensor; the kernel reads it, the host does not.  This is the merged gate/up linear followed by vLLM's
+    ``silu_and_mul_quant(result, input, scale)``, the quantising activation the reference's de-functionalisation
+    pass handles (magi_compiler/passes/piecewise_graph/fix_functionalization.py:110-112).  N must be a multiple of
+    16.  Inference only: no autograd is registered."""
+    M, N, K = _check(x, w_gate_up)
+    if N % 16 != 0:
+        raise ValueError(f"N ({N}) must be a multiple of 16 for the fp8 output")
+    if not isinstance(scale, torch.Tensor) or scale.dtype != torch.float32 or scale.numel() != 1:
+        raise TypeError("scale must be a one-element fp32 tensor")
+    if scale.device != x.device:
+        raise ValueError(f"scale is on {scale.device} but x is on {x.device}")
+    x2, w2 = _rows_view(x, K), _rows_view(w_gate_up, K)
+    y = torch.empty((M, N), dtype=torch.float8_e4m3fn, device=x.device)
+    if M > 0:
+        dev = x.device.index if x.device.index is not None else torch.cuda.current_device()
+        rc = _loader.load_library().magi_swiglu_forward_fp8_e4m3(
+            x2.data_ptr(), w2.data_ptr(), y.data_ptr(), scale.data_ptr(), M, N, K, x2.stride(0) if M > 1 else K,
+            w2.stride(0), N, dev, torch.cuda.current_stream(x.device).cuda_stream)
+        if rc != 0:
+            msg = f"magi_swiglu_forward_fp8_e4m3 failed ({rc}): {_loader.last_error()}"
+            raise (ValueError(msg) if rc < 0 else RuntimeError(msg))
+    return y.view(*x.shape[:-1], N)
+
+
 def _gemm_swiglu_setup_context(ctx, inputs, output):
     x, w_gate_up = inputs
     ctx.save_for_backward(x, w_gate_up)  # the 2N-wide pre-activations are never stored: backward recomputes them

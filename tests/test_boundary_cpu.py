@@ -35,6 +35,20 @@ def test_fake_impl_shape_dtype_device(lead):
         assert tuple(y.shape) == (*lead, 40) and y.dtype == torch.bfloat16 and y.device == x.device
 
 
+def test_fp8_output_op_schema_and_fake_impl():
+    op = torch.ops.magi_swiglu.gemm_swiglu_fp8.default
+    assert str(op._schema) == "magi_swiglu::gemm_swiglu_fp8(Tensor x, Tensor w_gate_up, Tensor scale) -> Tensor"
+    assert not op._schema.is_mutable
+    with FakeTensorMode():
+        x = torch.empty(3, 5, 64, dtype=torch.bfloat16, device="cuda")
+        w = torch.empty(2 * 48, 64, dtype=torch.bfloat16, device="cuda")
+        y = mb.gemm_swiglu_fp8(x, w, torch.empty(1, dtype=torch.float32, device="cuda"))
+        assert tuple(y.shape) == (3, 5, 48) and y.dtype == torch.float8_e4m3fn and y.device == x.device
+    with pytest.raises(TypeError):  # CPU tensors: no CPU path
+        mb.gemm_swiglu_fp8(torch.zeros(4, 64, dtype=torch.bfloat16), torch.zeros(32, 64, dtype=torch.bfloat16),
+                           torch.ones(1))
+
+
 def test_fake_impl_with_symbolic_rows():
     from torch.fx.experimental.proxy_tensor import make_fx
 

@@ -56,13 +56,46 @@ static inline double stream_cost_ns(int64_t N, int64_t num_kb, int bn, int z, in
   return (double)waves * ((double)kpz * (step_ns > 533.0 ? step_ns : 533.0) + 1500.0 + 6.0 * bn + (z > 1 ? 2500.0 : 0.0));
 }
 
+// Cheapest tile width for a persistent grid of `units` workers on tiles of `rows` x bn: whole waves of tiles, one
+// tile of width bn costing (bn + 146) x `unit_cost` (fixed part: epilogue, pipeline refill, lower operand reuse of
+// narrow tiles; measured on B200).  Widths are multiples of 32 from bn_max down to 128.
+static double tile_wave_cost(int64_t M, int64_t N, int rows, int64_t units, int bn_max, double unit_cost, int* bn_out) {
+  double best = -1.0;
+  if (units < 1) units = 1;
+  for (int bn = bn_max; bn >= 128; bn -= 32) {
+    const int64_t tiles = ((M + rows - 1) / rows) * ((N + bn - 1) / bn);
+    const double cost = (double)((tiles + units - 1) / units) * (bn + 146) * unit_cost;
+    if (best < 0 || cost < best) {
+      best = cost;
+      *bn_out = bn;
+    }
+  }
+  return best;
+}
+
 static int make_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, int stages, int group_m, int max_ctas,
                      int sm_count, int64_t ws_limit, Plan* p) {
   if (M < 0 || N <= 0 || K <= 0 || M > 0x7fffff00LL || N > 0x3fffff00LL || K > 0x7fffff00LL)
     return fail(MAGI_SWIGLU_ERR_SHAPE, "shape out of range: M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
   if (N % 8 != 0 || K % 8 != 0)
     return fail(MAGI_SWIGLU_ERR_SHAPE, "N (%lld) and K (%lld) must be multiples of 8", (long long)N, (long long)K);
-  if (variant == MAGI_SWIGLU_VARIANT_AUTO) variant = (M <= 128) ? MAGI_SWIGLU_VARIANT_STREAM : MAGI_SWIGLU_VARIANT_MMA2;
+  if (variant == MAGI_SWIGLU_VARIANT_AUTO) {
+    variant = (M <= 128) ? MAGI_SWIGLU_VARIANT_STREAM : MAGI_SWIGLU_VARIANT_MMA2;
+    // A CTA pair works on 256 rows at a time; when the last 256-row unit is at most half full and there are few
+    // units (M = 320 or 384, say), 128-row tiles on single CTAs waste less.  Measured on B200, a single-CTA tile of
+    // width bn takes about 1.12 x the time of a pair tile of the same width (each CTA loads all of W's tile rows
+    // instead of half), and bn <= 224 keeps three pipeline stages in shared memory.
+    if (M > kBM && N >= 128 && block_n == 0 && sm_count >= 2 && (max_ctas <= 0 || max_ctas >= 2)) {
+      const int avail = (max_ctas > 0 && max_ctas < sm_count) ? max_ctas : sm_count;
+      int bn_pair = 0, bn_single = 0;
+      const double cost_pair = tile_wave_cost(M, N, 2 * kBM, avail / 2, 256, 1.0, &bn_pair);
+      const double cost_single = tile_wave_cost(M, N, kBM, avail, 224, 1.12, &bn_single);
+      if (cost_single < 0.95 * cost_pair) {  // 5 %: the pair schedule is the better-measured default
+        variant = MAGI_SWIGLU_VARIANT_MMA;
+        block_n = bn_single;
+      }
+    }
+  }
   if (variant != MAGI_SWIGLU_VARIANT_MMA && variant != MAGI_SWIGLU_VARIANT_STREAM &&
       variant != MAGI_SWIGLU_VARIANT_SIMT && variant != MAGI_SWIGLU_VARIANT_MMA2)
     return fail(MAGI_SWIGLU_ERR_VARIANT, "unknown variant %d", variant);
@@ -92,17 +125,8 @@ static int make_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
       if (N < 128) {
         block_n = round_up((int)N, 16);
       } else {
-        const int64_t units = ctas / 2;
-        const int64_t m_units = (M + 2 * kBM - 1) / (2 * kBM);
-        int64_t best_cost = -1;
-        for (int bn = 256; bn >= 128; bn -= 32) {  // multiples of 32: both half tiles stay multiples of 16
-          const int64_t tiles = m_units * ((N + bn - 1) / bn);
-          const int64_t cost = ((tiles + units - 1) / units) * (bn + 146);
-          if (best_cost < 0 || cost < best_cost) {
-            best_cost = cost;
-            block_n = bn;
-          }
-        }
+        // multiples of 32: both half tiles stay multiples of 16
+        tile_wave_cost(M, N, 2 * kBM, ctas / 2, 256, 1.0, &block_n);
       }
     } else if (variant == MAGI_SWIGLU_VARIANT_MMA) {
       block_n = (N >= 128) ? 128 : round_up((int)N, 16);

@@ -89,6 +89,20 @@ def test_plan_for_cta_pairs():
         _loader.plan(300, 528, 320, variant="mma2", max_ctas=1, sm_count=148)
 
 
+def test_plan_uses_single_cta_tiles_when_the_last_row_pair_is_half_empty():
+    # M = 384 is three 128-row granules: CTA pairs would run four (two 256-row units), single CTAs run three
+    for M in (288, 320, 384):
+        p = _loader.plan(M, 28672, 8192, sm_count=148)
+        assert p["variant"] == _loader.VARIANT_MMA and p["ctas"] == 1 and p["block_n"] <= 224 and p["stages"] >= 3
+        assert p["tiles"] == 3 * -(-28672 // p["block_n"])
+    # full units, or many of them: pairs stay
+    for M in (256, 512, 640, 1024, 8192 + 128):
+        assert _loader.plan(M, 28672, 8192, sm_count=148)["variant"] == _loader.VARIANT_MMA2
+    # an explicit width or variant is never overridden
+    assert _loader.plan(384, 28672, 8192, block_n=256, sm_count=148)["variant"] == _loader.VARIANT_MMA2
+    assert _loader.plan(384, 28672, 8192, variant="mma2", sm_count=148)["variant"] == _loader.VARIANT_MMA2
+
+
 def test_plan_respects_explicit_knobs_and_rejects_bad_ones():
     p = _loader.plan(4096, 4096, 4096, variant="mma", block_n=64, stages=3, max_ctas=10, sm_count=148)
     assert (p["block_n"], p["stages"], p["grid"], p["acc_bufs"], p["n_mma"]) == (64, 3, 10, 2, 1)

@@ -79,6 +79,7 @@ def test_against_reference_fixture(golden, name, variant):
 SHAPES = [  # (M, N, K): tails in every dimension, single-tile and multi-tile
     (1, 8, 8), (1, 64, 64), (16, 128, 64), (17, 72, 200), (64, 264, 128), (120, 136, 72), (128, 128, 1024),
     (129, 128, 64), (255, 192, 136), (256, 8, 64), (300, 520, 328), (515, 1000, 96), (33, 2816, 64),
+    (384, 28672, 72), (300, 14336, 128),  # three 128-row granules and several waves: AUTO picks single-CTA tiles
 ]
 
 

@@ -165,6 +165,26 @@ int magi_swiglu_backward_act_bf16(const void* h, const void* dy, void* dh,
                                   int64_t M, int64_t N, int64_t ldh, int64_t lddy, int64_t lddh,
                                   int device, void* cuda_stream);
 
+/* The forward for training: as magi_swiglu_forward_bf16, and the same kernel also writes the pre-activations
+ * h = [G | U] ([M, 2N] bf16, row stride ldh, each value rounded once from its fp32 accumulator), so that the backward
+ * (magi_swiglu_backward_act_bf16 on h and dY) needs no recomputation.  Costs one extra write of M x 2N bf16.
+ * Replaces: the tensors PyTorch's autograd saves for F.silu(gate_proj(x)) * up_proj(x)
+ * (tests/model_definition.py:337-339): the outputs of the two projections. */
+int magi_swiglu_forward_bf16_preact(const void* x, const void* w_gate_up, void* y, void* h,
+                                    int64_t M, int64_t N, int64_t K,
+                                    int64_t ldx, int64_t ldw, int64_t ldy, int64_t ldh,
+                                    int device, void* cuda_stream);
+
+/* The first half of the backward in ONE kernel: recomputes G = X·Wg^T and U = X·Wu^T on the tile kernels and, in the
+ * epilogue, turns the fp32 accumulators and dY straight into dH = [dG | dU] (formulas as above) — the 2N-wide
+ * pre-activations are never written to memory.  x [M,K], w_gate_up [2N,K], dy [M,N] (row stride lddy), dh [M,2N] (row
+ * stride lddh); requirements as magi_swiglu_forward_bf16, plus lddy % 8 == 0 and a 16-byte aligned dy.
+ * Replaces: the same autograd as magi_swiglu_backward_act_bf16, together with the recomputation in front of it. */
+int magi_swiglu_backward_dh_bf16(const void* x, const void* w_gate_up, const void* dy, void* dh,
+                                 int64_t M, int64_t N, int64_t K,
+                                 int64_t ldx, int64_t ldw, int64_t lddy, int64_t lddh,
+                                 int device, void* cuda_stream);
+
 /* Scratch bytes the preferred schedule of magi_swiglu_forward_bf16_ws wants for this problem (0 = none needed;
  * negative = argument error).  Needs no GPU when sm_count > 0.
  * Replaces: nothing in the reference. */

@@ -81,6 +81,11 @@ struct KArgs {
   int wide_store;     // y base and row pitch are 32-byte aligned: 256-bit stores (one full sector per thread)
   const float* row_scale;  // optional [M] fp32: accumulators of row m are multiplied by row_scale[m] before the
                            // epilogue (a fused RMSNorm: 1/rms(x_m), the norm weight being folded into W); null = none
+  __nv_bfloat16* h;   // non-null: the forward also writes the pre-activations H = [G | U] (bf16, [M, 2N], row stride ldh)
+  long long ldh;
+  int wide_h;         // rows of H allow 32-byte stores
+  const __nv_bfloat16* dy;  // non-null: backward mode, Y is dH [M, 2N] = [dG | dU] computed from the accumulators and dY
+  long long lddy;
   const float* out_scale;  // non-null: Y is fp8 e4m3 (one byte per element), y = sat(silu(g)*u / *out_scale)
   int plain;          // 1: plain GEMM C = A·B^T; B's first N rows fill output columns [0,N), its last N rows [N,2N)
   int x_hint, w_hint, y_hint;  // L2 eviction priority of X tiles, W tiles and Y stores: 0 normal, 1 first, 2 last
@@ -182,6 +187,36 @@ __device__ __forceinline__ void store_cols_plain(__nv_bfloat16* dst, const uint3
       }
     } else if (16 * j + 8 <= cols_valid) {
       st_global_v4_hint(dst + 16 * j, plain_pack8(v + 16 * j), policy);
+    }
+  }
+}
+
+// Backward of the activation on fp32 accumulators: from G, U (recomputed, never rounded) and dY (bf16, read here)
+//   dG = dY * U * s * (1 + G * (1 - s)),   dU = dY * G * s,   s = sigmoid(G)
+// kCols consecutive columns of one row; dG goes to dst_g, dU to dst_u (N columns further in the same row of dH).
+template <int kCols>
+__device__ __forceinline__ void store_cols_bwd(__nv_bfloat16* dst_g, __nv_bfloat16* dst_u, const __nv_bfloat16* dy,
+                                               const uint32_t* g, const uint32_t* u, int cols_valid, uint64_t policy) {
+#pragma unroll
+  for (int j = 0; j < kCols / 8; ++j) {
+    if (8 * j + 8 <= cols_valid) {
+      const uint4 dv = __ldg(reinterpret_cast<const uint4*>(dy + 8 * j));
+      const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&dv);
+      uint4 og, ou;
+      __nv_bfloat162* og2 = reinterpret_cast<__nv_bfloat162*>(&og);
+      __nv_bfloat162* ou2 = reinterpret_cast<__nv_bfloat162*>(&ou);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 d = __bfloat1622float2(d2[q]);
+        const float gx = __uint_as_float(g[8 * j + 2 * q]), gy = __uint_as_float(g[8 * j + 2 * q + 1]);
+        const float ux = __uint_as_float(u[8 * j + 2 * q]), uy = __uint_as_float(u[8 * j + 2 * q + 1]);
+        const float sx = __fdividef(1.0f, 1.0f + __expf(-gx)), sy = __fdividef(1.0f, 1.0f + __expf(-gy));
+        og2[q] = __floats2bfloat162_rn(d.x * ux * sx * (1.0f + gx * (1.0f - sx)),
+                                       d.y * uy * sy * (1.0f + gy * (1.0f - sy)));
+        ou2[q] = __floats2bfloat162_rn(d.x * gx * sx, d.y * gy * sy);
+      }
+      st_global_v4_hint(dst_g + 8 * j, og, policy);
+      st_global_v4_hint(dst_u + 8 * j, ou, policy);
     }
   }
 }
@@ -556,7 +591,23 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
               u[j] = __float_as_uint(__uint_as_float(u[j]) * row_scale_m);
             }
           }
-          if (a.out_scale != nullptr) {  // fp8 output: one byte per element
+          if (a.h != nullptr) {  // training forward: keep the pre-activations for the backward
+            __nv_bfloat16* hrow = a.h + (long long)row * a.ldh + col0 + seg * seg_cols + c;
+            if (w == 32) {
+              store_cols_plain<32>(hrow, g, valid - c, a.wide_h != 0, y_policy);
+              store_cols_plain<32>(hrow + a.N, u, valid - c, a.wide_h != 0, y_policy);
+            } else {
+              store_cols_plain<16>(hrow, g, valid - c, a.wide_h != 0, y_policy);
+              store_cols_plain<16>(hrow + a.N, u, valid - c, a.wide_h != 0, y_policy);
+            }
+          }
+          if (a.dy != nullptr) {  // backward: dH = [dG | dU] from the recomputed pre-activations and dY
+            const __nv_bfloat16* dyp = a.dy + (long long)row * a.lddy + col0 + seg * seg_cols + c;
+            if (w == 32)
+              store_cols_bwd<32>(yrow + c, yrow + a.N + c, dyp, g, u, valid - c, y_policy);
+            else
+              store_cols_bwd<16>(yrow + c, yrow + a.N + c, dyp, g, u, valid - c, y_policy);
+          } else if (a.out_scale != nullptr) {  // fp8 output: one byte per element
             uint8_t* y8 = reinterpret_cast<uint8_t*>(a.y) + (long long)row * a.ldy + col0 + seg * seg_cols + c;
             if (w == 32)
               store_cols_fp8<32>(y8, g, u, valid - c, out_inv_scale, y_policy);

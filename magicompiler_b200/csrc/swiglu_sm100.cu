@@ -110,7 +110,8 @@ struct DeviceGuard {
 static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int64_t ldx,
                         int64_t ldw, int64_t ldy, int device, void* stream_v, int variant, int block_n, int stages,
                         int group_m, int max_ctas, void* workspace, int64_t workspace_bytes, int plain = 0,
-                        const float* row_scale = nullptr, const float* out_scale = nullptr) {
+                        const float* row_scale = nullptr, const float* out_scale = nullptr, const void* dy = nullptr,
+                        int64_t lddy = 0, void* h = nullptr, int64_t ldh = 0) {
   g_err[0] = 0;
   if (M == 0 && N > 0 && K > 0) return 0;
   if (!x || !w || !y) return fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
@@ -206,6 +207,11 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   a.plain = plain;
   a.row_scale = row_scale;
   a.out_scale = out_scale;
+  a.dy = static_cast<const __nv_bfloat16*>(dy);
+  a.lddy = lddy;
+  a.h = static_cast<__nv_bfloat16*>(h);
+  a.ldh = ldh;
+  a.wide_h = (((uintptr_t)h & 31u) == 0 && ldh % 16 == 0 && N % 16 == 0) ? 1 : 0;
   a.k_splits = p.k_splits;
   a.kb_per_split = p.kb_per_split;
   a.ws = p.k_splits > 1 ? static_cast<float*>(workspace) : nullptr;
@@ -396,6 +402,35 @@ int magi_swiglu_forward_fp8_e4m3(const void* x, const void* w_gate_up, void* y_f
   const int variant = MAGI_SWIGLU_VARIANT_AUTO;
   return magi::forward_impl(x, w_gate_up, y_fp8, M, N, K, ldx, ldw, ldy, device, cuda_stream, variant, 0, 0, 0, 0, nullptr,
                             0, 0, nullptr, scale);
+}
+
+int magi_swiglu_forward_bf16_preact(const void* x, const void* w_gate_up, void* y, void* h, int64_t M, int64_t N, int64_t K,
+                                    int64_t ldx, int64_t ldw, int64_t ldy, int64_t ldh, int device, void* cuda_stream) {
+  magi::g_err[0] = 0;
+  if (M > 0 && !h) return magi::fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
+  if (ldh < 2 * N)
+    return magi::fail(MAGI_SWIGLU_ERR_SHAPE, "row stride too small: ldh=%lld (2N=%lld)", (long long)ldh, (long long)(2 * N));
+  if (ldh % 8 || ((uintptr_t)h & 15u))
+    return magi::fail(MAGI_SWIGLU_ERR_ALIGN, "h must be 16-byte aligned with a row stride that is a multiple of 8");
+  // no scratch: the split-K reduce kernel does not write H, so narrow problems run unsplit here
+  return magi::forward_impl(x, w_gate_up, y, M, N, K, ldx, ldw, ldy, device, cuda_stream, MAGI_SWIGLU_VARIANT_AUTO, 0, 0, 0,
+                            0, nullptr, 0, 0, nullptr, nullptr, nullptr, 0, h, ldh);
+}
+
+int magi_swiglu_backward_dh_bf16(const void* x, const void* w_gate_up, const void* dy, void* dh, int64_t M, int64_t N,
+                                 int64_t K, int64_t ldx, int64_t ldw, int64_t lddy, int64_t lddh, int device,
+                                 void* cuda_stream) {
+  magi::g_err[0] = 0;
+  if (M > 0 && !dy) return magi::fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
+  if (lddy < N || lddh < 2 * N)
+    return magi::fail(MAGI_SWIGLU_ERR_SHAPE, "row strides too small: lddy=%lld (N=%lld) lddh=%lld (2N=%lld)",
+                      (long long)lddy, (long long)N, (long long)lddh, (long long)(2 * N));
+  if (lddy % 8 || ((uintptr_t)dy & 15u))
+    return magi::fail(MAGI_SWIGLU_ERR_ALIGN, "dy must be 16-byte aligned with a row stride that is a multiple of 8");
+  // `plain` makes the common checks see dH's width (2N); the backward epilogue takes precedence in the kernel.
+  // No scratch is passed, so narrow problems run unsplit (the split-K reduce kernel has no backward epilogue).
+  return magi::forward_impl(x, w_gate_up, dh, M, N, K, ldx, ldw, lddh, device, cuda_stream, MAGI_SWIGLU_VARIANT_AUTO, 0,
+                            0, 0, 0, nullptr, 0, 1, nullptr, nullptr, dy, lddy);
 }
 
 int magi_swiglu_gemm_nt_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,

@@ -250,6 +250,104 @@ def swiglu_backward_act(h: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
     return dh
 
 
+BWD_DH_OP_NAME = "magi_swiglu::swiglu_backward_dh"
+
+
+@magi_register_custom_op(name=BWD_DH_OP_NAME, mutates_args=(),
+                         infer_output_meta_fn=lambda x, w_gate_up, dy: dy.new_empty((dy.shape[0], 2 * dy.shape[1])),
+                         is_compute_sensitive=True)
+def swiglu_backward_dh(x: torch.Tensor, w_gate_up: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
+    """``dH = [dG | dU]`` (``[M, 2N]`` bf16) from ``x [M, K]``, the packed weight and ``dY [M, N]`` in ONE kernel
+    (``magi_swiglu_backward_dh_bf16``): the tile kernels recompute the pre-activations into tensor memory and the
+    epilogue applies the activation's derivative to the fp32 accumulators, so ``H`` never reaches HBM."""
+    M, N, K = _check(x, w_gate_up)
+    if x.dim() != 2 or dy.dim() != 2 or dy.dtype != torch.bfloat16 or dy.device != x.device \
+            or tuple(dy.shape) != (M, N):
+        raise ValueError(f"shapes do not match: x {tuple(x.shape)}, w_gate_up {tuple(w_gate_up.shape)}, "
+                         f"dy {tuple(dy.shape)} {dy.dtype} (need [M,K], [2N,K], bf16 [M,N])")
+    x2, w2, dy2 = _rows_view(x, K), _rows_view(w_gate_up, K), _rows_view(dy, N)
+    dh = torch.empty((M, 2 * N), dtype=torch.bfloat16, device=x.device)
+    if M > 0:
+        dev = x.device.index if x.device.index is not None else torch.cuda.current_device()
+        rc = _loader.load_library().magi_swiglu_backward_dh_bf16(
+            x2.data_ptr(), w2.data_ptr(), dy2.data_ptr(), dh.data_ptr(), M, N, K, x2.stride(0) if M > 1 else K,
+            w2.stride(0), dy2.stride(0) if M > 1 else N, 2 * N, dev, torch.cuda.current_stream(x.device).cuda_stream)
+        if rc != 0:
+            msg = f"magi_swiglu_backward_dh_bf16 failed ({rc}): {_loader.last_error()}"
+            raise (ValueError(msg) if rc < 0 else RuntimeError(msg))
+    return dh
+
+
+PREACT_OP_NAME = "magi_swiglu::gemm_swiglu_preact"
+
+
+def _gemm_swiglu_preact_meta(x: torch.Tensor, w_gate_up: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    n = w_gate_up.shape[0] // 2
+    rows = x.numel() // x.shape[-1] if x.dim() != 2 else x.shape[0]
+    return x.new_empty((*x.shape[:-1], n)), x.new_empty((rows, 2 * n))
+
+
+def _gemm_swiglu_preact_setup_context(ctx, inputs, output):
+    x, w_gate_up = inputs
+    ctx.set_materialize_grads(False)  # the gradient of the auxiliary output H is normally absent: keep it None
+    ctx.save_for_backward(x, w_gate_up, output[1])
+
+
+def _gemm_swiglu_preact_backward(ctx, grad_y, grad_h):
+    """dH from the SAVED pre-activations (one element-wise kernel), then dX = dH · W and dW = dH^T · X (library)."""
+    x, w, h = ctx.saved_tensors
+    if grad_y is None and grad_h is None:
+        return None, None
+    k = x.shape[-1]
+    x2 = x.reshape(-1, k)
+    dh = None
+    if grad_y is not None:
+        dh = torch.ops.magi_swiglu.swiglu_backward_act(h, grad_y.reshape(-1, grad_y.shape[-1]).contiguous())
+    if grad_h is not None:
+        dh = grad_h if dh is None else dh + grad_h
+    dx = torch.matmul(dh, w).view(x.shape) if ctx.needs_input_grad[0] else None
+    dw = torch.matmul(dh.t(), x2) if ctx.needs_input_grad[1] else None
+    return dx, dw
+
+
+@magi_register_custom_op(
+    name=PREACT_OP_NAME,
+    mutates_args=(),
+    infer_output_meta_fn=_gemm_swiglu_preact_meta,
+    setup_context_fn=_gemm_swiglu_preact_setup_context,
+    backward_fn=_gemm_swiglu_preact_backward,
+    is_compute_sensitive=True,
+    is_subgraph_boundary=True,
+)
+def gemm_swiglu_preact(x: torch.Tensor, w_gate_up: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """``(y, h)``: the fused op and, from the same kernel, the pre-activations ``h = [x·Wg^T | x·Wu^T]``
+    (``[M, 2N]`` bf16; ``magi_swiglu_forward_bf16_preact``).  Its autograd keeps ``h`` (what PyTorch keeps for the
+    reference's eager expression, tests/model_definition.py:337-339) and so runs no GEMM again in the backward; the
+    single-output op keeps nothing but its inputs and recomputes.  Use ``gemm_swiglu_train`` for the ``y``-only form."""
+    M, N, K = _check(x, w_gate_up)
+    x2, w2 = _rows_view(x, K), _rows_view(w_gate_up, K)
+    if w2.data_ptr() != w_gate_up.data_ptr() and w_gate_up.numel() > 0:
+        raise ValueError("w_gate_up must have unit inner stride, a row stride that is a multiple of 8 and a "
+                         "16-byte-aligned base; pack it once with magicompiler_b200.pack_gate_up")
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    h = torch.empty((M, 2 * N), dtype=torch.bfloat16, device=x.device)
+    if M > 0:
+        dev = x.device.index if x.device.index is not None else torch.cuda.current_device()
+        rc = _loader.load_library().magi_swiglu_forward_bf16_preact(
+            x2.data_ptr(), w2.data_ptr(), y.data_ptr(), h.data_ptr(), M, N, K, x2.stride(0) if M > 1 else K,
+            w2.stride(0), N, 2 * N, dev, torch.cuda.current_stream(x.device).cuda_stream)
+        if rc != 0:
+            msg = f"magi_swiglu_forward_bf16_preact failed ({rc}): {_loader.last_error()}"
+            raise (ValueError(msg) if rc < 0 else RuntimeError(msg))
+    return y.view(*x.shape[:-1], N), h
+
+
+def gemm_swiglu_train(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """``gemm_swiglu`` for training steps where memory allows keeping the ``[M, 2N]`` pre-activations: forward +
+    backward run four GEMMs' worth of tensor work instead of five (no recomputation)."""
+    return torch.ops.magi_swiglu.gemm_swiglu_preact(x, w_gate_up)[0]
+
+
 FP8_OP_NAME = "magi_swiglu::gemm_swiglu_fp8"
 
 
@@ -292,14 +390,14 @@ def _gemm_swiglu_setup_context(ctx, inputs, output):
 
 
 def _gemm_swiglu_backward(ctx, grad_out):
-    """dX = dH · W and dW = dH^T · X with dH = [dG | dU]; H = X · W^T is recomputed on the op's own tile kernels
-    (gemm_nt); the two gradient GEMMs need transposed operands and go to the library."""
+    """dX = dH · W and dW = dH^T · X with dH = [dG | dU] from one kernel that recomputes H = X · W^T in tensor memory
+    and applies the activation's derivative in its epilogue (swiglu_backward_dh); the two gradient GEMMs need
+    transposed operands and go to the library."""
     x, w = ctx.saved_tensors
     k = x.shape[-1]
     x2 = x.reshape(-1, k)
     dy2 = grad_out.reshape(-1, grad_out.shape[-1]).contiguous()
-    h = torch.ops.magi_swiglu.gemm_nt(x2, w)
-    dh = torch.ops.magi_swiglu.swiglu_backward_act(h, dy2)
+    dh = torch.ops.magi_swiglu.swiglu_backward_dh(x2, w, dy2)
     dx = torch.matmul(dh, w).view(x.shape) if ctx.needs_input_grad[0] else None
     dw = torch.matmul(dh.t(), x2) if ctx.needs_input_grad[1] else None
     return dx, dw

@@ -110,10 +110,13 @@ class FuseSwiGLUPass(_PassBase):
     ``x``) of a Dynamo-level FX graph into ``gemm_swiglu(x, pack_gate_up_cached(Wg, Wu))``.
 
     ``allowed_devices``: device types of the traced tensors for which the rewrite is made (the kernel exists for
-    CUDA; "meta" lets shape-only traces through; tests that stand a CPU function in for the kernel add "cpu")."""
+    CUDA; "meta" lets shape-only traces through; tests that stand a CPU function in for the kernel add "cpu").
+    ``save_preactivations``: emit the two-output training op ``gemm_swiglu_preact`` (its backward reads the kept
+    ``[M, 2N]`` pre-activations instead of recomputing them) and use its first output."""
 
-    def __init__(self, allowed_devices: tuple[str, ...] = ("cuda", "meta")):
+    def __init__(self, allowed_devices: tuple[str, ...] = ("cuda", "meta"), save_preactivations: bool = False):
         self.allowed_devices = tuple(allowed_devices)
+        self.save_preactivations = bool(save_preactivations)
 
     def _matches(self, graph: torch.fx.Graph):
         found = []
@@ -158,7 +161,11 @@ class FuseSwiGLUPass(_PassBase):
             x, wg, wu = gate.args[0], gate.args[1], up.args[1]
             with graph.inserting_before(mul):
                 packed = graph.call_function(torch.ops.magi_swiglu.pack_gate_up_cached.default, (wg, wu))
-                fused = graph.call_function(torch.ops.magi_swiglu.gemm_swiglu.default, (x, packed))
+                if self.save_preactivations:
+                    both = graph.call_function(torch.ops.magi_swiglu.gemm_swiglu_preact.default, (x, packed))
+                    fused = graph.call_function(operator.getitem, (both, 0))
+                else:
+                    fused = graph.call_function(torch.ops.magi_swiglu.gemm_swiglu.default, (x, packed))
             for new, fn in ((packed, _pack_meta), (fused, None)):
                 try:  # carry shape metadata forward when the graph has it (fake tensors from Dynamo)
                     if fn is not None:
@@ -177,7 +184,8 @@ class FuseSwiGLUPass(_PassBase):
         return count
 
 
-def install_into_magi_compiler(allowed_devices: tuple[str, ...] = ("cuda", "meta")) -> bool:
+def install_into_magi_compiler(allowed_devices: tuple[str, ...] = ("cuda", "meta"),
+                               save_preactivations: bool = False) -> bool:
     """Opt-in: make MagiCompiler's ``FullGraphPassManager`` run ``FuseSwiGLUPass`` first.  Returns False when
     MagiCompiler is not importable.  (Upstream, the same effect is two lines in ``full_graph_pass_mgr.py``.)"""
     try:
@@ -191,7 +199,7 @@ def install_into_magi_compiler(allowed_devices: tuple[str, ...] = ("cuda", "meta
 
     def patched_init(self, pass_config):
         original_init(self, pass_config)
-        self.passes.insert(0, FuseSwiGLUPass(allowed_devices))
+        self.passes.insert(0, FuseSwiGLUPass(allowed_devices, save_preactivations))
 
     cls.__init__ = patched_init
     cls._magi_swiglu_installed = True

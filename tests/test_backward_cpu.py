@@ -28,6 +28,13 @@ def test_backward_op_schema_and_fake_impl():
         dy = torch.empty(10, 48, dtype=torch.bfloat16, device="cuda")
         dh = mb.swiglu_backward_act(h, dy)
         assert dh.shape == (10, 96) and dh.dtype == torch.bfloat16
+    op = torch.ops.magi_swiglu.swiglu_backward_dh.default
+    assert str(op._schema) == "magi_swiglu::swiglu_backward_dh(Tensor x, Tensor w_gate_up, Tensor dy) -> Tensor"
+    with FakeTensorMode():
+        x = torch.empty(10, 64, dtype=torch.bfloat16, device="cuda")
+        w = torch.empty(96, 64, dtype=torch.bfloat16, device="cuda")
+        dh = mb.swiglu_backward_dh(x, w, torch.empty(10, 48, dtype=torch.bfloat16, device="cuda"))
+        assert dh.shape == (10, 96) and dh.dtype == torch.bfloat16
 
 
 def test_autograd_graph_through_fake_tensors():
@@ -41,3 +48,16 @@ def test_autograd_graph_through_fake_tensors():
     assert gx.shape == x.shape and gw.shape == w.shape and gx.dtype == torch.bfloat16
     (gx_only,) = torch.autograd.grad(mb.gemm_swiglu(x, w.detach()), (x,), torch.empty_like(y))
     assert gx_only.shape == x.shape
+
+
+def test_training_op_keeps_the_preactivations_and_differentiates():
+    op = torch.ops.magi_swiglu.gemm_swiglu_preact.default
+    assert str(op._schema) == "magi_swiglu::gemm_swiglu_preact(Tensor x, Tensor w_gate_up) -> (Tensor, Tensor)"
+    assert "magi_swiglu::gemm_swiglu_preact" in mb.SPLITTING_OPS
+    x = torch.empty(4, 6, 64, dtype=torch.bfloat16, device="meta", requires_grad=True)
+    w = torch.empty(80, 64, dtype=torch.bfloat16, device="meta", requires_grad=True)
+    y, h = mb.gemm_swiglu_preact(x, w)
+    assert y.shape == (4, 6, 40) and h.shape == (24, 80) and h.dtype == torch.bfloat16
+    y = mb.gemm_swiglu_train(x, w)
+    gx, gw = torch.autograd.grad(y, (x, w), torch.empty_like(y))
+    assert gx.shape == x.shape and gw.shape == w.shape and gw.dtype == torch.bfloat16

@@ -151,6 +151,64 @@ def test_backward_act_kernel_special_cases():
         mb.swiglu_backward_act(h, dy[:, :8])
 
 
+@pytest.mark.parametrize("shape", [(1, 64, 8), (64, 1024, 2816), (128, 264, 200), (300, 328, 520), (384, 72, 28672),
+                                   (1000, 512, 2048)])
+def test_fused_backward_dh_kernel(shape):
+    """swiglu_backward_dh (recompute in tensor memory + derivative in the epilogue) against the fp32 formula, in every
+    schedule AUTO picks (streaming, CTA pairs, single-CTA tiles); it is at least as close to it as the two-kernel
+    route through a bf16 H."""
+    M, K, N = shape
+    x, w = make_inputs(M, K, N, seed=N)
+    dy = torch.randn(M, N, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)
+    xd, wd, dyd = x.cuda(), w.cuda(), dy.cuda()
+    dh = mb.swiglu_backward_dh(xd, wd, dyd)
+    assert dh.shape == (M, 2 * N) and dh.dtype == torch.bfloat16
+    h = xd.float() @ wd.float().t()
+    g, u = h[:, :N], h[:, N:]
+    s = torch.sigmoid(g)
+    gold = torch.cat([dyd.float() * u * s * (1 + g * (1 - s)), dyd.float() * g * s], dim=1)
+    m = _grad_errors(dh, gold)
+    assert m["max_norm"] <= 1e-2 and m["frob"] <= 5e-3, m
+    two_step = mb.swiglu_backward_act(mb.gemm_nt(xd, wd), dyd) if N % 8 == 0 and (2 * N) % 16 == 0 else None
+    if two_step is not None:
+        assert m["frob"] <= _grad_errors(two_step, gold)["frob"] * 1.02 + 1e-6
+    # a strided dY (a column slice of a wider gradient) is read in place
+    wide = torch.zeros(M, N + 8, dtype=torch.bfloat16, device="cuda")
+    wide[:, :N] = dyd
+    assert torch.equal(mb.swiglu_backward_dh(xd, wd, wide[:, :N]), dh)
+    with pytest.raises(ValueError):
+        mb.swiglu_backward_dh(xd, wd, dyd[:, : N - 8] if N > 8 else dyd[:0])
+
+
+@pytest.mark.parametrize("shape", [(64, 1024, 2816), (300, 328, 520), (384, 72, 28672), (4096, 1024, 2048)])
+def test_training_forward_keeps_preactivations_and_backward_uses_them(shape):
+    """gemm_swiglu_preact: y is bit-identical to the inference op (same schedule), h is the single-rounded X·W^T, and the gradients
+    from the kept h meet the same bounds as the recomputing backward."""
+    from oracle import swiglu_backward_gold
+
+    M, K, N = shape
+    x, w = make_inputs(M, K, N, seed=M + 1)
+    dy = torch.randn(M, N, generator=torch.Generator().manual_seed(8)).to(torch.bfloat16).cuda()
+    xd = x.cuda().requires_grad_(True)
+    wd = w.cuda().requires_grad_(True)
+    y, h = mb.gemm_swiglu_preact(xd, wd)
+    y_inf = mb.gemm_swiglu(x.cuda(), w.cuda())
+    if mb.plan(M, N, K)["k_splits"] == 1 or mb.workspace_bytes(M, N, K) == 0:
+        assert torch.equal(y, y_inf)
+    else:  # the inference op splits K through scratch for this shape (another summation order); this op does not
+        assert _grad_errors(y, y_inf.float())["max_norm"] <= 8e-3
+    h_gold = x.cuda().float() @ w.cuda().float().t()
+    m = _grad_errors(h, h_gold)
+    assert m["max_norm"] <= 4e-3 and m["frob"] <= 3e-3, m  # one bf16 rounding of an fp32-accumulated product
+    if (2 * N) % 16 == 0:
+        assert torch.equal(h, mb.gemm_nt(x.cuda(), w.cuda()))
+    mb.gemm_swiglu_train(xd, wd).backward(dy)
+    dx_gold, dw_gold = swiglu_backward_gold(x.cuda(), w.cuda(), dy)
+    for name, got, gold in (("dx", xd.grad, dx_gold), ("dw", wd.grad, dw_gold)):
+        m = _grad_errors(got, gold)
+        assert m["max_norm"] <= 2e-2 and m["frob"] <= 1e-2, (name, m)
+
+
 def test_training_step_through_torch_compile():
     """The op inside a compiled training step (AOTAutograd traces its backward formula): gradients match eager."""
     torch._dynamo.reset()

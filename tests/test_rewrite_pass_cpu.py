@@ -38,13 +38,13 @@ class MLP(torch.nn.Module):
         return self.down_proj(h)
 
 
-def run_pass(module, x):
+def run_pass(module, x, **pass_kwargs):
     """Compile with a backend that applies the pass to the Dynamo graph; returns (targets before, after, output)."""
     seen = {}
 
     def backend(gm, example_inputs):
         seen["before"] = [n.target for n in gm.graph.nodes if n.op == "call_function"]
-        p = FuseSwiGLUPass()
+        p = FuseSwiGLUPass(**pass_kwargs)
         seen["applicable"] = p.is_applicable(gm.graph)
         seen["count"] = p(gm.graph) if seen["applicable"] else 0
         gm.recompile()
@@ -63,6 +63,16 @@ def test_pattern_is_rewritten_to_the_fused_op():
     assert F.silu not in seen["after"]
     assert sum(t in (F.linear, torch._C._nn.linear) for t in seen["after"]) == 1  # only down_proj is left
     assert tuple(y.shape) == (10, 64) and y.dtype == torch.bfloat16
+
+
+def test_training_variant_emits_the_two_output_op():
+    import operator
+
+    seen, y = run_pass(MLP(), torch.empty(3, 10, 64, dtype=torch.bfloat16, device="meta"), save_preactivations=True)
+    assert seen["count"] == 1 and GEMM not in seen["after"]
+    assert seen["after"].count(torch.ops.magi_swiglu.gemm_swiglu_preact.default) == 1
+    assert operator.getitem in seen["after"] and F.silu not in seen["after"]
+    assert tuple(y.shape) == (3, 10, 64) and y.dtype == torch.bfloat16
 
 
 def test_operand_order_and_leading_dims():

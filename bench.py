@@ -272,6 +272,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-incumbents", action="store_true", help="skip timing eager CUDA and the library GEMM")
+    ap.add_argument("--train", action="store_true",
+                    help="also time forward + backward of the op (both autograd forms) against the eager expression")
     ap.add_argument("--no-flush", action="store_true", help="profiling runs only: skip the L2 flush kernels")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" and not args.no_flush else args.warmup
@@ -487,6 +489,26 @@ def main():
                            "what": "F.silu(F.linear(x,Wg))*F.linear(x,Wu): 2 library GEMMs + 2 element-wise kernels"},
             "library_gemm_only": {"ms": t_gemm, "value": as_metric(t_gemm), "unit": unit,
                                   "what": "F.linear(x, W[2N,K]) alone, no activation"}}
+        if args.train:
+            # forward + backward of the op alone (dY given), 3 x the forward FLOPs of useful work
+            dy = torch.randn(M, N, device=dev, dtype=torch.float32).to(torch.bfloat16)
+            xr, wr = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+
+            def step(fn):
+                def run():
+                    xr.grad = None
+                    wr.grad = None
+                    fn(xr, wr).backward(dy)
+                return run
+
+            t_rec = timed(step(mb.gemm_swiglu))
+            t_keep = timed(step(mb.gemm_swiglu_train))
+            t_eag = timed(step(lambda a, b: F.silu(F.linear(a, b[:N])) * F.linear(a, b[N:])))
+            line["training"] = {
+                "unit": "ms per forward+backward", "flops": 3 * flops,
+                "gemm_swiglu_recompute": {"ms": t_rec, "tflops": 3 * flops / (t_rec * 1e-3) / 1e12},
+                "gemm_swiglu_train_kept_preactivations": {"ms": t_keep, "tflops": 3 * flops / (t_keep * 1e-3) / 1e12},
+                "eager_cuda": {"ms": t_eag, "tflops": 3 * flops / (t_eag * 1e-3) / 1e12}}
     if world == 1 and not args.no_cpu_baseline:
         v, rows, threads, t, reps = cpu_eager_tflops(M, K, N, x_cpu, w_cpu)
         if bound == "hbm":

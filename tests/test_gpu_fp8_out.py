@@ -96,3 +96,28 @@ def test_fp8_leading_dimensions_graph_capture_and_errors():
         mb.gemm_swiglu_fp8(x, w, s.double())
     with pytest.raises(ValueError):
         mb.gemm_swiglu_fp8(x, w, s.cpu())
+
+
+def test_fp8_output_against_vllm_silu_and_mul_quant():
+    """The op the reference's pass names, run for real when vLLM's compiled ops are present: it quantises the
+    bf16-rounded projections (and rounds the activation to bf16 before scaling), the fused kernel rounds once from
+    fp32, so a few percent of the bytes differ by one fp8 step and none by more."""
+    try:
+        import vllm._C  # noqa: F401
+    except Exception as exc:  # not installed, or built without this device
+        pytest.skip(f"vLLM compiled ops unavailable: {exc}")
+    if not hasattr(torch.ops._C, "silu_and_mul_quant"):
+        pytest.skip("this vLLM build has no silu_and_mul_quant")
+    for M, K, N in ((256, 512, 384), (1000, 1024, 2816)):
+        x, w = make_inputs(M, K, N, seed=N)
+        x, w = x.cuda(), w.cuda()
+        h = mb.gemm_nt(x, w)  # [M, 2N] bf16 = the merged gate/up linear's output
+        scale = torch.tensor([mb.gemm_swiglu(x, w).float().abs().max().item() / 300.0], dtype=torch.float32,
+                             device="cuda")
+        ref = torch.empty(M, N, dtype=torch.float8_e4m3fn, device="cuda")
+        torch.ops._C.silu_and_mul_quant(ref, h, scale)
+        y8 = mb.gemm_swiglu_fp8(x, w, scale)
+        a, b = y8.float(), ref.float()
+        same = (y8.view(torch.uint8) == ref.view(torch.uint8)) | ((a == 0) & (b == 0))
+        assert same.float().mean().item() >= 0.93, same.float().mean().item()
+        assert ((a - b).abs() <= _step(torch.maximum(a.abs(), b.abs())) * 1.001).all()

@@ -207,8 +207,8 @@ def run_mlp_block(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
     M, K, N, _, desc = WORKLOADS["mlp_block"]
     x_cpu, w_cpu, wd_cpu = make_inputs(M, K, N, seed=0, with_down=True)
-    mlp = mb.TensorParallelSwiGLUMLP(w_cpu, wd_cpu, rank, world, chunks=args.chunks,
-                                     down_fn=mb.gemm_nt if args.down == "own" else None).to(dev)
+    mlp = mb.TensorParallelSwiGLUMLP(w_cpu, wd_cpu, rank, world, chunks=args.chunks, reduce=args.reduce,
+                                     down_fn=mb.gemm_nt_out if args.down == "own" else None).to(dev)
     del w_cpu, wd_cpu
     x = x_cpu.to(dev)
 
@@ -239,15 +239,16 @@ def run_mlp_block(args, rank, world, local_rank):
         value = flops / (ms * 1e-3) / 1e12
         per_gpu = value / world
         print(json.dumps({
-            "metric": "SwiGLU MLP block TFLOP/s (fused gate/up + down projection + all-reduce)", "value": value,
+            "metric": f"SwiGLU MLP block TFLOP/s (fused gate/up + down projection + {args.reduce.replace('_', '-')})",
+            "value": value,
             "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic (CPU generator seed 0, X~N(0,1), W~N(0,0.02), bf16)",
             "config": {"workload": "mlp_block", "shape": desc, "chunks": args.chunks,
                        "down_projection": "magi_swiglu_gemm_nt_bf16 (own tile kernel)" if args.down == "own"
                        else "torch.matmul (library GEMM)",
-                       "parallelism": f"tp{world}: column-parallel gate/up, row-parallel down, NCCL all-reduce of "
-                                      f"[{M},{K}] bf16", "l2": "inputs (1.7 GB) larger than L2, back-to-back steps"},
+                       "parallelism": f"tp{world}: column-parallel gate/up, row-parallel down, NCCL "
+                                      f"{args.reduce.replace('_', '-')} of [{M},{K}] bf16", "l2": "inputs (1.7 GB) larger than L2, back-to-back steps"},
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": float(peaks["bf16_tflops_sustained"]),
                          "unit": "TFLOP/s", "frac": per_gpu / float(peaks["bf16_tflops_sustained"]), "traffic": None,
                          "peak_kind": f"{kind} cuBLAS bf16 sustained (kernels timed inside a long step)"},
@@ -268,6 +269,8 @@ def main():
     ap.add_argument("--stages", type=int, default=0)
     ap.add_argument("--group-m", type=int, default=0)
     ap.add_argument("--chunks", type=int, default=1, help="mlp_block: row chunks whose all-reduce overlaps the next chunk")
+    ap.add_argument("--reduce", default="all_reduce", choices=["all_reduce", "reduce_scatter"],
+                    help="mlp_block: all ranks get the whole result, or each keeps its rows of the sum")
     ap.add_argument("--down", default="own", choices=["own", "library"], help="mlp_block: kernel of the down projection")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")

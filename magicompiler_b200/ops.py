@@ -193,12 +193,9 @@ def rmsnorm_gemm_swiglu(x: torch.Tensor, w_folded: torch.Tensor, eps: float) -> 
 GEMM_NT_OP_NAME = "magi_swiglu::gemm_nt"
 
 
-@magi_register_custom_op(name=GEMM_NT_OP_NAME, mutates_args=(),
-                         infer_output_meta_fn=lambda a, b: a.new_empty((*a.shape[:-1], b.shape[0])),
-                         is_compute_sensitive=True)
-def gemm_nt(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    """``a @ b.T`` (``F.linear(a, b)``) in bf16 on the tile kernels of the fused op (``magi_swiglu_gemm_nt_bf16``):
-    ``a`` is ``[..., K]``, ``b`` is ``[N, K]`` with N a multiple of 16; fp32 accumulation, one rounding."""
+def gemm_nt_out(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``F.linear(a, b)`` on the tile kernels, written into ``out`` (``[M, N]`` bf16, unit inner stride, row stride a
+    multiple of 8, 16-byte-aligned base — e.g. a row slice of a larger result) when given: no copy afterwards."""
     if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
         raise TypeError("gemm_nt computes in bf16 only")
     if not (a.is_cuda and b.is_cuda) or a.device != b.device:
@@ -208,16 +205,35 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     n, k = b.shape
     a2, b2 = _rows_view(a, k), _rows_view(b, k)
     m = a2.shape[0]
-    c = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
+    if out is None:
+        c = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
+    else:
+        c = out
+        if c.dtype != torch.bfloat16 or c.device != a.device or tuple(c.shape) != (m, n) or c.stride(1) != 1 \
+                or (m > 1 and (c.stride(0) < n or c.stride(0) % 8)) or c.data_ptr() % 16:
+            raise ValueError("out must be a bf16 [M, N] tensor on a's device with unit inner stride, a row stride that "
+                             "is a multiple of 8 and a 16-byte-aligned base")
     if m > 0:
         dev = a.device.index if a.device.index is not None else torch.cuda.current_device()
         rc = _loader.load_library().magi_swiglu_gemm_nt_bf16(
-            a2.data_ptr(), b2.data_ptr(), c.data_ptr(), m, n, k, a2.stride(0) if m > 1 else k, b2.stride(0), n, dev,
-            torch.cuda.current_stream(a.device).cuda_stream)
+            a2.data_ptr(), b2.data_ptr(), c.data_ptr(), m, n, k, a2.stride(0) if m > 1 else k, b2.stride(0),
+            c.stride(0) if m > 1 else n, dev, torch.cuda.current_stream(a.device).cuda_stream)
         if rc != 0:
             msg = f"magi_swiglu_gemm_nt_bf16 failed ({rc}): {_loader.last_error()}"
             raise (ValueError(msg) if rc < 0 else RuntimeError(msg))
-    return c.view(*a.shape[:-1], n)
+    return c if out is not None else c.view(*a.shape[:-1], n)
+
+
+gemm_nt_out.supports_out = True  # TensorParallelSwiGLUMLP passes its result slice as out=
+
+
+@magi_register_custom_op(name=GEMM_NT_OP_NAME, mutates_args=(),
+                         infer_output_meta_fn=lambda a, b: a.new_empty((*a.shape[:-1], b.shape[0])),
+                         is_compute_sensitive=True)
+def gemm_nt(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``a @ b.T`` (``F.linear(a, b)``) in bf16 on the tile kernels of the fused op (``magi_swiglu_gemm_nt_bf16``):
+    ``a`` is ``[..., K]``, ``b`` is ``[N, K]`` with N a multiple of 16; fp32 accumulation, one rounding."""
+    return gemm_nt_out(a, b)
 
 
 BWD_ACT_OP_NAME = "magi_swiglu::swiglu_backward_act"

@@ -73,39 +73,76 @@ class ColumnParallelSwiGLU(torch.nn.Module):
 
 
 class TensorParallelSwiGLUMLP(torch.nn.Module):
-    """Full SwiGLU MLP over ``world`` ranks: fused column-parallel gate/up, row-parallel down, one all-reduce.
+    """Full SwiGLU MLP over ``world`` ranks: fused column-parallel gate/up, row-parallel down, one reduction.
 
-    ``chunks`` > 1 cuts the rows into that many slices and all-reduces slice i asynchronously while slice
-    i+1 is computed, so the NVLink transfer hides behind the GEMMs.
+    ``chunks`` > 1 cuts the rows into that many slices and reduces slice i asynchronously while slice i+1 is
+    computed, so the NVLink transfer hides behind the GEMMs.
+
+    ``reduce``: ``"all_reduce"`` (every rank gets the whole ``[M, K]`` result, fairscale's ``RowParallelLinear`` of
+    example/training/llama3.py:169) or ``"reduce_scatter"`` (each rank keeps the rows ``owned_rows(M)`` of the sum —
+    half the bytes on the links; the next layer all-gathers them or works row-sharded).  With reduce-scatter every
+    slice's row count must be a multiple of ``world``.
+
+    ``down_fn(h, w_down)`` returns the partial down projection; if it has a true ``supports_out`` attribute it is
+    called as ``down_fn(h, w_down, out=...)`` and writes straight into the result (``gemm_nt_out``).
     """
 
     def __init__(self, w_gate_up_full: torch.Tensor, w_down_full: torch.Tensor, rank: int = 0, world: int = 1,
-                 group=None, chunks: int = 1, swiglu_fn: Callable | None = None, down_fn: Callable | None = None):
+                 group=None, chunks: int = 1, swiglu_fn: Callable | None = None, down_fn: Callable | None = None,
+                 reduce: str = "all_reduce"):
         super().__init__()
+        if reduce not in ("all_reduce", "reduce_scatter"):
+            raise ValueError(f"reduce must be 'all_reduce' or 'reduce_scatter', got {reduce!r}")
         self.rank, self.world, self.group, self.chunks = rank, world, group, max(1, int(chunks))
+        self.reduce = reduce
         self._down = down_fn  # (h [m, N/P], w_down [K_out, N/P]) -> [m, K_out]; None = library GEMM (torch.matmul)
         self.gate_up = ColumnParallelSwiGLU(w_gate_up_full, rank, world, swiglu_fn)
         self.w_down = torch.nn.Parameter(shard_down(w_down_full, rank, world), requires_grad=False)
 
+    def _slices(self, m: int) -> list[tuple[int, int]]:
+        step = -(-m // self.chunks) if m else 0
+        return [(lo, min(m, lo + step)) for lo in range(0, m, step or 1)]
+
+    def owned_rows(self, m: int) -> torch.Tensor:
+        """Global row indices of this rank's output under ``reduce="reduce_scatter"``, in output order."""
+        parts = []
+        for lo, hi in self._slices(m):
+            per = (hi - lo) // self.world
+            parts.append(torch.arange(lo + self.rank * per, lo + (self.rank + 1) * per))
+        return torch.cat(parts) if parts else torch.empty(0, dtype=torch.long)
+
+    def _down_into(self, h: torch.Tensor, dst: torch.Tensor) -> None:
+        if self._down is None:
+            torch.matmul(h, self.w_down.t(), out=dst)  # plain library GEMM: partial sums of this rank
+        elif getattr(self._down, "supports_out", False):
+            self._down(h, self.w_down, out=dst)
+        else:
+            dst.copy_(self._down(h, self.w_down))
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         lead = x.shape[:-1]
         x2 = x.reshape(-1, x.shape[-1])
-        m = x2.shape[0]
-        out = torch.empty((m, self.w_down.shape[0]), dtype=self.w_down.dtype, device=x.device)
-        step = -(-m // self.chunks) if m else 0
-        works = []
-        for lo in range(0, m, step or 1):
-            hi = min(m, lo + step)
-            h = self.gate_up(x2[lo:hi])
-            if self._down is None:
-                torch.matmul(h, self.w_down.t(), out=out[lo:hi])  # plain library GEMM: partial sums of this rank
-            else:
-                out[lo:hi] = self._down(h, self.w_down)
-            if self.world > 1:
-                works.append(dist.all_reduce(out[lo:hi], op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+        m, k_out = x2.shape[0], self.w_down.shape[0]
+        scatter = self.reduce == "reduce_scatter" and self.world > 1
+        slices = self._slices(m)
+        if scatter and any((hi - lo) % self.world for lo, hi in slices):
+            raise ValueError(f"reduce_scatter needs every row slice to be a multiple of {self.world} rows "
+                             f"(M={m}, chunks={self.chunks})")
+        partial = torch.empty((m, k_out), dtype=self.w_down.dtype, device=x.device)
+        out = torch.empty((m // self.world, k_out), dtype=self.w_down.dtype, device=x.device) if scatter else partial
+        works, done = [], 0
+        for lo, hi in slices:
+            self._down_into(self.gate_up(x2[lo:hi]), partial[lo:hi])
+            if scatter:
+                per = (hi - lo) // self.world
+                works.append(dist.reduce_scatter_tensor(out[done:done + per], partial[lo:hi], op=dist.ReduceOp.SUM,
+                                                        group=self.group, async_op=True))
+                done += per
+            elif self.world > 1:
+                works.append(dist.all_reduce(partial[lo:hi], op=dist.ReduceOp.SUM, group=self.group, async_op=True))
         for wk in works:
             wk.wait()
-        return out.view(*lead, self.w_down.shape[0])
+        return out if scatter else out.view(*lead, k_out)
 
 
 def reference_mlp(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:

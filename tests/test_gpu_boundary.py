@@ -245,6 +245,15 @@ def test_plain_gemm_on_the_tile_kernels(shape):
     assert error_metrics(c, lib.float())["max_norm"] <= 8e-3  # at most a bf16 step from the library GEMM
     with pytest.raises(ValueError):
         mb.gemm_nt(a, b[: N - 8] if N > 8 else b[:, :4])
+    # written in place into a row slice of a larger, wider buffer: same bytes, nothing outside the slice touched
+    big = torch.full((M + 5, N + 8), 7.0, dtype=torch.bfloat16, device="cuda")
+    dst = big[2:2 + M, :N]
+    assert mb.gemm_nt_out(a, b, out=dst) is dst
+    assert torch.equal(dst, c)
+    big[2:2 + M, :N] = 7.0
+    assert (big == 7.0).all()
+    with pytest.raises(ValueError):
+        mb.gemm_nt_out(a, b, out=torch.empty(M, N, dtype=torch.float32, device="cuda"))
 
 
 def test_mlp_with_own_down_projection():

@@ -42,6 +42,13 @@ def _rank(rank, world, port, q):
         for chunks in (1, 4):
             z = mb.TensorParallelSwiGLUMLP(w, wd, rank, world, chunks=chunks).to(dev)(xd).float()
             ok_mlp &= bool(torch.allclose(z, ref, rtol=3e-2, atol=3e-2 * ref.abs().max().item()))
+            # own down projection written in place, reduce-scatter instead of all-reduce: this rank's rows of the sum
+            rs = mb.TensorParallelSwiGLUMLP(w, wd, rank, world, chunks=chunks, down_fn=mb.gemm_nt_out,
+                                            reduce="reduce_scatter").to(dev)
+            z_rs = rs(xd).float()
+            rows = rs.owned_rows(M).to(dev)
+            ok_mlp &= tuple(z_rs.shape) == (M // world, K)
+            ok_mlp &= bool(torch.allclose(z_rs, ref[rows], rtol=3e-2, atol=3e-2 * ref.abs().max().item()))
         torch.cuda.synchronize()
         q.put((rank, ok_cols, ok_mlp, mb.device_status(rank)["code"]))
     except Exception as exc:  # report instead of leaving the parent to time out

@@ -79,6 +79,24 @@ def _rank_main(rank, world, port, chunks, q):
         z = mlp(x)
         ref = torch.matmul(full.float(), wd.float().t())
         ok_mlp = torch.allclose(z, ref, rtol=1e-4, atol=1e-4)
+        # reduce-scatter form: each rank keeps its rows of every slice; a down_fn that writes into out= is used as such
+        def down(h, wdown, out=None):
+            return torch.matmul(h, wdown.t(), out=out)
+        down.supports_out = True
+        rs = TensorParallelSwiGLUMLP(w, wd.float(), rank, world, chunks=min(chunks, 2), reduce="reduce_scatter",
+                                     swiglu_fn=lambda a, b: _oracle_fn(a, b).float(), down_fn=down)
+        z_rs = rs(x)
+        rows = rs.owned_rows(x.shape[0])
+        ok_mlp = ok_mlp and list(z_rs.shape) == [20, 64] and torch.allclose(z_rs, ref[rows], rtol=1e-4, atol=1e-4)
+        gathered = [torch.empty_like(rows) for _ in range(world)]
+        dist.all_gather(gathered, rows)
+        ok_mlp = ok_mlp and sorted(torch.cat(gathered).tolist()) == list(range(40))  # every row owned exactly once
+        try:
+            TensorParallelSwiGLUMLP(w, wd.float(), rank, world, chunks=3, reduce="reduce_scatter",
+                                    swiglu_fn=lambda a, b: _oracle_fn(a, b).float())(x)  # slices of 14, 14, 12 rows
+            ok_mlp = ok_mlp and world == 2  # 14 and 12 are multiples of 2
+        except ValueError:
+            ok_mlp = ok_mlp and world != 2
         q.put((rank, ok_cols, ok_mlp, list(z.shape)))
     except Exception as exc:  # report instead of leaving the parent to time out
         q.put((rank, False, False, [repr(exc)]))

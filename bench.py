@@ -275,6 +275,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-incumbents", action="store_true", help="skip timing eager CUDA and the library GEMM")
+    ap.add_argument("--compiled-incumbent", action="store_true",
+                    help="also time torch.compile (Inductor) of the eager expression: 2 library GEMMs + 1 generated kernel")
     ap.add_argument("--train", action="store_true",
                     help="also time forward + backward of the op (both autograd forms) against the eager expression")
     ap.add_argument("--no-flush", action="store_true", help="profiling runs only: skip the L2 flush kernels")
@@ -492,6 +494,13 @@ def main():
                            "what": "F.silu(F.linear(x,Wg))*F.linear(x,Wu): 2 library GEMMs + 2 element-wise kernels"},
             "library_gemm_only": {"ms": t_gemm, "value": as_metric(t_gemm), "unit": unit,
                                   "what": "F.linear(x, W[2N,K]) alone, no activation"}}
+        if args.compiled_incumbent:
+            compiled = torch.compile(lambda a, b: F.silu(F.linear(a, b[:N])) * F.linear(a, b[N:]))
+            with torch.no_grad():
+                t_comp = timed(lambda: compiled(x, w))
+            line["incumbents"]["torch_compile"] = {
+                "ms": t_comp, "value": as_metric(t_comp), "unit": unit,
+                "what": "torch.compile (Inductor) of the eager expression: 2 library GEMMs + 1 generated kernel"}
         if args.train:
             # forward + backward of the op alone (dY given), 3 x the forward FLOPs of useful work
             dy = torch.randn(M, N, device=dev, dtype=torch.float32).to(torch.bfloat16)

@@ -146,6 +146,29 @@ int magi_swiglu_forward_fp8_e4m3(const void* x, const void* w_gate_up, void* y_f
                                  int64_t ldx, int64_t ldw, int64_t ldy,
                                  int device, void* cuda_stream);
 
+/* Layouts of the nvfp4 scale factors. */
+#define MAGI_SWIGLU_SCALES_LINEAR 0          /* scale of (row m, 16-column block b) at y_scale[m * ld_scale + b] */
+#define MAGI_SWIGLU_SCALES_SWIZZLED_128X4 1  /* tiles of 128 rows x 4 blocks (512 bytes), tile (m/128, b/4) at
+                                              * ((m/128) * ceil(N/64) + b/4) * 512, inside it row r = m % 128 at
+                                              * (r % 32) * 16 + (r / 32) * 4 + b % 4: the layout block-scaled GEMMs
+                                              * read; buffer of round_up(M,128) * round_up(N/16,4) bytes, padding
+                                              * entries are not written */
+
+/* The fused op with an nvfp4 output: blocks of 16 consecutive outputs share one e4m3 scale factor
+ *   sf = e4m3(gs * max|y| / 6),   code = e2m1(y * gs / sf)   (all codes 0 when sf == 0),
+ * gs = *global_scale (one fp32 value in device memory, read by the kernel; usually 448 * 6 / max|y| of a calibration
+ * run), y = silu(g)*u taken from the fp32 accumulators.  y_fp4 is [M, N/2] bytes, two codes per byte with the even
+ * column in the low nibble, row stride ldy BYTES (a multiple of 8); y_scale holds one byte per block in the chosen
+ * layout.  N % 16 == 0; other requirements as magi_swiglu_forward_bf16.
+ * Replaces: the merged gate/up linear followed by vLLM's silu_and_mul_nvfp4_quant(result, result_block_scale, input,
+ * input_global_scale), which the reference's de-functionalisation pass handles
+ * (passes/piecewise_graph/fix_functionalization.py:113-120). */
+int magi_swiglu_forward_nvfp4(const void* x, const void* w_gate_up, void* y_fp4, void* y_scale,
+                              const float* global_scale,
+                              int64_t M, int64_t N, int64_t K,
+                              int64_t ldx, int64_t ldw, int64_t ldy, int64_t ld_scale, int scale_layout,
+                              int device, void* cuda_stream);
+
 /* Plain bf16 GEMM on the same tile kernels: C[M,N] = A[M,K] · B[N,K]^T (both operands row-major with the reduction
  * dimension contiguous, i.e. y = F.linear(a, b)), fp32 accumulation, one rounding.  N % 16 == 0, K % 8 == 0, strides
  * multiples of 8, 16-byte aligned pointers.  Used for the row-parallel down projection of the MLP block.

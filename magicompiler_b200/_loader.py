@@ -87,6 +87,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.magi_swiglu_forward_bf16_scaled.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, vp, vp, i64]
     lib.magi_swiglu_forward_fp8_e4m3.restype = i32
     lib.magi_swiglu_forward_fp8_e4m3.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, vp]
+    lib.magi_swiglu_forward_nvfp4.restype = i32
+    lib.magi_swiglu_forward_nvfp4.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, i32, i32, vp]
     lib.magi_swiglu_forward_bf16_preact.restype = i32
     lib.magi_swiglu_forward_bf16_preact.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, i32, vp]
     lib.magi_swiglu_backward_dh_bf16.restype = i32

@@ -4,6 +4,7 @@
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <stdint.h>
 
 namespace magi {
@@ -156,6 +157,38 @@ __device__ __forceinline__ void st_global_v4_hint(void* ptr, uint4 v, uint64_t p
   asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(ptr), "r"(v.x), "r"(v.y), "r"(v.z),
                "r"(v.w), "l"(policy)
                : "memory");
+}
+__device__ __forceinline__ void st_global_v2_hint(void* ptr, uint2 v, uint64_t policy) {
+  asm volatile("st.global.L2::cache_hint.v2.b32 [%0], {%1, %2}, %3;" ::"l"(ptr), "r"(v.x), "r"(v.y), "l"(policy)
+               : "memory");
+}
+// eight fp32 values -> eight e2m1 (fp4) codes, element 0 in the low nibble of the low byte; round to nearest even,
+// saturating at +-6
+__device__ __forceinline__ uint32_t pack8_e2m1(float v0, float v1, float v2, float v3, float v4, float v5, float v6,
+                                               float v7) {
+  uint32_t out;
+  asm("{\n"
+      ".reg .b8 b0, b1, b2, b3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n"
+      "mov.b32 %0, {b0, b1, b2, b3};\n"
+      "}"
+      : "=r"(out)
+      : "f"(v0), "f"(v1), "f"(v2), "f"(v3), "f"(v4), "f"(v5), "f"(v6), "f"(v7));
+  return out;
+}
+// fp32 -> e4m3 (round to nearest even, saturating) and back
+__device__ __forceinline__ uint32_t f32_to_e4m3(float v) {
+  uint16_t o;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(o) : "f"(0.0f), "f"(v));
+  return (uint32_t)o & 0xffu;
+}
+__device__ __forceinline__ float e4m3_to_f32(uint32_t b) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((uint16_t)b));
+  return __half2float(__ushort_as_half((unsigned short)(h2 & 0xffffu)));
 }
 
 // ---------------------------------------------------------------- tcgen05

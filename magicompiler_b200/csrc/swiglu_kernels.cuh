@@ -86,7 +86,13 @@ struct KArgs {
   int wide_h;         // rows of H allow 32-byte stores
   const __nv_bfloat16* dy;  // non-null: backward mode, Y is dH [M, 2N] = [dG | dU] computed from the accumulators and dY
   long long lddy;
-  const float* out_scale;  // non-null: Y is fp8 e4m3 (one byte per element), y = sat(silu(g)*u / *out_scale)
+  const float* out_scale;  // out_kind 1: Y is fp8 e4m3 (one byte per element), y = sat(silu(g)*u / *out_scale);
+                           // out_kind 2: Y is nvfp4 (two e2m1 codes per byte), *out_scale is the tensor-wide scale
+  int out_kind;            // 0 bf16, 1 fp8, 2 nvfp4
+  uint8_t* sf;             // nvfp4: e4m3 scale factor per (row, 16 columns)
+  long long ld_sf;         // linear layout: bytes per row of sf
+  int sf_swizzled;         // 1: 128 x 4 tiled layout
+  int sf_ktiles;
   int plain;          // 1: plain GEMM C = A·B^T; B's first N rows fill output columns [0,N), its last N rows [N,2N)
   int x_hint, w_hint, y_hint;  // L2 eviction priority of X tiles, W tiles and Y stores: 0 normal, 1 first, 2 last
   // Split-K (STREAM schedule on narrow weights): k_splits CTAs share one tile, each sums kb_per_split K-steps and
@@ -242,6 +248,45 @@ __device__ __forceinline__ void store_cols_fp8(uint8_t* dst, const uint32_t* g, 
         w4[q] = (uint32_t)lo | ((uint32_t)hi << 16);
       }
       st_global_v4_hint(dst + 16 * j, make_uint4(w4[0], w4[1], w4[2], w4[3]), policy);
+    }
+  }
+}
+
+// Where the scale factor of row m, 16-column block kb lives.  Linear: sf[m * ld + kb].  Swizzled: the 128 x 4 tiling
+// of block-scaled GEMM operands (tiles of 128 rows x 4 blocks, 512 bytes each, tile row r at (r % 32) * 16 +
+// (r / 32) * 4), `ktiles` = ceil(blocks per row / 4).
+__device__ __forceinline__ long long nvfp4_sf_offset(long long m, int kb, int swizzled, long long ld, int ktiles) {
+  if (!swizzled) return m * ld + kb;
+  const long long tile = (m >> 7) * ktiles + (kb >> 2);
+  const int r = (int)(m & 127);
+  return tile * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3);
+}
+
+// nvfp4 output: blocks of 16 consecutive outputs share one e4m3 scale factor,
+//   sf = e4m3(gs * max|y| / 6),   code_i = e2m1(y_i * gs / sf)   (0 when sf == 0),
+// two codes per byte (even column in the low nibble); gs is the tensor-wide scale.  N % 16 == 0.
+template <int kCols>
+__device__ __forceinline__ void store_cols_fp4(uint8_t* dst, uint8_t* sf, long long m, int kb0, int sf_swizzled,
+                                               long long ld_sf, int sf_ktiles, const uint32_t* g, const uint32_t* u,
+                                               int cols_valid, float gs, float inv_gs, uint64_t policy) {
+#pragma unroll
+  for (int j = 0; j < kCols / 16; ++j) {
+    if (16 * j + 16 <= cols_valid) {
+      float v[16];
+      float vmax = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        v[i] = silu_mul(__uint_as_float(g[16 * j + i]), __uint_as_float(u[16 * j + i]));
+        vmax = fmaxf(vmax, fabsf(v[i]));
+      }
+      const uint32_t sf8 = f32_to_e4m3(gs * (vmax * (1.0f / 6.0f)));
+      const float sff = e4m3_to_f32(sf8);
+      const float os = (sff != 0.0f) ? __fdividef(1.0f, sff * inv_gs) : 0.0f;
+      uint2 o;
+      o.x = pack8_e2m1(v[0] * os, v[1] * os, v[2] * os, v[3] * os, v[4] * os, v[5] * os, v[6] * os, v[7] * os);
+      o.y = pack8_e2m1(v[8] * os, v[9] * os, v[10] * os, v[11] * os, v[12] * os, v[13] * os, v[14] * os, v[15] * os);
+      st_global_v2_hint(dst + 8 * j, o, policy);
+      sf[nvfp4_sf_offset(m, kb0 + j, sf_swizzled, ld_sf, sf_ktiles)] = (uint8_t)sf8;
     }
   }
 }
@@ -509,7 +554,8 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       __nv_bfloat16* yrow_tile = a.y + (long long)row * a.ldy + col0;
       const bool wide = a.wide_store != 0;  // every 16-column group of every row starts on a 32-byte boundary
       const float row_scale_m = (a.row_scale != nullptr && row_ok) ? __ldg(a.row_scale + row) : 1.0f;
-      const float out_inv_scale = (a.out_scale != nullptr) ? 1.0f / __ldg(a.out_scale) : 1.0f;
+      const float out_gs = (a.out_kind != 0) ? __ldg(a.out_scale) : 1.0f;
+      const float out_inv_scale = 1.0f / out_gs;
 
       if (kCtas == 1 && a.k_splits > 1) {
         // ---- split-K: park this CTA's fp32 partial sums; swiglu_splitk_reduce_kernel finishes the tile
@@ -607,7 +653,16 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
               store_cols_bwd<32>(yrow + c, yrow + a.N + c, dyp, g, u, valid - c, y_policy);
             else
               store_cols_bwd<16>(yrow + c, yrow + a.N + c, dyp, g, u, valid - c, y_policy);
-          } else if (a.out_scale != nullptr) {  // fp8 output: one byte per element
+          } else if (a.out_kind == 2) {  // nvfp4 output: half a byte per element + one scale byte per 16
+            const int colg = col0 + seg * seg_cols + c;
+            uint8_t* y4 = reinterpret_cast<uint8_t*>(a.y) + (long long)row * a.ldy + (colg >> 1);
+            if (w == 32)
+              store_cols_fp4<32>(y4, a.sf, row, colg >> 4, a.sf_swizzled, a.ld_sf, a.sf_ktiles, g, u, valid - c,
+                                 out_gs, out_inv_scale, y_policy);
+            else
+              store_cols_fp4<16>(y4, a.sf, row, colg >> 4, a.sf_swizzled, a.ld_sf, a.sf_ktiles, g, u, valid - c,
+                                 out_gs, out_inv_scale, y_policy);
+          } else if (a.out_kind == 1) {  // fp8 output: one byte per element
             uint8_t* y8 = reinterpret_cast<uint8_t*>(a.y) + (long long)row * a.ldy + col0 + seg * seg_cols + c;
             if (w == 32)
               store_cols_fp8<32>(y8, g, u, valid - c, out_inv_scale, y_policy);

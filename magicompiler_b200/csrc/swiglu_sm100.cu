@@ -111,11 +111,12 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
                         int64_t ldw, int64_t ldy, int device, void* stream_v, int variant, int block_n, int stages,
                         int group_m, int max_ctas, void* workspace, int64_t workspace_bytes, int plain = 0,
                         const float* row_scale = nullptr, const float* out_scale = nullptr, const void* dy = nullptr,
-                        int64_t lddy = 0, void* h = nullptr, int64_t ldh = 0) {
+                        int64_t lddy = 0, void* h = nullptr, int64_t ldh = 0, void* sf = nullptr, int64_t ld_sf = 0,
+                        int sf_swizzled = 0) {
   g_err[0] = 0;
   if (M == 0 && N > 0 && K > 0) return 0;
   if (!x || !w || !y) return fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
-  if (ldx < K || ldw < K || ldy < (plain ? 2 * N : N))
+  if (ldx < K || ldw < K || ldy < (plain ? 2 * N : (sf ? N / 2 : N)))  // an nvfp4 row is N/2 bytes
     return fail(MAGI_SWIGLU_ERR_SHAPE, "row strides too small: ldx=%lld ldw=%lld (K=%lld) ldy=%lld (N=%lld)",
                 (long long)ldx, (long long)ldw, (long long)K, (long long)ldy, (long long)N);
   if (ldx % 8 || ldw % 8 || ldy % 8) return fail(MAGI_SWIGLU_ERR_ALIGN, "row strides must be multiples of 8 elements");
@@ -207,6 +208,11 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   a.plain = plain;
   a.row_scale = row_scale;
   a.out_scale = out_scale;
+  a.out_kind = out_scale ? (sf ? 2 : 1) : 0;
+  a.sf = static_cast<uint8_t*>(sf);
+  a.ld_sf = ld_sf;
+  a.sf_swizzled = sf_swizzled;
+  a.sf_ktiles = (int)((N / 16 + 3) / 4);
   a.dy = static_cast<const __nv_bfloat16*>(dy);
   a.lddy = lddy;
   a.h = static_cast<__nv_bfloat16*>(h);
@@ -402,6 +408,26 @@ int magi_swiglu_forward_fp8_e4m3(const void* x, const void* w_gate_up, void* y_f
   const int variant = MAGI_SWIGLU_VARIANT_AUTO;
   return magi::forward_impl(x, w_gate_up, y_fp8, M, N, K, ldx, ldw, ldy, device, cuda_stream, variant, 0, 0, 0, 0, nullptr,
                             0, 0, nullptr, scale);
+}
+
+int magi_swiglu_forward_nvfp4(const void* x, const void* w_gate_up, void* y_fp4, void* y_scale, const float* global_scale,
+                              int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldy, int64_t ld_scale,
+                              int scale_layout, int device, void* cuda_stream) {
+  magi::g_err[0] = 0;
+  if (M > 0 && (!global_scale || !y_scale)) return magi::fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
+  if (N % 16 != 0 || ldy % 8 != 0 || ldy < N / 2)
+    return magi::fail(MAGI_SWIGLU_ERR_SHAPE,
+                      "nvfp4 output needs N (%lld) to be a multiple of 16 and ldy (%lld bytes) a multiple of 8 >= N/2",
+                      (long long)N, (long long)ldy);
+  if (scale_layout != MAGI_SWIGLU_SCALES_LINEAR && scale_layout != MAGI_SWIGLU_SCALES_SWIZZLED_128X4)
+    return magi::fail(MAGI_SWIGLU_ERR_VARIANT, "unknown scale layout %d", scale_layout);
+  if (scale_layout == MAGI_SWIGLU_SCALES_LINEAR && ld_scale < N / 16)
+    return magi::fail(MAGI_SWIGLU_ERR_SHAPE, "ld_scale=%lld is smaller than N/16=%lld", (long long)ld_scale,
+                      (long long)(N / 16));
+  // No scratch: narrow problems run unsplit (the split-K reduce kernel writes bf16 only).
+  return magi::forward_impl(x, w_gate_up, y_fp4, M, N, K, ldx, ldw, ldy, device, cuda_stream, MAGI_SWIGLU_VARIANT_AUTO, 0,
+                            0, 0, 0, nullptr, 0, 0, nullptr, global_scale, nullptr, 0, nullptr, 0, y_scale, ld_scale,
+                            scale_layout == MAGI_SWIGLU_SCALES_SWIZZLED_128X4);
 }
 
 int magi_swiglu_forward_bf16_preact(const void* x, const void* w_gate_up, void* y, void* h, int64_t M, int64_t N, int64_t K,

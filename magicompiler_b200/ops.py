@@ -294,6 +294,65 @@ def swiglu_backward_dh(x: torch.Tensor, w_gate_up: torch.Tensor, dy: torch.Tenso
     return dh
 
 
+NVFP4_OP_NAME = "magi_swiglu::gemm_swiglu_nvfp4"
+
+
+def nvfp4_scale_shape(rows: int, n: int, swizzled: bool) -> tuple[int, ...]:
+    """Shape of the scale-factor tensor for ``rows`` x ``n`` outputs: ``[rows, n/16]`` linear, or the padded flat
+    buffer of the 128 x 4 tiled layout."""
+    blocks = n // 16
+    if not swizzled:
+        return (rows, blocks)
+    return (-(-rows // 128) * 128 * -(-blocks // 4) * 4,)
+
+
+def _gemm_swiglu_nvfp4_meta(x, w_gate_up, global_scale, swizzled_scales):
+    n = w_gate_up.shape[0] // 2
+    rows = x.numel() // x.shape[-1] if x.dim() != 2 else x.shape[0]
+    blocks = n // 16
+    if swizzled_scales:
+        sf_shape = (((rows + 127) // 128) * 128 * ((blocks + 3) // 4) * 4,)
+    else:
+        sf_shape = (rows, blocks)
+    return (x.new_empty((*x.shape[:-1], n // 2), dtype=torch.uint8),
+            x.new_empty(sf_shape, dtype=torch.float8_e4m3fn))
+
+
+@magi_register_custom_op(name=NVFP4_OP_NAME, mutates_args=(), infer_output_meta_fn=_gemm_swiglu_nvfp4_meta,
+                         is_compute_sensitive=True)
+def gemm_swiglu_nvfp4(x: torch.Tensor, w_gate_up: torch.Tensor, global_scale: torch.Tensor,
+                      swizzled_scales: bool) -> tuple[torch.Tensor, torch.Tensor]:
+    """The fused op with an nvfp4 output (``magi_swiglu_forward_nvfp4``): returns ``(codes, scales)`` —
+    ``codes`` uint8 ``[..., N/2]`` (two e2m1 values per byte, even column in the low nibble) and one e4m3 scale per
+    16 outputs, ``[M, N/16]`` or, with ``swizzled_scales``, the zero-padded 128 x 4 tiled buffer block-scaled GEMMs
+    read.  ``global_scale`` is a one-element fp32 CUDA tensor read by the kernel.  Dequantised value =
+    ``e2m1 * scale / global_scale``.  This is the merged gate/up linear followed by vLLM's
+    ``silu_and_mul_nvfp4_quant`` (magi_compiler/passes/piecewise_graph/fix_functionalization.py:113-120), rounded
+    once from the fp32 accumulators.  N must be a multiple of 16.  Inference only."""
+    M, N, K = _check(x, w_gate_up)
+    if N % 16 != 0:
+        raise ValueError(f"N ({N}) must be a multiple of 16 for the nvfp4 output")
+    if not isinstance(global_scale, torch.Tensor) or global_scale.dtype != torch.float32 or global_scale.numel() != 1:
+        raise TypeError("global_scale must be a one-element fp32 tensor")
+    if global_scale.device != x.device:
+        raise ValueError(f"global_scale is on {global_scale.device} but x is on {x.device}")
+    x2, w2 = _rows_view(x, K), _rows_view(w_gate_up, K)
+    codes = torch.empty((M, N // 2), dtype=torch.uint8, device=x.device)
+    shape = nvfp4_scale_shape(M, N, bool(swizzled_scales))
+    # the tiled layout has padding entries the kernel does not write: hand out zeros there
+    scales = (torch.zeros if swizzled_scales else torch.empty)(shape, dtype=torch.uint8, device=x.device)
+    if M > 0:
+        dev = x.device.index if x.device.index is not None else torch.cuda.current_device()
+        rc = _loader.load_library().magi_swiglu_forward_nvfp4(
+            x2.data_ptr(), w2.data_ptr(), codes.data_ptr(), scales.data_ptr(), global_scale.data_ptr(), M, N, K,
+            x2.stride(0) if M > 1 else K, w2.stride(0), N // 2, N // 16, 1 if swizzled_scales else 0, dev,
+            torch.cuda.current_stream(x.device).cuda_stream)
+        if rc != 0:
+            msg = f"magi_swiglu_forward_nvfp4 failed ({rc}): {_loader.last_error()}"
+            raise (ValueError(msg) if rc < 0 else RuntimeError(msg))
+    return codes.view(*x.shape[:-1], N // 2), scales.view(torch.float8_e4m3fn)
+
+
 PREACT_OP_NAME = "magi_swiglu::gemm_swiglu_preact"
 
 

@@ -17,7 +17,10 @@ fixtures produced by running the reference's own ``TransformerMLP`` (``tests/gol
 from .swiglu_oracle import (  # noqa: F401
     build,
     error_metrics,
+    e2m1_round,
     make_inputs,
+    nvfp4_quantize_gold,
+    nvfp4_swizzled_offsets,
     rmsnorm_swiglu_gold,
     rmsnorm_swiglu_ref_eager,
     swiglu_backward_gold,

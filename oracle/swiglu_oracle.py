@@ -159,3 +159,49 @@ def rmsnorm_swiglu_ref_eager(x: torch.Tensor, norm_weight: torch.Tensor, w: torc
     xn = x * torch.rsqrt(variance + eps)
     xn = (xn.to(norm_weight.dtype) * norm_weight).to(x.dtype)
     return swiglu_ref_eager(xn, w)
+
+
+_E2M1_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def e2m1_round(q: torch.Tensor) -> torch.Tensor:
+    """fp32 -> e2m1 codes (0..15, bit 3 = sign), round to nearest with ties to the even code, saturating at 6."""
+    a = q.abs()
+    code = torch.zeros_like(a, dtype=torch.uint8)
+    # (lower bound, inclusive?) of each magnitude code; a tie goes to the even code
+    for c, (lo, incl) in enumerate([(0.25, False), (0.75, True), (1.25, False), (1.75, True), (2.5, False),
+                                    (3.5, True), (5.0, False)], start=1):
+        code = torch.where((a >= lo) if incl else (a > lo), torch.full_like(code, c), code)
+    return code | ((q < 0) | ((q == 0) & (torch.signbit(q)))).to(torch.uint8) * 8
+
+
+def nvfp4_quantize_gold(y: torch.Tensor, global_scale: float):
+    """NVFP4 quantisation of an fp32 ``[M, N]`` tensor the way vLLM's ``silu_and_mul_nvfp4_quant`` /
+    ``scaled_fp4_quant`` kernels do it (vLLM is not a dependency of MagiCompiler and not part of its checkout; the
+    reference only names the op, magi_compiler/passes/piecewise_graph/fix_functionalization.py:113-120; this follows
+    the published algorithm — parity unpinned: no build of that kernel is available to run beside it):
+    per block of 16 columns  sf = e4m3(gs * max|y| / 6),  code = e2m1(y * (1 / (sf / gs))), zeros when sf == 0.
+    Returns (codes uint8 [M, N] one code per element, sf float8_e4m3fn [M, N/16], dequantised fp32 [M, N])."""
+    M, N = y.shape
+    gs = torch.tensor(global_scale, dtype=torch.float32)
+    yb = y.float().reshape(M, N // 16, 16)
+    vmax = yb.abs().amax(dim=-1)
+    sf = gs * (vmax * torch.tensor(1.0 / 6.0, dtype=torch.float32))
+    sf8 = sf.clamp(max=448.0).to(torch.float8_e4m3fn)
+    sff = sf8.float()
+    inv_gs = torch.tensor(1.0, dtype=torch.float32) / gs
+    out_scale = torch.where(sff != 0, 1.0 / (sff * inv_gs), torch.zeros_like(sff))
+    codes = e2m1_round(yb * out_scale[..., None]).reshape(M, N)
+    mag = torch.tensor(_E2M1_VALUES)[(codes & 7).long()] * torch.where((codes & 8) != 0, -1.0, 1.0)
+    deq = (mag.reshape(M, N // 16, 16) * (sff * inv_gs)[..., None]).reshape(M, N)
+    return codes, sf8, deq
+
+
+def nvfp4_swizzled_offsets(M: int, N: int) -> torch.Tensor:
+    """Byte offset of scale (m, b) in the 128 x 4 tiled layout of block-scale factors: tiles of 128 rows x 4 blocks
+    (512 bytes), tile row r at (r % 32) * 16 + (r / 32) * 4.  Returns int64 [M, N/16]."""
+    m = torch.arange(M).view(M, 1)
+    b = torch.arange(N // 16).view(1, N // 16)
+    ktiles = -(-(N // 16) // 4)
+    r = m % 128
+    return ((m // 128) * ktiles + b // 4) * 512 + (r % 32) * 16 + (r // 32) * 4 + b % 4

@@ -49,6 +49,21 @@ def test_fp8_output_op_schema_and_fake_impl():
                            torch.ones(1))
 
 
+def test_nvfp4_output_op_schema_and_fake_impl():
+    op = torch.ops.magi_swiglu.gemm_swiglu_nvfp4.default
+    assert str(op._schema) == ("magi_swiglu::gemm_swiglu_nvfp4(Tensor x, Tensor w_gate_up, Tensor global_scale, "
+                               "bool swizzled_scales) -> (Tensor, Tensor)")
+    with FakeTensorMode():
+        x = torch.empty(3, 50, 64, dtype=torch.bfloat16, device="cuda")
+        w = torch.empty(2 * 48, 64, dtype=torch.bfloat16, device="cuda")
+        gs = torch.empty(1, dtype=torch.float32, device="cuda")
+        codes, sf = mb.gemm_swiglu_nvfp4(x, w, gs, False)
+        assert tuple(codes.shape) == (3, 50, 24) and codes.dtype == torch.uint8
+        assert tuple(sf.shape) == (150, 3) and sf.dtype == torch.float8_e4m3fn
+        codes, sf = mb.gemm_swiglu_nvfp4(x, w, gs, True)
+        assert tuple(sf.shape) == mb.nvfp4_scale_shape(150, 48, True) == (256 * 4,)
+
+
 def test_fake_impl_with_symbolic_rows():
     from torch.fx.experimental.proxy_tensor import make_fx
 

@@ -111,3 +111,24 @@ def test_rmsnorm_oracle_matches_reference_fixture(golden):
     assert float((to_bits(got) != to_bits(ref)).mean()) <= 1e-3
     m = error_metrics(ref, rmsnorm_swiglu_gold(x, gamma, w, eps))
     assert m["max_norm"] <= TOL_MAX_NORM and m["frob"] <= TOL_FROB, m
+
+
+def test_nvfp4_gold_rounding_table_and_layout():
+    """Known answers of the e2m1 grid (round to nearest, ties to the even code, saturation at 6) and the 128 x 4
+    tiled scale layout (a bijection onto a buffer of padded size)."""
+    from oracle import e2m1_round, nvfp4_quantize_gold, nvfp4_swizzled_offsets
+
+    q = torch.tensor([0.0, 0.25, 0.26, 0.5, 0.75, 1.0, 1.25, 1.26, 1.75, 2.5, 2.6, 3.5, 5.0, 5.1, 100.0, -0.3, -7.0])
+    assert e2m1_round(q).tolist() == [0, 0, 1, 1, 2, 2, 2, 3, 4, 4, 5, 6, 6, 7, 7, 9, 15]
+    y = torch.zeros(4, 32)
+    y[0, :16] = torch.linspace(-6, 6, 16)
+    y[1, 16:] = 3.0
+    codes, sf, deq = nvfp4_quantize_gold(y, 1.0)
+    assert sf.float().tolist() == [[1.0, 0.0], [0.0, 0.5], [0.0, 0.0], [0.0, 0.0]]
+    assert (codes[2:] == 0).all() and (codes[1, 16:] == 7).all() and torch.equal(deq[1, 16:], torch.full((16,), 3.0))
+    assert codes[0, 0] == 15 and codes[0, 15] == 7
+    for M, N in ((1, 16), (130, 208), (256, 2816)):
+        off = nvfp4_swizzled_offsets(M, N)
+        size = -(-M // 128) * 128 * -(-(N // 16) // 4) * 4
+        assert off.unique().numel() == off.numel() and 0 <= off.min() and off.max() < size
+    assert nvfp4_swizzled_offsets(256, 128)[33, 5].item() == (0 * 2 + 1) * 512 + 1 * 16 + 1 * 4 + 1

@@ -105,9 +105,69 @@ def _is_bf16_on(devices: tuple[str, ...], *nodes: torch.fx.Node) -> bool:
     return True
 
 
+_CHUNK_FUNCS = {torch.chunk, torch.split, torch.functional.split, torch.Tensor.chunk, torch.Tensor.split}
+
+
+def _last_dim(node: torch.fx.Node):
+    ev = _example(node)
+    return int(ev.shape[-1]) if isinstance(ev, torch.Tensor) and isinstance(ev.shape[-1], int) else None
+
+
+def _half_of(node: torch.fx.Node):
+    """If ``node`` is the first or second half of another node's last dimension — ``h.chunk(2, -1)[i]``,
+    ``h.split(N, -1)[i]`` or ``h[..., :N]`` / ``h[..., N:]`` with N half the width — returns
+    ``(h, i, helper nodes)``; otherwise None."""
+    if node.op != "call_function" or node.target is not operator.getitem or len(node.args) != 2:
+        return None
+    src, idx = node.args
+    if not isinstance(src, torch.fx.Node):
+        return None
+    if isinstance(idx, int) and idx in (0, 1):  # an element of chunk(...) / split(...)
+        is_fn = src.op == "call_function" and src.target in _CHUNK_FUNCS
+        is_method = src.op == "call_method" and src.target in ("chunk", "split")
+        if not (is_fn or is_method) or not src.args or not isinstance(src.args[0], torch.fx.Node):
+            return None
+        h = src.args[0]
+        arg = src.args[1] if len(src.args) > 1 else src.kwargs.get("chunks", src.kwargs.get("split_size_or_sections"))
+        dim = src.args[2] if len(src.args) > 2 else src.kwargs.get("dim", 0)
+        ev = _example(h)
+        rank = ev.dim() if isinstance(ev, torch.Tensor) else None
+        if not (dim == -1 or (rank is not None and dim == rank - 1)):
+            return None
+        name = src.target if isinstance(src.target, str) else getattr(src.target, "__name__", "")
+        if name == "chunk":
+            if arg != 2:
+                return None
+        else:  # split: exactly two pieces of half the width
+            width = _last_dim(h)
+            if width is None or not isinstance(arg, int) or 2 * arg != width:
+                return None
+        return h, idx, (src,)
+    if isinstance(idx, tuple) and idx and isinstance(idx[-1], slice):  # h[..., :N] / h[:, N:]
+        lead, last = idx[:-1], idx[-1]
+        if not all(e is Ellipsis or (isinstance(e, slice) and e == slice(None)) for e in lead):
+            return None
+        ev = _example(src)
+        if not isinstance(ev, torch.Tensor):
+            return None
+        if Ellipsis not in lead and len(idx) != ev.dim():
+            return None
+        width = _last_dim(src)
+        if width is None or width % 2 or last.step not in (None, 1):
+            return None
+        half = width // 2
+        if last.start in (None, 0) and last.stop == half:
+            return src, 0, ()
+        if last.start == half and last.stop in (None, width):
+            return src, 1, ()
+    return None
+
+
 class FuseSwiGLUPass(_PassBase):
     """Rewrites every ``silu(linear(x, Wg)) * linear(x, Wu)`` (either operand order, bias-free linears that share
-    ``x``) of a Dynamo-level FX graph into ``gemm_swiglu(x, pack_gate_up_cached(Wg, Wu))``.
+    ``x``) of a Dynamo-level FX graph into ``gemm_swiglu(x, pack_gate_up_cached(Wg, Wu))``, and the merged-projection
+    form ``h = linear(x, W); silu(h[..., :N]) * h[..., N:]`` (``chunk``, ``split`` or slices; the SiluAndMul layout of
+    the ops magi_compiler/passes/piecewise_graph/fix_functionalization.py:100-125 handles) into ``gemm_swiglu(x, W)``.
 
     ``allowed_devices``: device types of the traced tensors for which the rewrite is made (the kernel exists for
     CUDA; "meta" lets shape-only traces through; tests that stand a CPU function in for the kernel add "cpu").
@@ -150,8 +210,44 @@ class FuseSwiGLUPass(_PassBase):
                 break
         return found
 
+    def _matches_merged(self, graph: torch.fx.Graph):
+        """``h = linear(x, W_gate_up); silu(h[..., :N]) * h[..., N:]`` (chunk, split or slices): the merged-projection
+        form, whose weight is already packed gate rows first."""
+        found = []
+        for mul in graph.nodes:
+            is_mul = (mul.op == "call_function" and mul.target in _MUL_TARGETS) or \
+                     (mul.op == "call_method" and mul.target == "mul")
+            if not is_mul or len(mul.args) != 2 or not all(isinstance(a, torch.fx.Node) for a in mul.args):
+                continue
+            for act, up in (mul.args, mul.args[::-1]):
+                is_silu = (act.op == "call_function" and act.target in _SILU_TARGETS) or \
+                          (act.op == "call_method" and act.target == "silu")
+                if not is_silu or not act.args or not isinstance(act.args[0], torch.fx.Node):
+                    continue
+                gate = act.args[0]
+                hg, hu = _half_of(gate), _half_of(up)
+                if hg is None or hu is None or hg[0] is not hu[0] or (hg[1], hu[1]) != (0, 1):
+                    continue
+                lin = hg[0]
+                helpers = tuple(dict.fromkeys(hg[2] + hu[2]))
+                if not _is_linear_without_bias(lin) or not isinstance(lin.args[1], torch.fx.Node):
+                    continue
+                if len(act.users) != 1 or len(gate.users) != 1 or len(up.users) != 1:
+                    continue
+                inner = set(helpers) | {gate, up}
+                if any(u not in inner for u in lin.users) or any(u not in (gate, up) for hn in helpers for u in hn.users):
+                    continue  # the merged projection (or a piece of it) is used elsewhere: it must stay
+                if not _is_bf16_on(self.allowed_devices, lin.args[0], lin.args[1]):
+                    continue
+                evw = _example(lin.args[1])
+                if isinstance(evw, torch.Tensor) and (evw.dim() != 2 or evw.shape[0] % 16 or evw.shape[1] % 8):
+                    continue
+                found.append((mul, act, gate, up, helpers, lin))
+                break
+        return found
+
     def is_applicable(self, graph: torch.fx.Graph, shape: int | None = None) -> bool:
-        return bool(self._matches(graph))
+        return bool(self._matches(graph)) or bool(self._matches_merged(graph))
 
     def __call__(self, graph: torch.fx.Graph) -> int:
         from .ops import gemm_swiglu  # registers the op
@@ -177,6 +273,23 @@ class FuseSwiGLUPass(_PassBase):
                     pass
             mul.replace_all_uses_with(fused)
             for dead in (mul, act, gate, up):
+                graph.erase_node(dead)
+            count += 1
+        for mul, act, gate, up, helpers, lin in self._matches_merged(graph):
+            x, packed = lin.args[0], lin.args[1]
+            with graph.inserting_before(mul):
+                if self.save_preactivations:
+                    both = graph.call_function(torch.ops.magi_swiglu.gemm_swiglu_preact.default, (x, packed))
+                    fused = graph.call_function(operator.getitem, (both, 0))
+                else:
+                    fused = graph.call_function(torch.ops.magi_swiglu.gemm_swiglu.default, (x, packed))
+            try:
+                ex, ep = _example(x), _example(packed)
+                fused.meta["example_value"] = ex.new_empty((*ex.shape[:-1], ep.shape[0] // 2))
+            except Exception:
+                pass
+            mul.replace_all_uses_with(fused)
+            for dead in (mul, act, gate, up, *helpers, lin):
                 graph.erase_node(dead)
             count += 1
         if count:

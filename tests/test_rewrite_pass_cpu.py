@@ -75,6 +75,49 @@ def test_training_variant_emits_the_two_output_op():
     assert tuple(y.shape) == (3, 10, 64) and y.dtype == torch.bfloat16
 
 
+class MergedMLP(torch.nn.Module):
+    """One merged gate/up projection followed by SiluAndMul: the layout of vLLM-style models whose activation ops
+    the reference handles in magi_compiler/passes/piecewise_graph/fix_functionalization.py:100-125."""
+
+    def __init__(self, form, k=64, n=96):
+        super().__init__()
+        self.gate_up_proj = torch.nn.Linear(k, 2 * n, bias=False, dtype=torch.bfloat16, device="meta")
+        self.form, self.n = form, n
+
+    def forward(self, x):
+        h, n = self.gate_up_proj(x), self.n
+        if self.form == "chunk":
+            a, b = h.chunk(2, dim=-1)
+        elif self.form == "torch.chunk":
+            a, b = torch.chunk(h, 2, -1)
+        elif self.form == "split":
+            a, b = h.split(n, dim=-1)
+        elif self.form == "slice":
+            a, b = h[..., :n], h[..., n:]
+        elif self.form == "uneven":
+            a, b = h[..., : n - 8], h[..., n - 8: 2 * n - 16]
+        elif self.form == "up_first":
+            b, a = h.chunk(2, dim=-1)
+        elif self.form == "reused":
+            a, b = h.chunk(2, dim=-1)
+            return F.silu(a) * b + h.sum()
+        return F.silu(a) * b
+
+
+@pytest.mark.parametrize("form", ["chunk", "torch.chunk", "split", "slice"])
+def test_merged_projection_form_is_rewritten_without_packing(form):
+    seen, y = run_pass(MergedMLP(form), torch.empty(2, 5, 64, dtype=torch.bfloat16, device="meta"))
+    assert seen["count"] == 1 and seen["after"].count(GEMM) == 1 and PACK not in seen["after"]
+    assert F.silu not in seen["after"] and not any(t in (F.linear, torch._C._nn.linear) for t in seen["after"])
+    assert tuple(y.shape) == (2, 5, 96) and y.dtype == torch.bfloat16
+
+
+@pytest.mark.parametrize("form", ["uneven", "up_first", "reused"])
+def test_merged_projection_lookalikes_are_left_alone(form):
+    seen, _ = run_pass(MergedMLP(form), torch.empty(10, 64, dtype=torch.bfloat16, device="meta"))
+    assert seen["count"] == 0 and GEMM not in seen["after"]
+
+
 def test_operand_order_and_leading_dims():
     seen, y = run_pass(MLP(swap=True), torch.empty(2, 5, 64, dtype=torch.bfloat16, device="meta"))
     assert seen["count"] == 1 and tuple(y.shape) == (2, 5, 64)

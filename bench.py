@@ -48,7 +48,7 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (bytes; key = workload@gpus).
 NCU_TRAFFIC = {
-    "llama3_8b_ffn@1": 976.2e6,   # profiles/swiglu_tc_kernel_pair_llama3_8b_ffn.md
+    "llama3_8b_ffn@1": 978.2e6,   # profiles/swiglu_tc_kernel_pair_llama3_8b_ffn.md
     "video_dit_ffn@1": 8377.7e6,
     "decode_m64@1": 946.7e6,     # profiles/swiglu_tc_kernel_stream_decode_m64.md
 }

@@ -140,6 +140,38 @@ def test_forward_rejects_bad_arguments_before_touching_a_device(lib):
         assert call() == -5           # valid arguments, but no sm_100 device: refused, never a CPU fallback
 
 
+def test_other_entry_points_reject_bad_arguments_on_the_host(lib):
+    """fp8 / nvfp4 outputs, the training forward and the fused backward validate before any device is touched."""
+    buf = (ctypes.c_char * 8192)()
+    b = ctypes.addressof(buf)
+    b += (-b) % 16
+    fp8, fp4 = lib.magi_swiglu_forward_fp8_e4m3, lib.magi_swiglu_forward_nvfp4
+    pre, bwd = lib.magi_swiglu_forward_bf16_preact, lib.magi_swiglu_backward_dh_bf16
+    # fp8: scale pointer, N % 16, ldy % 16
+    assert fp8(b, b, b, None, 8, 16, 8, 8, 8, 16, 0, None) == -1
+    assert fp8(b, b, b, b, 8, 8, 8, 8, 8, 16, 0, None) == -2 and "multiples of 16" in _loader.last_error()
+    assert fp8(b, b, b, b, 8, 16, 8, 8, 8, 24, 0, None) == -2
+    assert fp8(b, b, b, b, 0, 16, 8, 8, 8, 16, 0, None) == 0  # empty batch
+    # nvfp4: pointers, N % 16, row bytes, layout id, linear scale stride
+    assert fp4(b, b, b, None, b, 8, 16, 8, 8, 8, 8, 1, 0, 0, None) == -1
+    assert fp4(b, b, b, b, None, 8, 16, 8, 8, 8, 8, 1, 0, 0, None) == -1
+    assert fp4(b, b, b, b, b, 8, 24, 8, 8, 8, 16, 2, 0, 0, None) == -2
+    assert fp4(b, b, b, b, b, 8, 32, 8, 8, 8, 8, 2, 0, 0, None) == -2   # a row of 32 codes is 16 bytes
+    assert fp4(b, b, b, b, b, 8, 32, 8, 8, 8, 16, 2, 7, 0, None) == -4 and "layout" in _loader.last_error()
+    assert fp4(b, b, b, b, b, 8, 32, 8, 8, 8, 16, 1, 0, 0, None) == -2  # two blocks per row need ld_scale >= 2
+    assert fp4(b, b, b, b, b, 8, 32, 8, 8, 8, 16, 2, 0, 1000, None) == -5
+    # training forward: h pointer, width and alignment
+    assert pre(b, b, b, None, 8, 8, 8, 8, 8, 8, 16, 0, None) == -1
+    assert pre(b, b, b, b, 8, 8, 8, 8, 8, 8, 8, 0, None) == -2          # ldh < 2N
+    assert pre(b, b, b, b + 8, 8, 8, 8, 8, 8, 8, 16, 0, None) == -3
+    # fused backward: dy pointer, strides
+    assert bwd(b, b, None, b, 8, 8, 8, 8, 8, 8, 16, 0, None) == -1
+    assert bwd(b, b, b, b, 8, 8, 8, 8, 8, 4, 16, 0, None) == -2         # lddy < N
+    assert bwd(b, b, b, b, 8, 8, 8, 8, 8, 8, 8, 0, None) == -2          # lddh < 2N
+    assert bwd(b, b, b, b, 8, 8, 8, 8, 8, 12, 16, 0, None) == -3        # lddy % 8
+    assert bwd(b, b, b, b, 8, 8, 8, 8, 8, 8, 16, 1000, None) == -5
+
+
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_loader, "_lib", None)
     monkeypatch.setattr(_loader, "LIB_PATH", tmp_path / "libmagi_swiglu.so")

@@ -177,6 +177,18 @@ int magi_swiglu_forward_nvfp4(const void* x, const void* w_gate_up, void* y_fp4,
 int magi_swiglu_gemm_nt_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,
                       int64_t lda, int64_t ldb, int64_t ldc, int device, void* cuda_stream);
 
+/* The same plain GEMM with either operand stored the other way round, C[M,N] = op(A) · op(B)^T in bf16:
+ *   a_layout 0: A is [M, K] (row stride lda);  1: A is stored [K, M] (its transpose, row stride lda, M % 8 == 0);
+ *   b_layout 0: B is [N, K] (row stride ldb);  1: B is stored [K, N] (row stride ldb).
+ * With layout 1 the operand tile is MN-major in shared memory (tensor-map boxes of 64 columns x 64 reduction rows,
+ * operand descriptors and the MMA's major bits say so); nothing is transposed in memory.  N % 16 == 0, K % 8 == 0
+ * when K is a contiguous index, strides multiples of 8, 16-byte aligned pointers.
+ * Used for the two gradient GEMMs of the backward: dX = dH · W (b_layout 1) and dW = dH^T · X (both 1).
+ * Replaces: the matmuls PyTorch's autograd runs for the two projections of tests/model_definition.py:337-339. */
+int magi_swiglu_gemm_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,
+                          int64_t lda, int64_t ldb, int64_t ldc, int a_layout, int b_layout,
+                          int device, void* cuda_stream);
+
 /* Backward of the activation.  h is [M, 2N] = [G | U], the pre-activations X·Wg^T and X·Wu^T (bf16, row stride ldh),
  * dy is [M, N]; writes dh = [dG | dU] ([M, 2N], row stride lddh) with dG = dY*U*s*(1 + G*(1-s)), dU = dY*G*s,
  * s = sigmoid(G); fp32 arithmetic, one rounding.  The GEMMs around it (recomputing h, dX = dH·W, dW = dH^T·X) are

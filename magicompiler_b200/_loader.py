@@ -93,6 +93,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.magi_swiglu_forward_bf16_preact.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, i32, vp]
     lib.magi_swiglu_backward_dh_bf16.restype = i32
     lib.magi_swiglu_backward_dh_bf16.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, i32, vp]
+    lib.magi_swiglu_gemm_bf16.restype = i32
+    lib.magi_swiglu_gemm_bf16.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, i32, vp]
     lib.magi_swiglu_gemm_nt_bf16.restype = i32
     lib.magi_swiglu_gemm_nt_bf16.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, vp]
     lib.magi_swiglu_backward_act_bf16.restype = i32

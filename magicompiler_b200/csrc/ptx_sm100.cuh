@@ -324,12 +324,27 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
   return d;
 }
 
-// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, dense, MMA shape m x n (x16).
-__host__ __device__ __forceinline__ uint32_t umma_idesc_bf16(uint32_t m, uint32_t n) {
+// Shared-memory descriptor of an MN-major operand tile stored with the 128-byte swizzle: blocks of 64 MN elements
+// (one 128-byte row per K index), 64 K rows per block (8 KB), blocks of consecutive MN ranges 8 KB apart.  The start
+// address selects the 16 K rows of one MMA (2048 bytes per step).
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(8192 >> 4) << 16;  // leading-dimension offset: next block of 64 MN elements
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;  // stride offset: next group of 8 K rows
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+// Instruction descriptor: bf16 x bf16 -> fp32, dense, MMA shape m x n (x16); a_mn / b_mn = 1 when that operand's
+// tile is MN-major in shared memory (0 = K-major).
+__host__ __device__ __forceinline__ uint32_t umma_idesc_bf16(uint32_t m, uint32_t n, uint32_t a_mn = 0,
+                                                             uint32_t b_mn = 0) {
   return (1u << 4)        // D format fp32
          | (1u << 7)      // A format bf16
          | (1u << 10)     // B format bf16
-         | ((n >> 3) << 17) | ((m >> 4) << 24);
+         | (a_mn << 15) | (b_mn << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
 }  // namespace magi

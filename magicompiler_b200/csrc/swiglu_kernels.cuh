@@ -93,6 +93,8 @@ struct KArgs {
   long long ld_sf;         // linear layout: bytes per row of sf
   int sf_swizzled;         // 1: 128 x 4 tiled layout
   int sf_ktiles;
+  int a_mn, b_mn;     // plain GEMM only: 1 = that operand is stored with the reduction index as the ROW index
+                      // (A as [K, M], B as [K, N]), so its shared-memory tile is MN-major
   int plain;          // 1: plain GEMM C = A·B^T; B's first N rows fill output columns [0,N), its last N rows [N,2N)
   int x_hint, w_hint, y_hint;  // L2 eviction priority of X tiles, W tiles and Y stores: 0 normal, 1 first, 2 last
   // Split-K (STREAM schedule on narrow weights): k_splits CTAs share one tile, each sums kb_per_split K-steps and
@@ -402,7 +404,36 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
           const uint32_t st_a = tiles_base + stage * a.stage_bytes;  // X tile of this stage
           const uint32_t st_b = st_a + kABytes;                     // W rows of this stage
           const int k0 = kb * kBK;  // past the end of K the copy is zero-filled
-          if constexpr (kCtas == 1) {
+          if (x_role && a.a_mn) {
+            // A stored [K, M]: two boxes of 64 rows-of-A x 64 K (8 KB each, one 128-byte line per K index)
+#pragma unroll
+            for (int i = 0; i < kBM / 64; ++i) {
+              if constexpr (kCtas == 1)
+                tma_load_2d_hint(st_a + i * 8192, &tm_x, bar, row0 + 64 * i, k0, policy);
+              else
+                tma_load_2d_pair_hint(st_a + i * 8192, &tm_x, bar, row0 + 64 * i, k0, policy);
+            }
+          } else if (!x_role && a.b_mn) {
+            // B stored [K, 2N]: this CTA's columns of the first half, then of the second half, 64 at a time.
+            // One CTA: block_n columns of each half.  Pair: rank r brings all block_n columns of half r (one MMA
+            // over both halves, or split mode), else half of the columns of each half.
+            const int nb = a.block_n / 64;  // block_n is a multiple of 64 in this mode
+            for (int i = 0; i < 2 * nb / kCtas; ++i) {
+              int col;
+              if constexpr (kCtas == 1) {
+                col = (i / nb) * a.N + nt * a.block_n + 64 * (i % nb);
+              } else if (a.n_mma == 1 || a.split) {
+                col = (int)cta_rank * a.N + nt * a.block_n + 64 * i;
+              } else {
+                const int hb = nb / 2;
+                col = (i / hb) * a.N + nt * a.block_n + (int)cta_rank * (a.block_n / 2) + 64 * (i % hb);
+              }
+              if constexpr (kCtas == 1)
+                tma_load_2d_hint(st_b + i * 8192, &tm_w, bar, col, k0, policy);
+              else
+                tma_load_2d_pair_hint(st_b + i * 8192, &tm_w, bar, col, k0, policy);
+            }
+          } else if constexpr (kCtas == 1) {
             if (x_role)
               tma_load_2d_hint(st_a, &tm_x, bar, k0, row0, policy);
             else
@@ -426,7 +457,16 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && cta_rank == 0) {
       const uint32_t mma_n = (a.n_mma == 1) ? 2u * a.block_n : (uint32_t)a.block_n;
-      const uint32_t idesc = umma_idesc_bf16(kBM * kCtas, mma_n);
+      const uint32_t idesc = umma_idesc_bf16(kBM * kCtas, mma_n, (uint32_t)a.a_mn, (uint32_t)a.b_mn);
+      // operand descriptors of the k-th 16-wide K step of a stage (K-major: 32 bytes further along each row;
+      // MN-major: 16 rows = 2048 bytes further)
+      const bool a_mn = a.a_mn != 0, b_mn = a.b_mn != 0;
+      auto desc_a = [&](uint32_t base, int k) {
+        return a_mn ? umma_desc_mn_sw128(base + k * 2048) : umma_desc_k_sw128(base + k * 32);
+      };
+      auto desc_b = [&](uint32_t base, int k) {
+        return b_mn ? umma_desc_mn_sw128(base + k * 2048) : umma_desc_k_sw128(base + k * 32);
+      };
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -462,8 +502,7 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
             const uint32_t sa = tiles_base + s2 * a.stage_bytes;
 #pragma unroll
             for (int k = 0; k < kBK / 16; ++k)
-              umma_bf16<kCtas>(d_gate, umma_desc_k_sw128(sa + k * 32), umma_desc_k_sw128(sa + kABytes + k * 32), idesc,
-                               (uint32_t)((j | k) != 0));
+              umma_bf16<kCtas>(d_gate, desc_a(sa, k), desc_b(sa + kABytes, k), idesc, (uint32_t)((j | k) != 0));
             if (++s2 == a.stages) {
               s2 = 0;
               p2 ^= 1u;
@@ -476,8 +515,8 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
             const uint32_t sa = tiles_base + stage * a.stage_bytes;
 #pragma unroll
             for (int k = 0; k < kBK / 16; ++k)
-              umma_bf16<kCtas>(d_gate + a.block_n, umma_desc_k_sw128(sa + k * 32),
-                               umma_desc_k_sw128(sa + kABytes + a.b_second + k * 32), idesc, (uint32_t)((j | k) != 0));
+              umma_bf16<kCtas>(d_gate + a.block_n, desc_a(sa, k), desc_b(sa + kABytes + a.b_second, k), idesc,
+                               (uint32_t)((j | k) != 0));
             umma_commit<kCtas>(empty_bar(stage));
             if (++stage == a.stages) {
               stage = 0;
@@ -505,10 +544,9 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
 #pragma unroll
             for (int k = 0; k < kBK / 16; ++k) {
               const uint32_t acc = ((kb - kb0) | k) != 0;
-              const uint64_t ad = umma_desc_k_sw128(sa + k * 32);
-              umma_bf16<kCtas>(d_gate, ad, umma_desc_k_sw128(sb + k * 32), idesc, acc);
-              if (a.n_mma == 2)
-                umma_bf16<kCtas>(d_gate + a.block_n, ad, umma_desc_k_sw128(sb + a.b_second + k * 32), idesc, acc);
+              const uint64_t ad = desc_a(sa, k);
+              umma_bf16<kCtas>(d_gate, ad, desc_b(sb, k), idesc, acc);
+              if (a.n_mma == 2) umma_bf16<kCtas>(d_gate + a.block_n, ad, desc_b(sb + a.b_second, k), idesc, acc);
             }
             MAGI_TRACE_ADD(10);  // issuer: cycles spent issuing MMAs
           }

@@ -54,11 +54,28 @@ static const DeviceInfo* device_info(int device) {
   }
   return d.queried == 1 ? &d : nullptr;
 }
+// A 2-D map over a matrix stored with the reduction index as the row index ([K, cols], row stride ld elements):
+// boxes of 64 columns x 64 K rows, i.e. one 128-byte swizzled line per K index (the MN-major operand tile).
+static int encode_mn_major_map(EncodeTiledFn enc, const void* ptr, int64_t cols, int64_t K, int64_t ld, CUtensorMap* tm,
+                               const char* what) {
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)K};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)kBK};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MAGI_SWIGLU_ERR_DRIVER, "tensor map for %s rejected by the driver (CUresult %d)", what, (int)r);
+  return 0;
+}
+
 static int encode_maps(const void* x, const void* w, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw,
-                       const Plan& p, CUtensorMap* tm_x, CUtensorMap* tm_w) {
+                       const Plan& p, CUtensorMap* tm_x, CUtensorMap* tm_w, int a_mn = 0, int b_mn = 0) {
   EncodeTiledFn enc = tensor_map_encoder();
   if (!enc) return fail(MAGI_SWIGLU_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from the driver");
-  {
+  if (a_mn) {
+    if (int rc = encode_mn_major_map(enc, x, M, K, ldx, tm_x, "A ([K, M])")) return rc;
+  } else {
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
     const cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};
     const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)kBM};
@@ -68,7 +85,9 @@ static int encode_maps(const void* x, const void* w, int64_t M, int64_t N, int64
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(MAGI_SWIGLU_ERR_DRIVER, "tensor map for X rejected by the driver (CUresult %d)", (int)r);
   }
-  {
+  if (b_mn) {
+    if (int rc = encode_mn_major_map(enc, w, 2 * N, K, ldw, tm_w, "B ([K, N])")) return rc;
+  } else {
     // W viewed as [2][N][K].  One CTA per tile: one box brings block_n gate rows and the matching block_n up
     // rows.  CTA pair: each CTA brings half of the MMA's weight rows — all gate rows or all up rows when one
     // MMA covers gate|up or the tile is split in halves, else half of each.
@@ -112,11 +131,12 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
                         int group_m, int max_ctas, void* workspace, int64_t workspace_bytes, int plain = 0,
                         const float* row_scale = nullptr, const float* out_scale = nullptr, const void* dy = nullptr,
                         int64_t lddy = 0, void* h = nullptr, int64_t ldh = 0, void* sf = nullptr, int64_t ld_sf = 0,
-                        int sf_swizzled = 0) {
+                        int sf_swizzled = 0, int a_mn = 0, int b_mn = 0) {
   g_err[0] = 0;
   if (M == 0 && N > 0 && K > 0) return 0;
   if (!x || !w || !y) return fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
-  if (ldx < K || ldw < K || ldy < (plain ? 2 * N : (sf ? N / 2 : N)))  // an nvfp4 row is N/2 bytes
+  // an operand stored [K, cols] has rows of `cols` elements; an nvfp4 output row is N/2 bytes
+  if (ldx < (a_mn ? M : K) || ldw < (b_mn ? 2 * N : K) || ldy < (plain ? 2 * N : (sf ? N / 2 : N)))
     return fail(MAGI_SWIGLU_ERR_SHAPE, "row strides too small: ldx=%lld ldw=%lld (K=%lld) ldy=%lld (N=%lld)",
                 (long long)ldx, (long long)ldw, (long long)K, (long long)ldy, (long long)N);
   if (ldx % 8 || ldw % 8 || ldy % 8) return fail(MAGI_SWIGLU_ERR_ALIGN, "row strides must be multiples of 8 elements");
@@ -150,7 +170,12 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   }
 
   CUtensorMap tm_x, tm_w;
-  rc = encode_maps(x, w, M, N, K, ldx, ldw, p, &tm_x, &tm_w);
+  if ((a_mn || b_mn) && (p.variant != MAGI_SWIGLU_VARIANT_MMA && p.variant != MAGI_SWIGLU_VARIANT_MMA2))
+    return fail(MAGI_SWIGLU_ERR_VARIANT, "transposed operands need a tile schedule");
+  // an MN-major B tile is made of blocks of 64 columns: every MMA must start on a block and cover whole blocks per CTA
+  if (b_mn && (p.block_n % 64 != 0 || (p.n_mma == 2 && p.block_n % 128 != 0)))
+    return fail(MAGI_SWIGLU_ERR_VARIANT, "a B operand stored [K, N] needs a tile width of 64, 128 or 256 (got %d)", p.block_n);
+  rc = encode_maps(x, w, M, N, K, ldx, ldw, p, &tm_x, &tm_w, a_mn, b_mn);
   if (rc) return rc;
 
   int pair_clusters = 0;
@@ -206,6 +231,8 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   a.acc_bufs = p.acc_bufs;
   a.wide_store = (((uintptr_t)y & 31u) == 0 && ldy % 16 == 0 && (!plain || N % 16 == 0)) ? 1 : 0;
   a.plain = plain;
+  a.a_mn = a_mn;
+  a.b_mn = b_mn;
   a.row_scale = row_scale;
   a.out_scale = out_scale;
   a.out_kind = out_scale ? (sf ? 2 : 1) : 0;
@@ -469,6 +496,37 @@ int magi_swiglu_gemm_nt_bf16(const void* a, const void* b, void* c, int64_t M, i
   // (the streaming schedule's split-K reduce applies the activation).
   const int variant = (M <= 128) ? MAGI_SWIGLU_VARIANT_MMA : MAGI_SWIGLU_VARIANT_MMA2;
   return magi::forward_impl(a, b, c, M, N / 2, K, lda, ldb, ldc, device, cuda_stream, variant, 0, 0, 0, 0, nullptr, 0, 1);
+}
+
+int magi_swiglu_gemm_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                          int64_t ldc, int a_layout, int b_layout, int device, void* cuda_stream) {
+  magi::g_err[0] = 0;
+  if (N <= 0 || N % 16 != 0)
+    return magi::fail(MAGI_SWIGLU_ERR_SHAPE, "magi_swiglu_gemm_bf16 needs N (%lld) to be a positive multiple of 16", (long long)N);
+  if ((a_layout != 0 && a_layout != 1) || (b_layout != 0 && b_layout != 1))
+    return magi::fail(MAGI_SWIGLU_ERR_VARIANT, "operand layouts must be 0 (reduction index contiguous) or 1 (stored [K, rows])");
+  if (a_layout == 1 && M % 8 != 0)
+    return magi::fail(MAGI_SWIGLU_ERR_SHAPE, "an A operand stored [K, M] needs M (%lld) to be a multiple of 8", (long long)M);
+  const int variant = (M <= 128) ? MAGI_SWIGLU_VARIANT_MMA : MAGI_SWIGLU_VARIANT_MMA2;
+  int block_n = 0;
+  if (b_layout == 1) {
+    // tile widths an MN-major B tile allows: 256 (two MMAs per step, pairs only), 128, 64
+    const int64_t half = N / 2;
+    if (half < 128) {
+      block_n = 64;
+    } else if (variant == MAGI_SWIGLU_VARIANT_MMA) {
+      block_n = 128;
+    } else {
+      const magi::DeviceInfo* di = magi::device_info(device);
+      const int64_t units = di ? di->sm_count / 2 : 74;
+      const int64_t m_units = (M + 2 * magi::kBM - 1) / (2 * magi::kBM);
+      const int64_t c256 = ((m_units * ((half + 255) / 256) + units - 1) / units) * (256 + 146);
+      const int64_t c128 = ((m_units * ((half + 127) / 128) + units - 1) / units) * (128 + 146);
+      block_n = (c256 <= c128) ? 256 : 128;
+    }
+  }
+  return magi::forward_impl(a, b, c, M, N / 2, K, lda, ldb, ldc, device, cuda_stream, variant, block_n, 0, 0, 0, nullptr, 0,
+                            1, nullptr, nullptr, nullptr, 0, nullptr, 0, nullptr, 0, 0, a_layout, b_layout);
 }
 
 int magi_swiglu_backward_act_bf16(const void* h, const void* dy, void* dh, int64_t M, int64_t N, int64_t ldh,

@@ -37,6 +37,18 @@ def test_backward_op_schema_and_fake_impl():
         assert dh.shape == (10, 96) and dh.dtype == torch.bfloat16
 
 
+def test_transposed_gemm_op_schema_and_fake_impl():
+    op = torch.ops.magi_swiglu.gemm_bf16.default
+    assert str(op._schema) == "magi_swiglu::gemm_bf16(Tensor a, Tensor b, bool a_is_km, bool b_is_kn) -> Tensor"
+    with FakeTensorMode():
+        dh = torch.empty(40, 96, dtype=torch.bfloat16, device="cuda")
+        w = torch.empty(96, 64, dtype=torch.bfloat16, device="cuda")
+        x = torch.empty(40, 64, dtype=torch.bfloat16, device="cuda")
+        assert mb.gemm_bf16(dh, w, False, True).shape == (40, 64)      # dX = dH · W
+        assert mb.gemm_bf16(dh, x, True, True).shape == (96, 64)       # dW = dH^T · X
+        assert mb.gemm_bf16(x, w, False, False).shape == (40, 96)      # X · W^T
+
+
 def test_autograd_graph_through_fake_tensors():
     """The forward op carries an autograd formula built from library GEMMs and the backward op: gradients of the
     right shapes come back for x and for the packed weight (meta tensors: nothing runs on a device)."""

@@ -108,8 +108,15 @@ def _grad_errors(got, gold):
     return error_metrics(got, gold)
 
 
-@pytest.mark.parametrize("shape", [(256, 512, 384), (300, 328, 520), (64, 1024, 2816), (4096, 1024, 2048)])
-def test_backward_against_fp32_gold_and_reference_autograd(shape):
+@pytest.fixture(params=["library", "own"])
+def gradient_gemms(request):
+    prev = mb.set_gradient_gemms(request.param)
+    yield request.param
+    mb.set_gradient_gemms(prev)
+
+
+@pytest.mark.parametrize("shape", [(256, 512, 384), (304, 328, 520), (64, 1024, 2816), (4096, 1024, 2048)])
+def test_backward_against_fp32_gold_and_reference_autograd(shape, gradient_gemms):
     """dX and dW of the op against the fp32 gradient of the reference's expression.  Tolerance (bf16 gradients, one
     recomputed bf16 intermediate): max|d-gold|/max|gold| <= 2e-2 and Frobenius-relative <= 1e-2; and the op's error
     stays within 1.5x of what PyTorch's own bf16 autograd of the eager expression makes on the same inputs."""
@@ -254,6 +261,31 @@ def test_plain_gemm_on_the_tile_kernels(shape):
     assert (big == 7.0).all()
     with pytest.raises(ValueError):
         mb.gemm_nt_out(a, b, out=torch.empty(M, N, dtype=torch.float32, device="cuda"))
+
+
+@pytest.mark.parametrize("shape", [(256, 512, 512), (64, 256, 128), (304, 1056, 328), (1000, 4096, 2048), (8, 16, 8),
+                                   (520, 176, 72)])
+@pytest.mark.parametrize("a_is_km,b_is_kn", [(False, True), (True, False), (True, True), (False, False)])
+def test_gemm_with_operands_stored_either_way_round(shape, a_is_km, b_is_kn):
+    """gemm_bf16: an operand stored [K, rows] is read as an MN-major tile (no transpose in memory); all four
+    combinations against an fp32 gold and, bit for bit, against the same product with pre-transposed copies."""
+    from oracle import error_metrics
+
+    M, N, K = shape
+    g = torch.Generator().manual_seed(M + N + K)
+    A = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    B = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    a = A.t().contiguous() if a_is_km else A
+    b = B.t().contiguous() if b_is_kn else B
+    c = mb.gemm_bf16(a, b, a_is_km, b_is_kn)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    gold = A.float() @ B.float().t()
+    torch.backends.cuda.matmul.allow_tf32 = prev
+    m = error_metrics(c, gold)
+    assert c.shape == (M, N) and m["max_norm"] <= 1e-2 and m["frob"] <= 5e-3, m
+    assert error_metrics(c, torch.nn.functional.linear(A, B).float())["max_norm"] <= 8e-3
+    assert mb.device_status(0)["code"] == 0
 
 
 def test_mlp_with_own_down_projection():

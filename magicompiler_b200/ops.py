@@ -455,6 +455,15 @@ def gemm_swiglu_preact(x: torch.Tensor, w_gate_up: torch.Tensor) -> tuple[torch.
     return y.view(*x.shape[:-1], N), h
 
 
+def gemm_swiglu_auto(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """``gemm_swiglu_train`` when a gradient will be asked for (grad mode on and an argument requires grad), else the
+    plain ``gemm_swiglu``: training keeps the pre-activations (faster than recomputing them and still one tensor fewer
+    than PyTorch keeps for the eager expression), inference writes nothing extra."""
+    if torch.is_grad_enabled() and (x.requires_grad or w_gate_up.requires_grad):
+        return torch.ops.magi_swiglu.gemm_swiglu_preact(x, w_gate_up)[0]
+    return torch.ops.magi_swiglu.gemm_swiglu(x, w_gate_up)
+
+
 def gemm_swiglu_train(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     """``gemm_swiglu`` for training steps where memory allows keeping the ``[M, 2N]`` pre-activations: forward +
     backward run four GEMMs' worth of tensor work instead of five (no recomputation)."""

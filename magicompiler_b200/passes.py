@@ -171,12 +171,21 @@ class FuseSwiGLUPass(_PassBase):
 
     ``allowed_devices``: device types of the traced tensors for which the rewrite is made (the kernel exists for
     CUDA; "meta" lets shape-only traces through; tests that stand a CPU function in for the kernel add "cpu").
-    ``save_preactivations``: emit the two-output training op ``gemm_swiglu_preact`` (its backward reads the kept
-    ``[M, 2N]`` pre-activations instead of recomputing them) and use its first output."""
+    ``save_preactivations``: True emits the two-output training op ``gemm_swiglu_preact`` (its backward reads the kept
+    ``[M, 2N]`` pre-activations instead of recomputing them) and uses its first output; False emits ``gemm_swiglu``
+    (its backward recomputes); None (default) decides per match: the training op when the graph is traced with grad
+    mode on and the activations or a weight require grad, else the plain op."""
 
-    def __init__(self, allowed_devices: tuple[str, ...] = ("cuda", "meta"), save_preactivations: bool = False):
+    def __init__(self, allowed_devices: tuple[str, ...] = ("cuda", "meta"), save_preactivations: bool | None = None):
         self.allowed_devices = tuple(allowed_devices)
-        self.save_preactivations = bool(save_preactivations)
+        self.save_preactivations = save_preactivations
+
+    def _keep_preactivations(self, *nodes: torch.fx.Node) -> bool:
+        if self.save_preactivations is not None:
+            return bool(self.save_preactivations)
+        if not torch.is_grad_enabled():
+            return False
+        return any(isinstance(_example(n), torch.Tensor) and _example(n).requires_grad for n in nodes)
 
     def _matches(self, graph: torch.fx.Graph):
         found = []
@@ -257,7 +266,7 @@ class FuseSwiGLUPass(_PassBase):
             x, wg, wu = gate.args[0], gate.args[1], up.args[1]
             with graph.inserting_before(mul):
                 packed = graph.call_function(torch.ops.magi_swiglu.pack_gate_up_cached.default, (wg, wu))
-                if self.save_preactivations:
+                if self._keep_preactivations(x, wg, wu):
                     both = graph.call_function(torch.ops.magi_swiglu.gemm_swiglu_preact.default, (x, packed))
                     fused = graph.call_function(operator.getitem, (both, 0))
                 else:
@@ -278,7 +287,7 @@ class FuseSwiGLUPass(_PassBase):
         for mul, act, gate, up, helpers, lin in self._matches_merged(graph):
             x, packed = lin.args[0], lin.args[1]
             with graph.inserting_before(mul):
-                if self.save_preactivations:
+                if self._keep_preactivations(x, packed):
                     both = graph.call_function(torch.ops.magi_swiglu.gemm_swiglu_preact.default, (x, packed))
                     fused = graph.call_function(operator.getitem, (both, 0))
                 else:
@@ -298,7 +307,7 @@ class FuseSwiGLUPass(_PassBase):
 
 
 def install_into_magi_compiler(allowed_devices: tuple[str, ...] = ("cuda", "meta"),
-                               save_preactivations: bool = False) -> bool:
+                               save_preactivations: bool | None = None) -> bool:
     """Opt-in: make MagiCompiler's ``FullGraphPassManager`` run ``FuseSwiGLUPass`` first.  Returns False when
     MagiCompiler is not importable.  (Upstream, the same effect is two lines in ``full_graph_pass_mgr.py``.)"""
     try:

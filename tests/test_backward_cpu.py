@@ -73,3 +73,15 @@ def test_training_op_keeps_the_preactivations_and_differentiates():
     y = mb.gemm_swiglu_train(x, w)
     gx, gw = torch.autograd.grad(y, (x, w), torch.empty_like(y))
     assert gx.shape == x.shape and gw.shape == w.shape and gw.dtype == torch.bfloat16
+
+
+def test_auto_entry_picks_by_grad_mode_and_requires_grad():
+    x = torch.empty(4, 64, dtype=torch.bfloat16, device="meta")
+    w = torch.empty(80, 64, dtype=torch.bfloat16, device="meta")
+    assert mb.gemm_swiglu_auto(x, w).grad_fn is None
+    y = mb.gemm_swiglu_auto(x, w.clone().requires_grad_(True))
+    assert "gemm_swiglu_preact" in type(y.grad_fn).__name__ or "getitem" in type(y.grad_fn).__name__.lower() \
+        or y.requires_grad
+    assert y.shape == (4, 40) and y.requires_grad
+    with torch.no_grad():
+        assert not mb.gemm_swiglu_auto(x, w.clone().requires_grad_(True)).requires_grad

@@ -39,8 +39,11 @@ class MLP(torch.nn.Module):
 
 
 def run_pass(module, x, **pass_kwargs):
-    """Compile with a backend that applies the pass to the Dynamo graph; returns (targets before, after, output)."""
+    """Compile with a backend that applies the pass to the Dynamo graph; returns (targets before, after, output).
+    Unless a test says otherwise the pass emits the plain op (the choice between it and the training op has its own
+    test)."""
     seen = {}
+    pass_kwargs.setdefault("save_preactivations", False)
 
     def backend(gm, example_inputs):
         seen["before"] = [n.target for n in gm.graph.nodes if n.op == "call_function"]
@@ -116,6 +119,21 @@ def test_merged_projection_form_is_rewritten_without_packing(form):
 def test_merged_projection_lookalikes_are_left_alone(form):
     seen, _ = run_pass(MergedMLP(form), torch.empty(10, 64, dtype=torch.bfloat16, device="meta"))
     assert seen["count"] == 0 and GEMM not in seen["after"]
+
+
+def test_default_picks_the_training_op_only_when_a_gradient_can_be_asked_for():
+    PRE = torch.ops.magi_swiglu.gemm_swiglu_preact.default
+    x = torch.empty(10, 64, dtype=torch.bfloat16, device="meta")
+    seen, _ = run_pass(MLP(), x, save_preactivations=None)          # parameters require grad, grad mode on
+    assert seen["after"].count(PRE) == 1 and GEMM not in seen["after"]
+    with torch.no_grad():
+        seen, _ = run_pass(MLP(), x, save_preactivations=None)      # inference
+    assert seen["after"].count(GEMM) == 1 and PRE not in seen["after"]
+    frozen = MLP().requires_grad_(False)
+    seen, _ = run_pass(frozen, x, save_preactivations=None)         # nothing to differentiate
+    assert seen["after"].count(GEMM) == 1 and PRE not in seen["after"]
+    seen, _ = run_pass(frozen, x.clone().requires_grad_(True), save_preactivations=None)  # gradient w.r.t. x only
+    assert seen["after"].count(PRE) == 1
 
 
 def test_operand_order_and_leading_dims():

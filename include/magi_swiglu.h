@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define MAGI_SWIGLU_ABI_VERSION 3
+#define MAGI_SWIGLU_ABI_VERSION 4
 
 /* variant selector of magi_swiglu_forward_bf16 */
 #define MAGI_SWIGLU_VARIANT_AUTO   0  /* M <= 128 -> STREAM, else MMA2           */
@@ -231,20 +231,49 @@ int64_t magi_swiglu_workspace_bytes(int64_t M, int64_t N, int64_t K, int variant
  * launching: out[0]=variant, out[1]=block_n, out[2]=stages, out[3]=grid CTAs,
  * out[4]=tiles, out[5]=dynamic shared memory bytes, out[6]=accumulator buffers,
  * out[7]=MMAs per K=16 step, out[8]=CTAs per tile (1 or 2), out[9]=row units per raster band,
- * out[10]=1 if the tile is released to the MMA issuer in two halves, out[11]=CTAs that split K for one tile.  `sm_count` <= 0 means "query `device`".
- * Needs no GPU when sm_count > 0.
+ * out[10]=1 if the tile is released to the MMA issuer in two halves, out[11]=CTAs that split K for one tile,
+ * out[12]=1 if Y leaves through shared memory and TMA stores (0 = direct stores), out[13]=accumulator sets per
+ * slab that consecutive K=16 steps rotate through (1, 2 or 4), out[14..15]=0 (reserved).
+ * `sm_count` <= 0 means "query `device`".  Needs no GPU when sm_count > 0.
  * Replaces: nothing in the reference. */
 int magi_swiglu_plan(int64_t M, int64_t N, int64_t K, int variant,
                      int block_n, int stages, int group_m, int max_ctas,
-                     int device, int sm_count, int32_t out[12]);
+                     int device, int sm_count, int32_t out[16]);
 
 /* Reads (and clears) the device-side watchdog word of `device`.  Every wait in
  * the kernels is bounded; a wait that expires records
- * out[0]=code (0 = none; 1 = X producer, 2 = mma issuer, 3 = epilogue, 4 = W producer),
+ * out[0]=code (0 = none; 1 = X producer, 2 = mma issuer, 3 = epilogue, 4 = W producer, 7 = self-test),
  * out[1]=block index, out[2]=pipeline stage or accumulator buffer, out[3]=phase.
+ * A kernel whose wait expired returns normally (tensor memory freed, context usable) but its output is
+ * incomplete, and the host learns of it ONLY here: callers poll this at a point where they synchronise anyway.
  * This call SYNCHRONISES the device; it is for tests and debugging.
  * Replaces: nothing in the reference. */
 int magi_swiglu_device_status(int device, int32_t out[4]);
+
+/* Tuning aids for sweeps and tests (process-wide; not meant for production callers).  Sets knob `knob` to `value`
+ * and returns the previous value (for K_SPLITS/NO_SPLIT/Y_TMA >= -1, for L2_HINTS -1 or xwy), or
+ * MAGI_SWIGLU_ERR_VARIANT for an unknown knob.  Initial values come from the environment, read once when the first
+ * plan is made: MAGI_SWIGLU_K_SPLITS, MAGI_SWIGLU_NO_SPLIT, MAGI_SWIGLU_Y_TMA, MAGI_SWIGLU_L2_HINTS, MAGI_SWIGLU_CHAINS.
+ *   K_SPLITS  z > 0: force z-way split-K in the STREAM schedule (0 = choose)
+ *   NO_SPLIT  1: drain CTA-pair tiles in one piece instead of two separately released halves
+ *   Y_TMA     0 / 1: force direct stores / shared memory + TMA stores for Y in the tile schedules (-1 = choose)
+ *   CHAINS    1 / 2 / 4: at most that many accumulator sets per slab in the STREAM schedule (0 = choose)
+ *   L2_HINTS  three decimal digits xwy, each 0 normal / 1 evict-first / 2 evict-last, for X tiles, W tiles and Y
+ *             stores (-1 = defaults)
+ * Replaces: nothing in the reference. */
+#define MAGI_SWIGLU_TUNE_K_SPLITS 0
+#define MAGI_SWIGLU_TUNE_NO_SPLIT 1
+#define MAGI_SWIGLU_TUNE_Y_TMA    2
+#define MAGI_SWIGLU_TUNE_L2_HINTS 3
+#define MAGI_SWIGLU_TUNE_CHAINS   4
+int magi_swiglu_tuning(int knob, int value);
+
+/* Runs the kernels' bounded wait by itself: a one-block kernel whose thread 0 waits on an mbarrier that nothing
+ * signals (no copy, no MMA in flight), gives up after `limit_cycles` SM cycles (1e3..2e9) and records
+ * {code 7, block 0, index 42, phase 0} for magi_swiglu_device_status.  The kernel returns normally; nothing
+ * faults.  For tests of the give-up / report / clear path.
+ * Replaces: nothing in the reference. */
+int magi_swiglu_watchdog_selftest(int device, void* cuda_stream, int64_t limit_cycles);
 
 /* SM clock the most recent MMA/MMA2/STREAM kernel on `device` really ran at: out[0] = average MHz
  * (SM cycles / wall nanoseconds, both read inside the kernel by block 0), out[1] = that span in

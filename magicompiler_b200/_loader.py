@@ -25,7 +25,7 @@ NVCC_FLAGS = [
     "-shared", "-Xcompiler", "-fPIC",
 ]
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 VARIANT_AUTO, VARIANT_MMA, VARIANT_STREAM, VARIANT_SIMT, VARIANT_MMA2 = 0, 1, 2, 3, 4
 VARIANTS = {"auto": VARIANT_AUTO, "mma": VARIANT_MMA, "stream": VARIANT_STREAM, "simt": VARIANT_SIMT,
             "mma2": VARIANT_MMA2}
@@ -105,6 +105,10 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.magi_swiglu_plan.argtypes = [i64, i64, i64, i32, i32, i32, i32, i32, i32, i32, ctypes.POINTER(ctypes.c_int32)]
     lib.magi_swiglu_device_status.restype = i32
     lib.magi_swiglu_device_status.argtypes = [i32, ctypes.POINTER(ctypes.c_int32)]
+    lib.magi_swiglu_tuning.restype = i32
+    lib.magi_swiglu_tuning.argtypes = [i32, i32]
+    lib.magi_swiglu_watchdog_selftest.restype = i32
+    lib.magi_swiglu_watchdog_selftest.argtypes = [i32, vp, i64]
     lib.magi_swiglu_kernel_clock.restype = i32
     lib.magi_swiglu_kernel_clock.argtypes = [i32, ctypes.POINTER(ctypes.c_double)]
     lib.magi_swiglu_last_error.restype = ctypes.c_char_p
@@ -135,6 +139,24 @@ def load_library() -> ctypes.CDLL:
     return lib
 
 
+TUNING_KNOBS = {"k_splits": 0, "no_split": 1, "y_tma": 2, "l2_hints": 3, "chains": 4}
+_tuning_epoch = 0  # bumped by set_tuning so host-side caches keyed on the schedule notice
+
+
+def set_tuning(knob: str, value: int) -> int:
+    """Set a tuning aid of the library (``magi_swiglu_tuning``: k_splits, no_split, y_tma, l2_hints) and return its
+    previous value.  Process-wide; for tests and sweeps."""
+    global _tuning_epoch
+    lib = load_library()
+    prev = lib.magi_swiglu_tuning(TUNING_KNOBS[knob], int(value))
+    _tuning_epoch += 1
+    return prev
+
+
+def tuning_epoch() -> int:
+    return _tuning_epoch
+
+
 def last_error() -> str:
     return load_library().magi_swiglu_last_error().decode("utf-8", "replace")
 
@@ -143,13 +165,14 @@ def plan(M: int, N: int, K: int, variant: str | int = "auto", block_n: int = 0, 
          max_ctas: int = 0, device: int = 0, sm_count: int = 0) -> dict:
     """Schedule the library would use (pure host arithmetic when ``sm_count`` > 0)."""
     lib = load_library()
-    out = (ctypes.c_int32 * 12)()
+    out = (ctypes.c_int32 * 16)()
     v = VARIANTS[variant] if isinstance(variant, str) else int(variant)
     rc = lib.magi_swiglu_plan(M, N, K, v, block_n, stages, group_m, max_ctas, device, sm_count, out)
     if rc != 0:
         raise ValueError(f"magi_swiglu_plan failed ({rc}): {last_error()}")
-    keys = ["variant", "block_n", "stages", "grid", "tiles", "smem_bytes", "acc_bufs", "n_mma", "ctas", "group_m", "split", "k_splits"]
-    return dict(zip(keys, list(out)))
+    keys = ["variant", "block_n", "stages", "grid", "tiles", "smem_bytes", "acc_bufs", "n_mma", "ctas", "group_m", "split", "k_splits",
+            "y_tma", "chains"]
+    return dict(zip(keys, list(out)[:len(keys)]))
 
 
 def workspace_bytes(M: int, N: int, K: int, variant: str | int = "auto", block_n: int = 0, stages: int = 0,

@@ -39,7 +39,9 @@ constexpr int kTmemCols = 512;       // whole tensor memory of the SM (one CTA p
 constexpr uint32_t kABytes = kBM * kBK * 2;
 constexpr int kSmemLimit = 232448 - 1024;  // dynamic part of the 227 KB opt-in maximum (static barriers take the rest)
 constexpr int kSmemFloor = 120 * 1024;  // keeps a second CTA off the SM (it would block in tcgen05.alloc)
-constexpr long long kWaitLimitCycles = 6000000000LL;  // three to four seconds of SM cycles
+constexpr long long kWaitLimitCycles = 6000000000LL;  // default wait limit: three to four seconds of SM cycles
+constexpr int kStageOutBytes = 2048;   // one 32-row x 32-column bf16 box of Y on its way to a TMA store
+constexpr int kStagingBytes = kEpiWarps * 2 * kStageOutBytes;  // two boxes per epilogue warp
 
 __device__ unsigned int g_watchdog[4];  // {role that gave up, block, stage/buffer, parity}
 // {SM cycles, nanoseconds} block 0 of the most recent tile kernel spent between set-up and teardown: the
@@ -48,14 +50,16 @@ __device__ unsigned long long g_clock_probe[2];
 
 #ifdef MAGI_SWIGLU_TRACE
 // Tuning builds only: SM-cycle timestamps of block 0's second tile (MMA issuer and first epilogue warp).
-__device__ long long g_trace[16];
+__device__ long long g_trace[32];
 #define MAGI_TRACE(slot, cond) do { if (blockIdx.x == 0 && (cond)) g_trace[slot] = clock64(); } while (0)
 #define MAGI_TRACE_T0() const long long trace_t0 = clock64()
 #define MAGI_TRACE_ADD(slot) do { if (blockIdx.x == 0) g_trace[slot] += clock64() - trace_t0; } while (0)
+#define MAGI_TRACE_ADD_IF(slot, cond) do { if (blockIdx.x == 0 && (cond)) g_trace[slot] += clock64() - trace_t0; } while (0)
 #else
 #define MAGI_TRACE(slot, cond) do { } while (0)
 #define MAGI_TRACE_T0() do { } while (0)
 #define MAGI_TRACE_ADD(slot) do { } while (0)
+#define MAGI_TRACE_ADD_IF(slot, cond) do { } while (0)
 #endif
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
@@ -78,6 +82,9 @@ struct KArgs {
   int split;          // CTA pairs, two MMAs: tensor memory holds [gate_lo|up_lo|gate_hi|up_hi]; the low half of
                       // the tile is handed back to the MMA issuer before the high half has been drained
   int acc_bufs;       // tensor-memory accumulator buffers (2 = epilogue overlaps next tile)
+  int chains;         // 1, 2 or 4 accumulator sets per buffer: consecutive K=16 steps add into different sets (an MMA
+                      // that accumulates into the columns of the one before it issues ~180 cycles after it; narrow
+                      // slabs of the STREAM schedule are bound by that), the epilogue adds the sets in a fixed order
   int wide_store;     // y base and row pitch are 32-byte aligned: 256-bit stores (one full sector per thread)
   const float* row_scale;  // optional [M] fp32: accumulators of row m are multiplied by row_scale[m] before the
                            // epilogue (a fused RMSNorm: 1/rms(x_m), the norm weight being folded into W); null = none
@@ -102,10 +109,12 @@ struct KArgs {
   // k_splits == 1: no scratch is touched.
   int k_splits, kb_per_split;
   float* ws;  // [tile][split][M rows][2*block_n] fp32
+  int y_tma;  // 1: bf16 Y (or the plain GEMM's C) leaves through shared memory and TMA stores (tm_y is valid)
+  long long wait_limit;  // SM cycles after which a wait on an mbarrier gives up (kWaitLimitCycles by default)
 };
 
 __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned role,
-                                             unsigned idx) {
+                                             unsigned idx, long long limit) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   unsigned spins = 0;
@@ -113,7 +122,7 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 255u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > limit) {
         *abort_flag = 1;
         if (atomicCAS(&g_watchdog[0], 0u, role) == 0u) {
           g_watchdog[1] = blockIdx.x;
@@ -124,6 +133,23 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
       }
     }
   }
+}
+
+// Exercises the bounded wait by itself: one mbarrier that nothing ever signals, no copy or MMA in flight.  Thread 0
+// waits on it, gives up after `limit` cycles, records {role 7, block 0, index 42, parity 0} in g_watchdog like any
+// role of the tile kernels would, and the kernel returns normally.
+constexpr unsigned kWatchdogSelftestRole = 7u, kWatchdogSelftestIndex = 42u;
+__global__ void watchdog_selftest_kernel(long long limit) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) wait_bounded(smem_u32(&bar), 0u, &abort_flag, kWatchdogSelftestRole, kWatchdogSelftestIndex, limit);
+  __syncthreads();
 }
 
 // Banded raster: tiles are numbered band by band (group_m row-tiles per band); inside a band the
@@ -147,20 +173,50 @@ __device__ __forceinline__ uint64_t l2_policy(int hint) {
   return hint == 1 ? l2_policy_evict_first() : (hint == 2 ? l2_policy_evict_last() : l2_policy_evict_normal());
 }
 
+// y[i] = silu(g[i]) * u[i] for four neighbouring columns of one row, branch-free.
+// The epilogue is bound by the special-function unit (16 results per cycle and SM) and by instruction issue, so
+// the four sigmoids share ONE reciprocal: with a_i = 1 + 2^(-g_i*log2(e)), 1/a_i = (product of the other three a)
+// / (product of all four) — nine multiplications on the FMA pipe instead of three more rcp, 1.25 special-function
+// results per output instead of 2.  The exponent is clamped at 31 so the product stays below 2^125: exact down to
+// g = -21.49; below that the result is g*u*2^-31 instead of g*u*e^g (both below 1e-8*|u|), a NaN or infinity in one
+// column cannot reach its neighbours (min() drops a NaN exponent, the NaN returns through g*u), and g = -inf gives
+// an infinity of the sign of -u where the plain formula gives NaN.  Groups are aligned to four columns of Y whatever
+// the schedule, tile width or column shard, so every schedule still produces the same bits.
+__device__ __forceinline__ void silu_mul4(const uint32_t* g, const uint32_t* u, float (&y)[4]) {
+  constexpr float kNegLog2e = -1.4426950408889634f;
+#ifdef MAGI_SWIGLU_PLAIN_SILU  // tuning builds only: one ex2 and one rcp per output, for comparison
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float gi = __uint_as_float(g[i]);
+    y[i] = (gi * __uint_as_float(u[i])) * rcp_approx(1.0f + ex2_approx(gi * kNegLog2e));
+  }
+#else
+  float a[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) a[i] = 1.0f + ex2_approx(fminf(__uint_as_float(g[i]) * kNegLog2e, 31.0f));
+  const float p01 = a[0] * a[1], p23 = a[2] * a[3];
+  const float r = rcp_approx(p01 * p23);
+  const float r01 = r * p23, r23 = r * p01;
+  y[0] = (__uint_as_float(g[0]) * __uint_as_float(u[0])) * (r01 * a[1]);
+  y[1] = (__uint_as_float(g[1]) * __uint_as_float(u[1])) * (r01 * a[0]);
+  y[2] = (__uint_as_float(g[2]) * __uint_as_float(u[2])) * (r23 * a[3]);
+  y[3] = (__uint_as_float(g[3]) * __uint_as_float(u[3])) * (r23 * a[2]);
+#endif
+}
+
 __device__ __forceinline__ uint4 swiglu_pack8(const uint32_t* g, const uint32_t* u) {
+  float lo[4], hi[4];
+  silu_mul4(g, u, lo);
+  silu_mul4(g + 4, u + 4, hi);
   uint4 v;
   __nv_bfloat162 p;
-  p = __floats2bfloat162_rn(silu_mul(__uint_as_float(g[0]), __uint_as_float(u[0])),
-                            silu_mul(__uint_as_float(g[1]), __uint_as_float(u[1])));
+  p = __floats2bfloat162_rn(lo[0], lo[1]);
   v.x = *reinterpret_cast<uint32_t*>(&p);
-  p = __floats2bfloat162_rn(silu_mul(__uint_as_float(g[2]), __uint_as_float(u[2])),
-                            silu_mul(__uint_as_float(g[3]), __uint_as_float(u[3])));
+  p = __floats2bfloat162_rn(lo[2], lo[3]);
   v.y = *reinterpret_cast<uint32_t*>(&p);
-  p = __floats2bfloat162_rn(silu_mul(__uint_as_float(g[4]), __uint_as_float(u[4])),
-                            silu_mul(__uint_as_float(g[5]), __uint_as_float(u[5])));
+  p = __floats2bfloat162_rn(hi[0], hi[1]);
   v.z = *reinterpret_cast<uint32_t*>(&p);
-  p = __floats2bfloat162_rn(silu_mul(__uint_as_float(g[6]), __uint_as_float(u[6])),
-                            silu_mul(__uint_as_float(g[7]), __uint_as_float(u[7])));
+  p = __floats2bfloat162_rn(hi[2], hi[3]);
   v.w = *reinterpret_cast<uint32_t*>(&p);
   return v;
 }
@@ -316,7 +372,8 @@ __device__ __forceinline__ void store_cols(__nv_bfloat16* dst, const uint32_t* g
 
 template <int kCtas>
 __global__ void __launch_bounds__(kThreads, 1)
-swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const KArgs a) {
+swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
+                 const __grid_constant__ CUtensorMap tm_y, const KArgs a) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * kMaxStages + 4];
   __shared__ uint32_t tmem_slot;
@@ -348,6 +405,7 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     fence_barrier_init();
     prefetch_tensormap(&tm_x);
     prefetch_tensormap(&tm_w);
+    if (a.y_tma) prefetch_tensormap(&tm_y);
   }
   if (warp == 2) {
     tmem_alloc<kCtas>(smem_u32(&tmem_slot), kTmemCols);
@@ -393,7 +451,7 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         for (int kb = kb0; kb < kb1; ++kb) {
           {
             MAGI_TRACE_T0();
-            if (!wait_bounded(empty_bar(stage), phase ^ 1u, &abort_flag, x_role ? 1u : 4u, stage)) {
+            if (!wait_bounded(empty_bar(stage), phase ^ 1u, &abort_flag, x_role ? 1u : 4u, stage, a.wait_limit)) {
               ok = false;
               break;
             }
@@ -479,12 +537,12 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         MAGI_TRACE(0, it == 2);  // issuer starts waiting for the accumulator of tile 2
         {
           MAGI_TRACE_T0();
-          if (!wait_bounded(acc_empty_bar(buf), acc_phase ^ 1u, &abort_flag, 2u, 16 + buf)) break;
+          if (!wait_bounded(acc_empty_bar(buf), acc_phase ^ 1u, &abort_flag, 2u, 16 + buf, a.wait_limit)) break;
           MAGI_TRACE_ADD(15);  // issuer: cycles spent waiting for a free accumulator
         }
         MAGI_TRACE(1, it == 2);  // accumulator free
         tc_fence_after_sync();
-        const uint32_t d_gate = tmem_base + (uint32_t)(buf * acc_cols);
+        const uint32_t d_gate = tmem_base + (uint32_t)(buf * acc_cols * a.chains);
         int kb = kb0;
         if (kCtas == 2 && a.split) {
           // The low half [gate_lo|up_lo] is free while the epilogue still drains the high half: run the
@@ -493,7 +551,7 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
           int s2 = stage;
           uint32_t p2 = phase;
           for (int j = 0; j < ahead && ok; ++j) {
-            if (!wait_bounded(full_bar(s2), p2, &abort_flag, 2u, s2)) {
+            if (!wait_bounded(full_bar(s2), p2, &abort_flag, 2u, s2, a.wait_limit)) {
               ok = false;
               break;
             }
@@ -509,7 +567,7 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
             }
           }
           if (!ok) break;
-          if (!wait_bounded(acc_empty_bar(1), acc_phase ^ 1u, &abort_flag, 2u, 17)) break;
+          if (!wait_bounded(acc_empty_bar(1), acc_phase ^ 1u, &abort_flag, 2u, 17, a.wait_limit)) break;
           tc_fence_after_sync();
           for (int j = 0; j < ahead; ++j) {
             const uint32_t sa = tiles_base + stage * a.stage_bytes;
@@ -525,10 +583,15 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
           }
           kb = ahead;
         }
-        for (; kb < kb1; ++kb) {
+        // Split mode ends a tile the way it begins one, mirrored: the low-half MMAs of the last K-steps (as many as
+        // the ring holds) go first and the low half is handed to the epilogue while the high-half MMAs of those
+        // steps still run, so the drain of the low half overlaps tensor work at both ends of the tile.
+        const int kb_tail = (kCtas == 2 && a.split) ? max(kb, kb1 - a.stages) : kb1;
+        bool low_done = false;
+        for (; kb < kb_tail; ++kb) {
           {
             MAGI_TRACE_T0();
-            if (!wait_bounded(full_bar(stage), phase, &abort_flag, 2u, stage)) {
+            if (!wait_bounded(full_bar(stage), phase, &abort_flag, 2u, stage, a.wait_limit)) {
               ok = false;
               break;
             }
@@ -543,9 +606,11 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
             const uint32_t sb = sa + kABytes;
 #pragma unroll
             for (int k = 0; k < kBK / 16; ++k) {
-              const uint32_t acc = ((kb - kb0) | k) != 0;
+              // K=16 step k of every stage goes to accumulator set k % chains; a set's first MMA overwrites
+              const int set = k & (a.chains - 1);
+              const uint32_t acc = (kb != kb0 || k >= a.chains) ? 1u : 0u;
               const uint64_t ad = desc_a(sa, k);
-              umma_bf16<kCtas>(d_gate, ad, desc_b(sb, k), idesc, acc);
+              umma_bf16<kCtas>(d_gate + (uint32_t)(set * acc_cols), ad, desc_b(sb, k), idesc, acc);
               if (a.n_mma == 2) umma_bf16<kCtas>(d_gate + a.block_n, ad, desc_b(sb + a.b_second, k), idesc, acc);
             }
             MAGI_TRACE_ADD(10);  // issuer: cycles spent issuing MMAs
@@ -560,7 +625,50 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
             phase ^= 1u;
           }
         }
-        if (ok) umma_commit<kCtas>(acc_full_bar(buf));
+        if (ok && kb < kb1) {  // split mode: the tile's last K-steps, low half first
+          const int n_tail = kb1 - kb;
+          int s2 = stage;
+          uint32_t p2 = phase;
+          for (int j = 0; j < n_tail && ok; ++j) {
+            if (!wait_bounded(full_bar(s2), p2, &abort_flag, 2u, s2, a.wait_limit)) {
+              ok = false;
+              break;
+            }
+            MAGI_TRACE(3, it == 1 && j == n_tail - 1);  // last stage of tile 1 available
+            tc_fence_after_sync();
+            const uint32_t sa = tiles_base + s2 * a.stage_bytes;
+#pragma unroll
+            for (int k = 0; k < kBK / 16; ++k)
+              umma_bf16<kCtas>(d_gate, desc_a(sa, k), desc_b(sa + kABytes, k), idesc, 1u);
+            if (++s2 == a.stages) {
+              s2 = 0;
+              p2 ^= 1u;
+            }
+          }
+          if (!ok) break;
+          umma_commit<kCtas>(acc_full_bar(0));  // the low half is complete
+          low_done = true;
+          MAGI_TRACE(22, it == 1);  // low half of tile 1 committed
+          for (int j = 0; j < n_tail; ++j) {
+            const uint32_t sa = tiles_base + stage * a.stage_bytes;
+#pragma unroll
+            for (int k = 0; k < kBK / 16; ++k)
+              umma_bf16<kCtas>(d_gate + a.block_n, desc_a(sa, k), desc_b(sa + kABytes + a.b_second, k), idesc, 1u);
+            umma_commit<kCtas>(empty_bar(stage));
+            if (++stage == a.stages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        }
+        if (ok) {
+          if (kCtas == 2 && a.split) {  // one "complete" barrier per half
+            if (!low_done) umma_commit<kCtas>(acc_full_bar(0));
+            umma_commit<kCtas>(acc_full_bar(1));
+          } else {
+            umma_commit<kCtas>(acc_full_bar(buf));
+          }
+        }
         MAGI_TRACE(4, it == 1);  // all MMAs of tile 1 issued
         MAGI_TRACE(9, it == 2);  // all MMAs of tile 2 issued
       }
@@ -570,6 +678,9 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     const int q = warp & 3;
     const uint64_t y_policy = l2_policy(a.y_hint);
     const uint32_t acc_empty_remote0 = (kCtas == 2) ? map_to_cta(acc_empty_bar(0), 0) : 0u;
+    // Y through shared memory: this warp's two 32-row x 32-column boxes (64-byte rows, 64-byte swizzle) behind the ring
+    const uint32_t stg_base = tiles_base + (uint32_t)a.stages * a.stage_bytes + (uint32_t)(warp - 4) * (2u * kStageOutBytes);
+    uint32_t stg_par = 0;
     int it = 0;
     for (int item = unit; item < num_items; item += units, ++it) {
       const int t = item / a.k_splits;
@@ -578,7 +689,8 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       const uint32_t acc_phase = (a.acc_bufs == 2) ? ((it >> 1) & 1) : (it & 1);
       int mt, nt;
       tile_coords(a, t, mt, nt);
-      bool ok = wait_bounded(acc_full_bar(buf), acc_phase, &abort_flag, 3u, buf);
+      // split mode: acc_full_bar(0) = low half complete, acc_full_bar(1) = high half complete (waited for below)
+      bool ok = wait_bounded(acc_full_bar(buf), acc_phase, &abort_flag, 3u, buf, a.wait_limit);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       MAGI_TRACE(5, it == 1 && warp == 4 && lane == 0);  // epilogue sees tile 1 complete
@@ -588,7 +700,29 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       const bool row_ok = row < a.M;
       const int col0 = nt * a.block_n;
       const int valid_tile = min(a.block_n, a.N - col0);  // multiple of 8
-      const uint32_t t_tile = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * acc_cols);
+      const uint32_t t_tile = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * acc_cols * a.chains);
+      // Accumulator sets 1.. of a chained tile are added to the loaded chunk, 16 columns at a time, in set order.
+      auto add_chains = [&](uint32_t (&g)[32], uint32_t (&u)[32], uint32_t t_g, uint32_t t_u, int w) {
+        for (int set = 1; set < a.chains; ++set) {
+          for (int h = 0; h < w; h += 16) {
+            uint32_t tg[16], tu[16];
+            tmem_ld_x16(t_g + (uint32_t)(set * acc_cols + h), tg);
+            tmem_ld_x16(t_u + (uint32_t)(set * acc_cols + h), tu);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              asm volatile("" : "+r"(tg[i]), "+r"(tu[i]));  // uses of the loaded registers stay behind the wait
+              if (h == 0) {
+                g[i] = __float_as_uint(__uint_as_float(g[i]) + __uint_as_float(tg[i]));
+                u[i] = __float_as_uint(__uint_as_float(u[i]) + __uint_as_float(tu[i]));
+              } else {
+                g[16 + i] = __float_as_uint(__uint_as_float(g[16 + i]) + __uint_as_float(tg[i]));
+                u[16 + i] = __float_as_uint(__uint_as_float(u[16 + i]) + __uint_as_float(tu[i]));
+              }
+            }
+          }
+        }
+      };
       __nv_bfloat16* yrow_tile = a.y + (long long)row * a.ldy + col0;
       const bool wide = a.wide_store != 0;  // every 16-column group of every row starts on a 32-byte boundary
       const float row_scale_m = (a.row_scale != nullptr && row_ok) ? __ldg(a.row_scale + row) : 1.0f;
@@ -615,10 +749,11 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
           tmem_ld_wait();
           tmem_regs_ready(g);
           tmem_regs_ready(u);
+          if (a.chains > 1) add_chains(g, u, t_tile + c, t_tile + a.block_n + c, w);
           if (!chunk_w(c + 64)) {  // last read of the accumulator: hand it back before the stores
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+            if (lane == 0) mbar_arrive_relaxed(acc_empty_bar(buf));
             released = true;
           }
           if (row_ok) {
@@ -635,7 +770,7 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         if (!released) {
           tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+          if (lane == 0) mbar_arrive_relaxed(acc_empty_bar(buf));
         }
         continue;
       }
@@ -644,7 +779,14 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       // (low half then high half, each [gate|up] of bn/2 columns) that are released separately.
       const int num_seg = (kCtas == 2 && a.split) ? 2 : 1;
       const int seg_cols = a.block_n / num_seg;
+      bool seg_ok = true;
       for (int seg = 0; seg < num_seg; ++seg) {
+        if (seg == 1) {  // the high half has its own "complete" barrier
+          seg_ok = wait_bounded(acc_full_bar(1), acc_phase, &abort_flag, 3u, 1, a.wait_limit);
+          seg_ok = __all_sync(0xffffffffu, seg_ok);
+          if (!seg_ok) break;
+          tc_fence_after_sync();
+        }
         const uint32_t t_gate = t_tile + (uint32_t)(seg * a.block_n);
         const uint32_t t_up = t_gate + (uint32_t)seg_cols;
         const int valid = max(0, min(seg_cols, valid_tile - seg * seg_cols));
@@ -666,15 +808,65 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
             tmem_ld_x16_into32(t_up + c, u);
           }
         };
+        // One box of Y on its way out: the warp writes its 32 rows x 32 columns (16 packed words per lane) into the
+        // free one of its two staging buffers and lane 0 hands the buffer to a TMA store.  Row r of the box is
+        // 64 bytes; its 16-byte piece j sits at piece j ^ ((r >> 1) & 3) (the 64-byte swizzle of the tensor map),
+        // which spreads the lanes' 16-byte writes over all banks.  Rows and columns outside Y are clipped by the copy.
+        auto stage_out = [&](const uint32_t (&pk)[16], int col, int half) {
+          MAGI_TRACE_T0();
+          const uint32_t buf = stg_base + stg_par * kStageOutBytes;
+          if (lane == 0) bulk_wait_group_read<1>();  // the store that last read this buffer has finished reading it
+          __syncwarp();
+          const uint32_t rowaddr = buf + (uint32_t)lane * 64u;
+          const uint32_t sw = ((uint32_t)lane >> 1) & 3u;
+#pragma unroll
+          for (uint32_t j = 0; j < 4; ++j)
+            st_shared_v4(rowaddr + ((j ^ sw) << 4), pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          const int box_row0 = (mt * kCtas + (int)cta_rank) * kBM + q * 32;
+          if (lane == 0 && box_row0 < a.M) {
+            tma_store_3d_hint(buf, &tm_y, col, half, box_row0, y_policy);
+            bulk_commit_group();
+          }
+          stg_par ^= 1u;
+          MAGI_TRACE_ADD_IF(27, warp == 4 && lane == 0);  // staging + TMA store issue of one box
+        };
         auto process = [&](uint32_t (&g)[32], uint32_t (&u)[32], int c, int w) {
-          if (!row_ok) return;
-          if (a.row_scale != nullptr) {
+          if (a.row_scale != nullptr) {  // 1 for rows past M
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               g[j] = __float_as_uint(__uint_as_float(g[j]) * row_scale_m);
               u[j] = __float_as_uint(__uint_as_float(u[j]) * row_scale_m);
             }
           }
+          if (a.y_tma && w == 32 && a.h == nullptr) {  // bf16 Y (or plain C) through shared memory, all lanes take part
+            const int col = col0 + seg * seg_cols + c;
+            uint32_t pk[16];
+            if (a.plain) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint4 v = plain_pack8(g + 8 * j);
+                pk[4 * j] = v.x, pk[4 * j + 1] = v.y, pk[4 * j + 2] = v.z, pk[4 * j + 3] = v.w;
+              }
+              stage_out(pk, col, 0);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint4 v = plain_pack8(u + 8 * j);
+                pk[4 * j] = v.x, pk[4 * j + 1] = v.y, pk[4 * j + 2] = v.z, pk[4 * j + 3] = v.w;
+              }
+              stage_out(pk, col, 1);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint4 v = swiglu_pack8(g + 8 * j, u + 8 * j);
+                pk[4 * j] = v.x, pk[4 * j + 1] = v.y, pk[4 * j + 2] = v.z, pk[4 * j + 3] = v.w;
+              }
+              stage_out(pk, col, 0);
+            }
+            return;
+          }
+          if (!row_ok) return;
           if (a.h != nullptr) {  // training forward: keep the pre-activations for the backward
             __nv_bfloat16* hrow = a.h + (long long)row * a.ldh + col0 + seg * seg_cols + c;
             if (w == 32) {
@@ -721,15 +913,18 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
           }
         };
         auto release = [&]() {
-          MAGI_TRACE(6 + seg * 4, it == 1 && warp == 4 && lane == 0);  // warp 4 has read its last column
-          MAGI_TRACE(7 + seg * 4, it == 1 && warp == 11 && lane == 0);
+          MAGI_TRACE(6 + seg * 14, it == 1 && warp == 4 && lane == 0);  // warp 4 has read its last column (20: high half)
+          MAGI_TRACE(7 + seg * 14, it == 1 && warp == 11 && lane == 0);
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) {
+            // Relaxed arrivals: the tensor-memory reads being signalled are complete (tcgen05.wait::ld) and nothing else
+            // is published through this barrier, so the arrival must not wait for this warp's earlier global stores
+            // to become visible, which a releasing arrival does (about a thousand cycles on the tile's critical path).
             if constexpr (kCtas == 1)
-              mbar_arrive(acc_empty_bar(release_buf));
+              mbar_arrive_relaxed(acc_empty_bar(release_buf));
             else  // the leader's MMA issuer waits for both CTAs
-              mbar_arrive_cluster(acc_empty_remote0 + 8u * release_buf);
+              mbar_arrive_cluster_relaxed(acc_empty_remote0 + 8u * release_buf);
           }
         };
         uint32_t g[32], u[32];
@@ -737,22 +932,35 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         int w = width_at(c);
         bool released = false;
         while (w) {
-          load(g, u, c, w);
-          tmem_ld_wait();
-          tmem_regs_ready(g);
-          tmem_regs_ready(u);
+          {
+            MAGI_TRACE_T0();
+            load(g, u, c, w);
+            tmem_ld_wait();
+            tmem_regs_ready(g);
+            tmem_regs_ready(u);
+            if (a.chains > 1) add_chains(g, u, t_gate + c, t_up + c, w);
+            MAGI_TRACE_ADD_IF(24, warp == 4 && lane == 0);  // epilogue warp 4: tensor-memory loads and their wait
+          }
           const int c2 = c + 64, w2 = width_at(c2);
           if (!w2) {  // that was this warp's last read of the segment
+            MAGI_TRACE_T0();
             release();
             released = true;
+            MAGI_TRACE_ADD_IF(25, warp == 4 && lane == 0);  // hand-back of the accumulator
           }
-          process(g, u, c, w);
+          {
+            MAGI_TRACE_T0();
+            process(g, u, c, w);
+            MAGI_TRACE_ADD_IF(26, warp == 4 && lane == 0);  // arithmetic + stores of one chunk
+          }
           c = c2;
           w = w2;
         }
         if (!released) release();
       }
+      if (!seg_ok) break;
     }
+    if (a.y_tma && lane == 0) bulk_wait_group_read<0>();  // shared memory stays valid until the last store has read it
   }
 
   // ------------------------------------------------------------ teardown (also the abort path)

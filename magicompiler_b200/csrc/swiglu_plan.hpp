@@ -24,17 +24,50 @@ static int fail(int code, const char* fmt, ...) {
 }
 static int fail_cuda(cudaError_t e, const char* what) {
   snprintf(g_err, sizeof(g_err), "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+  cudaGetLastError();  // the error has been reported here: do not leave it for the next, unrelated launch check
   return e == cudaSuccess ? 1 : (int)e;
+}
+
+// Tuning aids.  Their initial values are read from the environment ONCE (first use), never on the launch path; tests
+// and sweeps change them afterwards through magi_swiglu_tuning():
+//   MAGI_SWIGLU_L2_HINTS=xwy  L2 priority of X tiles, W tiles, Y stores (each 0 normal, 1 evict-first, 2 evict-last)
+//   MAGI_SWIGLU_K_SPLITS=z    force z-way split-K in the STREAM schedule
+//   MAGI_SWIGLU_NO_SPLIT=1    drain pair tiles in one piece instead of two separately released halves
+//   MAGI_SWIGLU_Y_TMA=0|1     force Y through direct stores (0) or shared memory + TMA stores (1) in the tile schedules
+//   MAGI_SWIGLU_CHAINS=c      at most c (1, 2, 4) accumulator sets per slab in the STREAM schedule
+struct Tuning {
+  int hints[3] = {-1, -1, -1};
+  int k_splits = 0;
+  int no_split = 0;
+  int y_tma = -1;
+  int chains = 0;  // 0 = choose; 1, 2, 4 = at most that many accumulator sets in the STREAM schedule
+};
+static Tuning& tuning() {
+  static Tuning t = [] {
+    Tuning v;
+    if (const char* env = getenv("MAGI_SWIGLU_L2_HINTS")) {
+      if (strlen(env) == 3)
+        for (int i = 0; i < 3; ++i) v.hints[i] = (env[i] >= '0' && env[i] <= '2') ? env[i] - '0' : -1;
+    }
+    if (const char* env = getenv("MAGI_SWIGLU_K_SPLITS")) v.k_splits = atoi(env);
+    if (getenv("MAGI_SWIGLU_NO_SPLIT")) v.no_split = 1;
+    if (const char* env = getenv("MAGI_SWIGLU_Y_TMA")) v.y_tma = atoi(env) != 0;
+    if (const char* env = getenv("MAGI_SWIGLU_CHAINS")) v.chains = atoi(env);
+    return v;
+  }();
+  return t;
 }
 
 struct Plan {
   int variant, block_n, stages, grid, tiles, smem_bytes, acc_bufs, n_mma;
+  int chains;  // accumulator sets per buffer (STREAM schedule, narrow slabs): 1, 2 or 4
   int num_m_tiles, num_n_tiles, num_k_blocks, group_m;
   int ctas;  // CTAs per tile: 1, or 2 for the CTA-pair schedule
   int split; // CTA pairs with two MMAs per step and block_n % 32 == 0: two separately released half tiles
   int k_splits, kb_per_split;          // split-K of the STREAM schedule (1 = off)
   int64_t ws_bytes;                    // fp32 partial sums of a split-K plan (0 = none)
   uint32_t stage_bytes, b_second;
+  int y_tma;  // tile schedules: Y leaves through per-warp staging boxes in shared memory and TMA stores
 };
 
 static inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
@@ -73,8 +106,9 @@ static double tile_wave_cost(int64_t M, int64_t N, int rows, int64_t units, int 
   return best;
 }
 
+// allow_y_tma: the output is plain bf16 rows (Y of the fused op, C of the plain GEMM) that a TMA store can write.
 static int make_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, int stages, int group_m, int max_ctas,
-                     int sm_count, int64_t ws_limit, Plan* p) {
+                     int sm_count, int64_t ws_limit, Plan* p, int allow_y_tma = 1) {
   if (M < 0 || N <= 0 || K <= 0 || M > 0x7fffff00LL || N > 0x3fffff00LL || K > 0x7fffff00LL)
     return fail(MAGI_SWIGLU_ERR_SHAPE, "shape out of range: M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
   if (N % 8 != 0 || K % 8 != 0)
@@ -144,8 +178,7 @@ static int make_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
     // issue time; with scratch available, several CTAs share a slab and split K between them.
     const int64_t num_kb = (K + kBK - 1) / kBK;
     if (ws_limit > kWorkspaceCap) ws_limit = kWorkspaceCap;
-    int forced = 0;
-    if (const char* env = getenv("MAGI_SWIGLU_K_SPLITS")) forced = atoi(env);  // tuning aid
+    const int forced = tuning().k_splits;
     double best = stream_cost_ns(N, num_kb, block_n, 1, ctas);
     const int bn_lo = stream_auto_width ? 32 : block_n, bn_hi = stream_auto_width ? 256 : block_n;
     for (int bn = bn_lo; bn <= bn_hi; bn += 16) {
@@ -168,17 +201,40 @@ static int make_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
   p->block_n = block_n;
   p->n_mma = (2 * block_n <= 256) ? 1 : 2;
   p->acc_bufs = (4 * block_n <= kTmemCols) ? 2 : 1;
+  p->chains = 1;
+  if (variant == MAGI_SWIGLU_VARIANT_STREAM && tuning().chains != 1) {
+    // A narrow slab leaves most of tensor memory empty: spread the K=16 steps of a stage over 2 or 4 accumulator sets
+    // so that no MMA waits for the one before it.  One buffer then (a slab per CTA is the rule in this schedule).
+    const int fit_sets = kTmemCols / (2 * block_n);
+    int c = fit_sets >= 4 ? 4 : (fit_sets >= 2 ? 2 : 1);
+    if (tuning().chains > 0 && tuning().chains < c) c = tuning().chains;
+    if (c > 1) {
+      p->chains = c;
+      p->acc_bufs = 1;
+    }
+  }
   // weight rows per CTA and stage: gate + up rows of the tile, split between the CTAs of a pair
   p->stage_bytes = kABytes + 2u * (uint32_t)block_n * 128u / (uint32_t)pair;
   p->b_second = (uint32_t)block_n * 128u / (uint32_t)pair;
-  p->split = (pair == 2 && p->n_mma == 2 && block_n % 32 == 0 && !getenv("MAGI_SWIGLU_NO_SPLIT")) ? 1 : 0;
+  p->split = (pair == 2 && p->n_mma == 2 && block_n % 32 == 0 && !tuning().no_split) ? 1 : 0;
   const int fit = (kSmemLimit - 1024) / (int)p->stage_bytes;
   int max_stages = fit < kMaxStages ? fit : kMaxStages;
+  // Y through shared memory (tile schedules): the staging boxes take room behind the ring.  Taken when the ring keeps
+  // its depth or at least four stages (measured: the scattered per-row stores cost more than a fifth stage gains).
+  if (allow_y_tma && variant != MAGI_SWIGLU_VARIANT_STREAM && tuning().y_tma != 0) {
+    const int fit_tma = (kSmemLimit - 1024 - kStagingBytes) / (int)p->stage_bytes;
+    const int max_tma = fit_tma < kMaxStages ? fit_tma : kMaxStages;
+    const int want = stages > 0 ? stages : max_stages;
+    if (want <= max_tma || (stages == 0 && max_tma >= 4) || (tuning().y_tma == 1 && max_tma >= 2)) {
+      p->y_tma = 1;
+      max_stages = max_tma;
+    }
+  }
   if (stages == 0) stages = max_stages;
   if (stages < 2 || stages > max_stages)
     return fail(MAGI_SWIGLU_ERR_VARIANT, "stages=%d out of range [2,%d] for block_n=%d", stages, max_stages, block_n);
   p->stages = stages;
-  int smem = stages * (int)p->stage_bytes + 1024;
+  int smem = stages * (int)p->stage_bytes + 1024 + (p->y_tma ? kStagingBytes : 0);
   p->smem_bytes = smem < kSmemFloor ? kSmemFloor : smem;
   p->num_m_tiles = (int)((M + kBM * pair - 1) / (kBM * pair));
   p->num_n_tiles = (int)((N + block_n - 1) / block_n);

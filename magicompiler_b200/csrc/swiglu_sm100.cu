@@ -108,6 +108,24 @@ static int encode_maps(const void* x, const void* w, int64_t M, int64_t N, int64
   return 0;
 }
 
+// Y (or the plain GEMM's C) as a 3-D tensor [rows][halves][cols] for the epilogue's TMA stores: boxes of 32 rows x 32
+// columns (64-byte rows, 64-byte swizzle).  `halves` is 1 for the fused op and 2 for the plain GEMM, whose two
+// accumulator halves land `cols` columns apart; a box never spills from one half into the other.
+static int encode_y_map(const void* y, int64_t rows, int64_t cols, int64_t halves, int64_t ldy, CUtensorMap* tm) {
+  EncodeTiledFn enc = tensor_map_encoder();
+  if (!enc) return fail(MAGI_SWIGLU_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)halves, (cuuint64_t)rows};
+  // a dimension of extent 1 is never stepped along: give it the row pitch so the strides stay multiples of each other
+  const cuuint64_t strides[2] = {(cuuint64_t)(halves > 1 ? cols : ldy) * 2, (cuuint64_t)ldy * 2};
+  const cuuint32_t box[3] = {32, 1, 32};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(y), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MAGI_SWIGLU_ERR_DRIVER, "tensor map for Y rejected by the driver (CUresult %d)", (int)r);
+  return 0;
+}
+
 struct DeviceGuard {
   int prev = -1;
   bool changed = false;
@@ -150,8 +168,11 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   Plan p;
   if (workspace && (((uintptr_t)workspace & 255u) || workspace_bytes < 0))
     return fail(MAGI_SWIGLU_ERR_ALIGN, "workspace must be 256-byte aligned");
+  // bf16 rows a TMA store can write: Y of the fused op or C of the plain GEMM (not the quantised, pre-activation or
+  // backward outputs, whose epilogues store directly)
+  const int allow_y_tma = (!out_scale && !dy && !h) ? 1 : 0;
   int rc = make_plan(M, N, K, variant, block_n, stages, group_m, max_ctas, di->sm_count,
-                     workspace ? workspace_bytes : 0, &p);
+                     workspace ? workspace_bytes : 0, &p, allow_y_tma);
   if (rc) return rc;
 
   DeviceGuard guard;
@@ -169,7 +190,8 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
     return e == cudaSuccess ? 0 : fail_cuda(e, "launch of swiglu_simt_kernel");
   }
 
-  CUtensorMap tm_x, tm_w;
+  CUtensorMap tm_x, tm_w, tm_y;
+  memset(&tm_y, 0, sizeof(tm_y));
   if ((a_mn || b_mn) && (p.variant != MAGI_SWIGLU_VARIANT_MMA && p.variant != MAGI_SWIGLU_VARIANT_MMA2))
     return fail(MAGI_SWIGLU_ERR_VARIANT, "transposed operands need a tile schedule");
   // an MN-major B tile is made of blocks of 64 columns: every MMA must start on a block and cover whole blocks per CTA
@@ -177,6 +199,9 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
     return fail(MAGI_SWIGLU_ERR_VARIANT, "a B operand stored [K, N] needs a tile width of 64, 128 or 256 (got %d)", p.block_n);
   rc = encode_maps(x, w, M, N, K, ldx, ldw, p, &tm_x, &tm_w, a_mn, b_mn);
   if (rc) return rc;
+  // a Y layout the tensor-map encoder refuses simply keeps the direct stores (the staging boxes stay unused)
+  const int y_tma = (p.y_tma && encode_y_map(y, M, N, plain ? 2 : 1, ldy, &tm_y) == 0) ? 1 : 0;
+  g_err[0] = 0;
 
   int pair_clusters = 0;
   {
@@ -229,6 +254,7 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   a.b_second = p.b_second;
   a.split = p.split;
   a.acc_bufs = p.acc_bufs;
+  a.chains = p.chains;
   a.wide_store = (((uintptr_t)y & 31u) == 0 && ldy % 16 == 0 && (!plain || N % 16 == 0)) ? 1 : 0;
   a.plain = plain;
   a.a_mn = a_mn;
@@ -248,6 +274,8 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   a.k_splits = p.k_splits;
   a.kb_per_split = p.kb_per_split;
   a.ws = p.k_splits > 1 ? static_cast<float*>(workspace) : nullptr;
+  a.y_tma = y_tma;
+  a.wait_limit = kWaitLimitCycles;
   // Default L2 priorities (ncu, DRAM bytes per launch).  X: a band of X rows is re-read by every column tile ->
   // keep.  Y: written once -> evict first.  W: in the tile schedules a W tile is shared by all row units of the band
   // that run at the same time, and marking it evict-first makes late CTAs miss it (+25..70 % DRAM reads) -> normal;
@@ -255,16 +283,13 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   a.x_hint = 2;
   a.w_hint = (p.variant == MAGI_SWIGLU_VARIANT_STREAM) ? 1 : 0;
   a.y_hint = 1;
-  if (const char* env = getenv("MAGI_SWIGLU_L2_HINTS")) {  // three digits "xwy", each 0/1/2 (tuning aid)
-    if (strlen(env) == 3) {
-      a.x_hint = env[0] - '0';
-      a.w_hint = env[1] - '0';
-      a.y_hint = env[2] - '0';
-    }
-  }
+  const Tuning& tune = tuning();  // overrides for sweeps (environment at load, magi_swiglu_tuning afterwards)
+  if (tune.hints[0] >= 0) a.x_hint = tune.hints[0];
+  if (tune.hints[1] >= 0) a.w_hint = tune.hints[1];
+  if (tune.hints[2] >= 0) a.y_hint = tune.hints[2];
 
   if (p.ctas == 1) {
-    swiglu_tc_kernel<1><<<p.grid, kThreads, p.smem_bytes, stream>>>(tm_x, tm_w, a);
+    swiglu_tc_kernel<1><<<p.grid, kThreads, p.smem_bytes, stream>>>(tm_x, tm_w, tm_y, a);
     e = cudaGetLastError();
     if (e != cudaSuccess) return fail_cuda(e, "launch of swiglu_tc_kernel<1>");
     if (p.k_splits > 1) {
@@ -301,7 +326,7 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   cfg.stream = stream;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, swiglu_tc_kernel<2>, tm_x, tm_w, a);
+  e = cudaLaunchKernelEx(&cfg, swiglu_tc_kernel<2>, tm_x, tm_w, tm_y, a);
   return e == cudaSuccess ? 0 : fail_cuda(e, "launch of swiglu_tc_kernel<2>");
 }
 
@@ -367,6 +392,9 @@ int magi_swiglu_forward_bf16_static(const void* x, const void* w_gate_up, void* 
   if (M == 0 && N > 0 && K > 0) return 0;
   const magi::DeviceInfo* di = magi::device_info(device);
   if (!di) return magi::fail(MAGI_SWIGLU_ERR_DEVICE, "device %d is not available", device);
+  if (di->cc_major != 10 || di->cc_minor != 0)  // before the symbol look-up, which has no image on other GPUs
+    return magi::fail(MAGI_SWIGLU_ERR_DEVICE, "device %d is sm_%d%d; this library runs on sm_100 (B200) only", device,
+                      di->cc_major, di->cc_minor);
   // the schedule the scratch-taking entry point prefers for this problem, and the scratch it wants
   magi::Plan p;
   int rc = magi::make_plan(M, N, K, MAGI_SWIGLU_VARIANT_AUTO, 0, 0, 0, 0, di->sm_count, magi::kWorkspaceCap, &p);
@@ -572,7 +600,7 @@ int64_t magi_swiglu_workspace_bytes(int64_t M, int64_t N, int64_t K, int variant
 }
 
 int magi_swiglu_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, int stages, int group_m, int max_ctas,
-                     int device, int sm_count, int32_t out[12]) {
+                     int device, int sm_count, int32_t out[16]) {
   magi::g_err[0] = 0;
   if (!out) return magi::fail(MAGI_SWIGLU_ERR_NULL, "out is null");
   if (sm_count <= 0) {
@@ -595,6 +623,9 @@ int magi_swiglu_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
   out[9] = p.group_m;
   out[10] = p.split;
   out[11] = p.k_splits;
+  out[12] = p.y_tma;
+  out[13] = p.chains;
+  out[14] = out[15] = 0;
   return 0;
 }
 
@@ -619,11 +650,57 @@ int magi_swiglu_device_status(int device, int32_t out[4]) {
   return 0;
 }
 
+int magi_swiglu_tuning(int knob, int value) {
+  magi::g_err[0] = 0;
+  magi::Tuning& t = magi::tuning();
+  int prev = 0;
+  switch (knob) {
+    case MAGI_SWIGLU_TUNE_K_SPLITS:
+      prev = t.k_splits;
+      t.k_splits = value > 0 ? value : 0;
+      return prev;
+    case MAGI_SWIGLU_TUNE_NO_SPLIT:
+      prev = t.no_split;
+      t.no_split = value != 0;
+      return prev;
+    case MAGI_SWIGLU_TUNE_Y_TMA:
+      prev = t.y_tma;
+      t.y_tma = value < 0 ? -1 : (value != 0);
+      return prev;
+    case MAGI_SWIGLU_TUNE_CHAINS:
+      prev = t.chains;
+      t.chains = (value == 1 || value == 2 || value == 4) ? value : 0;
+      return prev;
+    case MAGI_SWIGLU_TUNE_L2_HINTS: {
+      prev = t.hints[0] < 0 ? -1 : t.hints[0] * 100 + t.hints[1] * 10 + t.hints[2];
+      const int h[3] = {value / 100, (value / 10) % 10, value % 10};
+      const bool ok = value >= 0 && h[0] <= 2 && h[1] <= 2 && h[2] <= 2;
+      for (int i = 0; i < 3; ++i) t.hints[i] = ok ? h[i] : -1;
+      return prev;
+    }
+    default:
+      return magi::fail(MAGI_SWIGLU_ERR_VARIANT, "unknown tuning knob %d", knob);
+  }
+}
+
+int magi_swiglu_watchdog_selftest(int device, void* cuda_stream, int64_t limit_cycles) {
+  magi::g_err[0] = 0;
+  if (limit_cycles < 1000 || limit_cycles > 2000000000LL)
+    return magi::fail(MAGI_SWIGLU_ERR_SHAPE, "limit_cycles=%lld out of range [1000, 2e9]", (long long)limit_cycles);
+  if (!magi::device_info(device)) return magi::fail(MAGI_SWIGLU_ERR_DEVICE, "device %d is not available", device);
+  magi::DeviceGuard guard;
+  cudaError_t e = guard.set(device);
+  if (e != cudaSuccess) return magi::fail_cuda(e, "cudaSetDevice");
+  magi::watchdog_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>((long long)limit_cycles);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : magi::fail_cuda(e, "launch of watchdog_selftest_kernel");
+}
+
 #ifdef MAGI_SWIGLU_TRACE
-int magi_swiglu_trace(long long out[16]) {  // reads the trace and clears its accumulating slots
+int magi_swiglu_trace(long long out[32]) {  // reads the trace and clears its accumulating slots
   cudaDeviceSynchronize();
-  int rc = (int)cudaMemcpyFromSymbol(out, magi::g_trace, sizeof(long long) * 16);
-  long long zero[16] = {0};
+  int rc = (int)cudaMemcpyFromSymbol(out, magi::g_trace, sizeof(long long) * 32);
+  long long zero[32] = {0};
   cudaMemcpyToSymbol(magi::g_trace, zero, sizeof(zero));
   return rc;
 }

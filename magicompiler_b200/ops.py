@@ -65,18 +65,13 @@ def _rows_view(t: torch.Tensor, cols: int) -> torch.Tensor:
     return t2 if ok else t2.contiguous()
 
 
-_workspaces: dict[tuple[int, int], torch.Tensor] = {}
-
-
-def _workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
-    """Scratch for split-K schedules, one per (device, stream) so launches that may overlap never share one.
-    It comes from torch's caching allocator (capture-aware); the library itself allocates nothing."""
-    key = (device.index if device.index is not None else torch.cuda.current_device(), stream)
-    ws = _workspaces.get(key)
-    if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        _workspaces[key] = ws
-    return ws
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Scratch for one split-K call, taken from torch's caching allocator on the current stream and dropped when the
+    call returns.  The allocator orders the block's reuse after this stream's work, keeps it apart from launches on
+    other streams, and, under CUDA-graph capture, gives it to the graph's private pool for as long as the graph lives
+    — so no captured graph can be left with a dangling scratch address and nothing accumulates per stream.  The
+    library itself allocates nothing."""
+    return torch.empty(nbytes, dtype=torch.uint8, device=device)
 
 
 _ws_need: dict[tuple, int] = {}  # (M, N, K, schedule knobs, device) -> scratch bytes the preferred schedule wants
@@ -127,7 +122,7 @@ def gemm_swiglu_out(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor 
             need = lib.magi_swiglu_workspace_bytes(M, N, K, v, block_n, stages, group_m, max_ctas, dev, 0)
             _ws_need[key] = need
         if need > 0:
-            ws = _workspace(x.device, stream, need)
+            ws = _workspace(x.device, need)
             ws_ptr, ws_len = ws.data_ptr(), ws.numel()
     rc = lib.magi_swiglu_forward_bf16_ws(x2.data_ptr(), w2.data_ptr(), y.data_ptr(), M, N, K, ldx, w2.stride(0),
                                          y.stride(0), dev, stream, v, block_n, stages, group_m, max_ctas,
@@ -138,8 +133,8 @@ def gemm_swiglu_out(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor 
     return y if x.dim() == 2 else y.view(*x.shape[:-1], N)
 
 
-def _split_env() -> str | None:
-    return os.environ.get("MAGI_SWIGLU_K_SPLITS")  # tuning aid of the library; part of the cache key
+def _split_env() -> int:
+    return _loader.tuning_epoch()  # a changed tuning aid of the library changes the scratch a shape wants
 
 
 RMS_OP_NAME = "magi_swiglu::rmsnorm_gemm_swiglu"
@@ -180,7 +175,7 @@ def rmsnorm_gemm_swiglu(x: torch.Tensor, w_folded: torch.Tensor, eps: float) -> 
         if M <= 128:
             need = lib.magi_swiglu_workspace_bytes(M, N, K, 0, 0, 0, 0, 0, dev, 0)
             if need > 0:
-                ws = _workspace(x.device, stream, need)
+                ws = _workspace(x.device, need)
                 ws_ptr, ws_len = ws.data_ptr(), ws.numel()
         rc = lib.magi_swiglu_forward_bf16_scaled(x2.data_ptr(), w_folded.data_ptr(), y.data_ptr(), scale.data_ptr(), M, N,
                                                  K, ldx, K, N, dev, stream, ws_ptr, ws_len)

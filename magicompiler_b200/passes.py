@@ -32,7 +32,7 @@ PACK_OP_NAME = "magi_swiglu::pack_gate_up_cached"
 _pack_cache: dict[tuple[int, int], tuple] = {}
 
 
-def _pack_meta(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+def _pack_meta(w_gate: torch.Tensor, w_up: torch.Tensor, frozen: bool = True) -> torch.Tensor:
     return w_gate.new_empty((w_gate.shape[0] + w_up.shape[0], w_gate.shape[1]))
 
 
@@ -42,40 +42,81 @@ def _pack_setup_context(ctx, inputs, output):
 
 def _pack_backward(ctx, grad):
     # the packed weight is cat([gate, up]): its gradient splits back into the two halves (training through the pass)
-    return grad[: ctx.gate_rows], grad[ctx.gate_rows:]
+    return grad[: ctx.gate_rows], grad[ctx.gate_rows:], None
+
+
+_retired_packs: list[torch.Tensor] = []  # packed buffers a CUDA graph may still read (see pack_gate_up_cached)
+
+
+def _capturing(t: torch.Tensor) -> bool:
+    return bool(t.is_cuda and torch.cuda.is_current_stream_capturing())
 
 
 @magi_register_custom_op(name=PACK_OP_NAME, mutates_args=(), infer_output_meta_fn=_pack_meta,
                          setup_context_fn=_pack_setup_context, backward_fn=_pack_backward)
-def pack_gate_up_cached(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
-    """``cat([w_gate, w_up])``, memoised on the identity, version counter and address of both arguments.
-
-    The cache entry dies with either argument (weak references).  A weight that is updated in place (optimizer
-    step) bumps its version counter and is packed again; tensors that are new objects on every call (a weight
-    offloaded to the host and brought back per iteration) are packed on every call.
-    """
+def _pack_gate_up_op(w_gate: torch.Tensor, w_up: torch.Tensor, frozen: bool) -> torch.Tensor:
     if w_gate.dim() != 2 or w_gate.shape != w_up.shape or w_gate.dtype != w_up.dtype or w_gate.device != w_up.device:
         raise ValueError(f"gate {tuple(w_gate.shape)}/{w_gate.dtype} and up {tuple(w_up.shape)}/{w_up.dtype} differ")
+    if not frozen:
+        return torch.cat([w_gate, w_up], dim=0)  # trainable weights: never memoised
     key = (id(w_gate), id(w_up))
     stamp = (w_gate._version, w_up._version, w_gate.data_ptr(), w_up.data_ptr())
     hit = _pack_cache.get(key)
     if hit is not None:
-        ref_g, ref_u, old_stamp, packed = hit
+        ref_g, ref_u, old_stamp, packed, in_graph = hit
         if ref_g() is w_gate and ref_u() is w_up and old_stamp == stamp:
+            if _capturing(packed) and not in_graph:
+                _pack_cache[key] = (ref_g, ref_u, old_stamp, packed, True)
             return packed
+        if in_graph:
+            _retired_packs.append(packed)  # a captured graph may replay with this address
     packed = torch.cat([w_gate, w_up], dim=0)
 
     def _drop(_ref, key=key):
-        _pack_cache.pop(key, None)
+        entry = _pack_cache.pop(key, None)
+        if entry is not None and entry[4]:
+            _retired_packs.append(entry[3])
 
     try:
-        _pack_cache[key] = (weakref.ref(w_gate, _drop), weakref.ref(w_up, _drop), stamp, packed)
+        _pack_cache[key] = (weakref.ref(w_gate, _drop), weakref.ref(w_up, _drop), stamp, packed, _capturing(packed))
     except TypeError:  # fake / functional tensors during tracing cannot be weakly referenced: do not cache
         pass
     return packed
 
 
+def weights_are_frozen(w_gate: torch.Tensor, w_up: torch.Tensor) -> bool:
+    """True unless a gradient can be asked for: grad mode on and either weight requiring grad."""
+    return not (torch.is_grad_enabled() and (w_gate.requires_grad or w_up.requires_grad))
+
+
+def pack_gate_up_cached(w_gate: torch.Tensor, w_up: torch.Tensor, frozen: bool | None = None) -> torch.Tensor:
+    """``cat([w_gate, w_up])`` through the op ``magi_swiglu::pack_gate_up_cached(w_gate, w_up, frozen)``, memoised for
+    FROZEN weights only.
+
+    The memo is keyed on the identity, version counter and address of both arguments and its entry dies with either
+    argument (weak references).  That key cannot see every way a training loop changes a weight (``param.data = ...``
+    keeps the version counter, ``param.data.copy_()`` counts elsewhere, FSDP re-points ``param.data`` at a freshly
+    gathered buffer that the allocator tends to place at the old address), so nothing is memoised while a gradient
+    can be asked for: ``frozen`` defaults to ``weights_are_frozen(w_gate, w_up)`` (the rewrite pass decides the same
+    way when it traces) and with ``frozen=False`` the concatenation runs on every call — one weight copy beside the
+    GEMM.  Frozen weights are taken at their word; code that overwrites them behind autograd's back calls
+    ``clear_pack_cache()`` afterwards.  Tensors that are new objects on every call (a weight offloaded to the host and
+    brought back per iteration) are packed on every call in either mode.
+
+    A packed buffer that was handed out while a CUDA graph was being captured is never freed by a later re-pack:
+    the graph has its address baked in, so the buffer is kept for the life of the process.
+    """
+    if frozen is None:
+        frozen = weights_are_frozen(w_gate, w_up)
+    return torch.ops.magi_swiglu.pack_gate_up_cached(w_gate, w_up, bool(frozen))
+
+
 def clear_pack_cache() -> None:
+    """Forget every memoised packed weight (call it after overwriting frozen weights in a way autograd's version
+    counter does not see).  Buffers that a captured CUDA graph may still read stay alive."""
+    for entry in _pack_cache.values():
+        if entry[4]:
+            _retired_packs.append(entry[3])
     _pack_cache.clear()
 
 
@@ -187,6 +228,15 @@ class FuseSwiGLUPass(_PassBase):
             return False
         return any(isinstance(_example(n), torch.Tensor) and _example(n).requires_grad for n in nodes)
 
+    @staticmethod
+    def _frozen(*weights: torch.fx.Node) -> bool:
+        """Whether the traced weights may be memoised once packed: only when the trace shows that no gradient can be
+        asked for (grad mode off, or every weight known not to require grad); unknown counts as trainable."""
+        if not torch.is_grad_enabled():
+            return True
+        evs = [_example(w) for w in weights]
+        return all(isinstance(ev, torch.Tensor) and not ev.requires_grad for ev in evs)
+
     def _matches(self, graph: torch.fx.Graph):
         found = []
         for mul in graph.nodes:
@@ -265,7 +315,8 @@ class FuseSwiGLUPass(_PassBase):
         for mul, act, gate, up in self._matches(graph):
             x, wg, wu = gate.args[0], gate.args[1], up.args[1]
             with graph.inserting_before(mul):
-                packed = graph.call_function(torch.ops.magi_swiglu.pack_gate_up_cached.default, (wg, wu))
+                packed = graph.call_function(torch.ops.magi_swiglu.pack_gate_up_cached.default,
+                                             (wg, wu, self._frozen(wg, wu)))
                 if self._keep_preactivations(x, wg, wu):
                     both = graph.call_function(torch.ops.magi_swiglu.gemm_swiglu_preact.default, (x, packed))
                     fused = graph.call_function(operator.getitem, (both, 0))

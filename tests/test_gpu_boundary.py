@@ -4,8 +4,9 @@ import pytest
 import torch
 
 import magicompiler_b200 as mb
+from magicompiler_b200 import _loader
 from magicompiler_b200.sharding import reference_mlp
-from oracle import make_inputs
+from oracle import TOL_FROB, TOL_MAX_NORM, error_metrics, make_inputs, swiglu_gold
 
 pytestmark = pytest.mark.gpu
 
@@ -99,6 +100,53 @@ def test_rewrite_pass_on_gpu_matches_eager_module():
         got, ref = cm(x), m(x)
         assert torch.allclose(got.float(), ref.float(), rtol=2e-2, atol=2e-2 * ref.float().abs().max().item())
     assert counts == [1] and len(_pack_cache) == 1
+
+
+def test_scratch_of_a_captured_graph_survives_later_larger_calls():
+    """A split-K call captured into a CUDA graph keeps its scratch for the life of the graph: a later eager call that
+    needs more scratch, and allocations over whatever was freed, must not disturb the graph's replay."""
+    M1, M2, N, K = 16, 128, 3584, 8192  # 1/8 decode shards: both split K; the second wants more scratch
+    assert 0 < mb.workspace_bytes(M1, N, K) < mb.workspace_bytes(M2, N, K)
+    x1, w = make_inputs(M1, K, N, seed=31)
+    x2, _ = make_inputs(M2, K, N, seed=32)
+    x1, x2, w = x1.cuda(), x2.cuda(), w.cuda()
+    expect1 = mb.gemm_swiglu(x1, w)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        mb.gemm_swiglu(x1, w)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y_graph = mb.gemm_swiglu(x1, w)
+    expect2 = mb.gemm_swiglu(x2, w)                      # larger scratch, eager
+    junk = [torch.full((1 << 20,), float("nan"), device="cuda") for _ in range(64)]  # lands on freed blocks
+    y_graph.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(y_graph, expect1)
+    assert torch.equal(mb.gemm_swiglu(x2, w), expect2)
+    del junk
+
+
+def test_bounded_wait_gives_up_reports_and_clears():
+    """The kernels' bounded wait by itself: a one-block kernel waits on a barrier nothing signals, gives up after about
+    a millisecond, returns normally and leaves {role, block, index} for device_status; the status clears on read and
+    the next launch of the real kernel on the same context is correct."""
+    import ctypes
+
+    lib = _loader.load_library()
+    assert mb.device_status(0)["code"] == 0
+    rc = lib.magi_swiglu_watchdog_selftest(0, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), 2_000_000)
+    assert rc == 0, _loader.last_error()
+    st = mb.device_status(0)  # synchronises
+    assert st == {"code": 7, "block": 0, "index": 42, "parity": 0}, st
+    assert mb.device_status(0)["code"] == 0, "reading the status clears it"
+    assert lib.magi_swiglu_watchdog_selftest(0, None, 10) < 0  # limit out of range: rejected on the host
+    x, w = make_inputs(256, 1024, 2816, seed=0)
+    y = mb.gemm_swiglu(x.cuda(), w.cuda())
+    m = error_metrics(y, swiglu_gold(x, w, want_eager=False)["gold"])
+    assert m["max_norm"] <= TOL_MAX_NORM and m["frob"] <= TOL_FROB and mb.device_status(0)["code"] == 0
 
 
 # ---------------------------------------------------------------- backward (training)

@@ -242,12 +242,17 @@ def test_decode_column_shards_split_k(M, n_shard):
 
 @pytest.mark.parametrize("splits", [2, 3, 5, 8])
 @pytest.mark.parametrize("shape", [(1, 264, 2048), (37, 72, 4096), (128, 528, 2304), (100, 2816, 1024)])
-def test_forced_k_splits_ragged(monkeypatch, splits, shape):
+def test_forced_k_splits_ragged(splits, shape):
     M, N, K = shape
-    monkeypatch.setenv("MAGI_SWIGLU_K_SPLITS", str(splits))
-    x, w = make_inputs(M, K, N, seed=splits + M)
-    y = mb.gemm_swiglu_out(x.cuda(), w.cuda(), variant="stream")
-    y2 = mb.gemm_swiglu_out(x.cuda(), w.cuda(), variant="stream")
+    prev = _loader.set_tuning("k_splits", splits)
+    try:
+        # the forced count is used unless it would leave a split without K-steps (then the planner chooses)
+        assert mb.plan(M, N, K, variant="stream")["k_splits"] in ({splits} if (-(-K // 64) // splits) >= 4 else {1, 2, 3, 4, 5, 6, 7, 8})
+        x, w = make_inputs(M, K, N, seed=splits + M)
+        y = mb.gemm_swiglu_out(x.cuda(), w.cuda(), variant="stream")
+        y2 = mb.gemm_swiglu_out(x.cuda(), w.cuda(), variant="stream")
+    finally:
+        _loader.set_tuning("k_splits", prev)
     assert_parity(y, swiglu_gold(x, w, want_eager=False)["gold"], f"{shape} z={splits}")
     assert torch.equal(y, y2)
 

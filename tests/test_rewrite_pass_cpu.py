@@ -68,6 +68,30 @@ def test_pattern_is_rewritten_to_the_fused_op():
     assert tuple(y.shape) == (10, 64) and y.dtype == torch.bfloat16
 
 
+def test_pass_memoises_the_packed_weight_only_for_frozen_weights():
+    """The pack node carries `frozen`: False when the trace shows trainable weights with grad mode on (the weight is
+    concatenated on every call), True under no_grad or when no weight requires grad (packed once)."""
+    def frozen_flags(module, ctx):
+        flags = []
+
+        def backend(gm, example_inputs):
+            FuseSwiGLUPass(allowed_devices=("meta",), save_preactivations=False)(gm.graph)
+            flags.extend(n.args[2] for n in gm.graph.nodes if n.op == "call_function" and n.target is PACK)
+            gm.recompile()
+            return gm.forward
+
+        torch._dynamo.reset()
+        with ctx:
+            torch.compile(module, backend=backend, fullgraph=True)(torch.empty(4, 64, dtype=torch.bfloat16, device="meta"))
+        return flags
+
+    import contextlib
+
+    assert frozen_flags(MLP(), contextlib.nullcontext()) == [False]          # trainable parameters, grad mode on
+    assert frozen_flags(MLP(), torch.no_grad()) == [True]                     # inference
+    assert frozen_flags(MLP().requires_grad_(False), contextlib.nullcontext()) == [True]
+
+
 def test_training_variant_emits_the_two_output_op():
     import operator
 
@@ -185,7 +209,37 @@ def test_cached_packer_packs_once_and_tracks_updates():
         pack_gate_up_cached(torch.zeros(4, 8), torch.zeros(6, 8))
 
 
-# a MagiCompiler checkout: $MAGI_COMPILER_ROOT, else a directory "reference" next to this repository
+def test_cached_packer_never_memoises_trainable_weights():
+    """Weight updates that autograd's version counter does not see (``param.data.copy_``, ``param.data = new``,
+    also at the SAME address, which is what FSDP's re-gathered flat parameter looks like) must reach the next call
+    while the weights are trainable: nothing is memoised when a gradient can be asked for."""
+    from magicompiler_b200 import passes
+
+    clear_pack_cache()
+    wg = torch.nn.Parameter(torch.randn(16, 8))
+    wu = torch.nn.Parameter(torch.randn(16, 8))
+    p1 = pack_gate_up_cached(wg, wu)
+    assert torch.equal(p1, torch.cat([wg, wu])) and len(passes._pack_cache) == 0
+    v = (wg._version, wu._version)
+    wg.data.copy_(torch.full((16, 8), 3.0))          # counted on .data's own counter, not on the parameter's
+    assert (wg._version, wu._version) == v
+    assert torch.equal(pack_gate_up_cached(wg, wu)[:16], torch.full((16, 8), 3.0))
+    fresh = torch.full((16, 8), 5.0)
+    wu.data = fresh                                     # re-pointed: same object, same version
+    assert torch.equal(pack_gate_up_cached(wg, wu)[16:], fresh)
+    old_ptr = wu.data_ptr()
+    wu.data.zero_()                                     # new contents at the SAME address
+    assert wu.data_ptr() == old_ptr and float(pack_gate_up_cached(wg, wu)[16:].detach().abs().max()) == 0.0
+    # without grad mode the same parameters count as frozen: memoised, and clear_pack_cache() is the explicit reset
+    with torch.no_grad():
+        q1 = pack_gate_up_cached(wg, wu)
+        assert pack_gate_up_cached(wg, wu).data_ptr() == q1.data_ptr() and len(passes._pack_cache) == 1
+        wg.data.fill_(7.0)
+        clear_pack_cache()
+        assert float(pack_gate_up_cached(wg, wu)[:16].min()) == 7.0
+    clear_pack_cache()
+
+
 def test_cached_packer_passes_gradients_to_both_weights():
     clear_pack_cache()
     wg = torch.nn.Parameter(torch.randn(8, 16))

@@ -232,8 +232,8 @@ int64_t magi_swiglu_workspace_bytes(int64_t M, int64_t N, int64_t K, int variant
  * out[4]=tiles, out[5]=dynamic shared memory bytes, out[6]=accumulator buffers,
  * out[7]=MMAs per K=16 step, out[8]=CTAs per tile (1 or 2), out[9]=row units per raster band,
  * out[10]=1 if the tile is released to the MMA issuer in two halves, out[11]=CTAs that split K for one tile,
- * out[12]=1 if Y leaves through shared memory and TMA stores (0 = direct stores), out[13]=accumulator sets per
- * slab that consecutive K=16 steps rotate through (1, 2 or 4), out[14..15]=0 (reserved).
+ * out[12]=1 if Y leaves through shared memory and TMA stores (0 = direct stores), out[13]=number of trailing tiles
+ * whose K-steps are dealt to the workers as equal ranges (stream-K; 0 = whole tiles only), out[14..15]=0 (reserved).
  * `sm_count` <= 0 means "query `device`".  Needs no GPU when sm_count > 0.
  * Replaces: nothing in the reference. */
 int magi_swiglu_plan(int64_t M, int64_t N, int64_t K, int variant,
@@ -250,14 +250,24 @@ int magi_swiglu_plan(int64_t M, int64_t N, int64_t K, int variant,
  * Replaces: nothing in the reference. */
 int magi_swiglu_device_status(int device, int32_t out[4]);
 
+/* The work items worker `unit` (a CTA, or a CTA pair) of the planned schedule walks through, in order, without
+ * launching anything: up to max_items records of six ints {tile, first K-step, end K-step, role, first peer, peers}
+ * are written to `out`, and the number of items the worker has is returned (negative = error).  role 0 = the whole
+ * K range given, nothing to exchange; 1 = head piece of a stream-K tile: the worker owns the tile and adds the sums
+ * that workers first_peer .. first_peer+peers-1 park in scratch; 2 = a later piece: the worker parks its sums.
+ * `workspace_bytes` is the scratch the caller would pass (0 = none: whole tiles only).  Pure host arithmetic.
+ * Replaces: nothing in the reference. */
+int magi_swiglu_schedule(int64_t M, int64_t N, int64_t K, int variant, int block_n, int stages, int group_m, int max_ctas,
+                         int sm_count, int64_t workspace_bytes, int unit, int32_t* out, int max_items);
+
 /* Tuning aids for sweeps and tests (process-wide; not meant for production callers).  Sets knob `knob` to `value`
  * and returns the previous value (for K_SPLITS/NO_SPLIT/Y_TMA >= -1, for L2_HINTS -1 or xwy), or
  * MAGI_SWIGLU_ERR_VARIANT for an unknown knob.  Initial values come from the environment, read once when the first
- * plan is made: MAGI_SWIGLU_K_SPLITS, MAGI_SWIGLU_NO_SPLIT, MAGI_SWIGLU_Y_TMA, MAGI_SWIGLU_L2_HINTS, MAGI_SWIGLU_CHAINS.
+ * plan is made: MAGI_SWIGLU_K_SPLITS, MAGI_SWIGLU_NO_SPLIT, MAGI_SWIGLU_Y_TMA, MAGI_SWIGLU_L2_HINTS, MAGI_SWIGLU_STREAM_K.
  *   K_SPLITS  z > 0: force z-way split-K in the STREAM schedule (0 = choose)
  *   NO_SPLIT  1: drain CTA-pair tiles in one piece instead of two separately released halves
  *   Y_TMA     0 / 1: force direct stores / shared memory + TMA stores for Y in the tile schedules (-1 = choose)
- *   CHAINS    1 / 2 / 4: at most that many accumulator sets per slab in the STREAM schedule (0 = choose)
+ *   STREAM_K  0 / 1: never / whenever possible, balance the last waves of the tile schedules by K ranges (-1 = choose)
  *   L2_HINTS  three decimal digits xwy, each 0 normal / 1 evict-first / 2 evict-last, for X tiles, W tiles and Y
  *             stores (-1 = defaults)
  * Replaces: nothing in the reference. */
@@ -265,7 +275,7 @@ int magi_swiglu_device_status(int device, int32_t out[4]);
 #define MAGI_SWIGLU_TUNE_NO_SPLIT 1
 #define MAGI_SWIGLU_TUNE_Y_TMA    2
 #define MAGI_SWIGLU_TUNE_L2_HINTS 3
-#define MAGI_SWIGLU_TUNE_CHAINS   4
+#define MAGI_SWIGLU_TUNE_STREAM_K 4
 int magi_swiglu_tuning(int knob, int value);
 
 /* Runs the kernels' bounded wait by itself: a one-block kernel whose thread 0 waits on an mbarrier that nothing

@@ -105,6 +105,9 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.magi_swiglu_plan.argtypes = [i64, i64, i64, i32, i32, i32, i32, i32, i32, i32, ctypes.POINTER(ctypes.c_int32)]
     lib.magi_swiglu_device_status.restype = i32
     lib.magi_swiglu_device_status.argtypes = [i32, ctypes.POINTER(ctypes.c_int32)]
+    lib.magi_swiglu_schedule.restype = i32
+    lib.magi_swiglu_schedule.argtypes = [i64, i64, i64, i32, i32, i32, i32, i32, i32, i64, i32,
+                                         ctypes.POINTER(ctypes.c_int32), i32]
     lib.magi_swiglu_tuning.restype = i32
     lib.magi_swiglu_tuning.argtypes = [i32, i32]
     lib.magi_swiglu_watchdog_selftest.restype = i32
@@ -139,7 +142,7 @@ def load_library() -> ctypes.CDLL:
     return lib
 
 
-TUNING_KNOBS = {"k_splits": 0, "no_split": 1, "y_tma": 2, "l2_hints": 3, "chains": 4}
+TUNING_KNOBS = {"k_splits": 0, "no_split": 1, "y_tma": 2, "l2_hints": 3, "stream_k": 4}
 _tuning_epoch = 0  # bumped by set_tuning so host-side caches keyed on the schedule notice
 
 
@@ -171,8 +174,23 @@ def plan(M: int, N: int, K: int, variant: str | int = "auto", block_n: int = 0, 
     if rc != 0:
         raise ValueError(f"magi_swiglu_plan failed ({rc}): {last_error()}")
     keys = ["variant", "block_n", "stages", "grid", "tiles", "smem_bytes", "acc_bufs", "n_mma", "ctas", "group_m", "split", "k_splits",
-            "y_tma", "chains"]
+            "y_tma", "sk_tiles"]
     return dict(zip(keys, list(out)[:len(keys)]))
+
+
+def schedule(M: int, N: int, K: int, unit: int, variant: str | int = "auto", block_n: int = 0, stages: int = 0,
+             group_m: int = 0, max_ctas: int = 0, sm_count: int = 148, workspace_bytes: int = 64 << 20) -> list[dict]:
+    """The work items worker ``unit`` (a CTA or CTA pair) of the planned schedule walks through, in order
+    (``magi_swiglu_schedule``; pure host arithmetic): dicts with tile, K-step range, role and peers."""
+    lib = load_library()
+    v = VARIANTS[variant] if isinstance(variant, str) else int(variant)
+    cap = 1 << 16
+    buf = (ctypes.c_int32 * (6 * cap))()
+    n = lib.magi_swiglu_schedule(M, N, K, v, block_n, stages, group_m, max_ctas, sm_count, workspace_bytes, unit, buf, cap)
+    if n < 0:
+        raise ValueError(f"magi_swiglu_schedule failed ({n}): {last_error()}")
+    keys = ("tile", "kb0", "kb1", "role", "first_peer", "peers")
+    return [dict(zip(keys, buf[6 * i:6 * i + 6])) for i in range(min(n, cap))]
 
 
 def workspace_bytes(M: int, N: int, K: int, variant: str | int = "auto", block_n: int = 0, stages: int = 0,

@@ -82,9 +82,6 @@ struct KArgs {
   int split;          // CTA pairs, two MMAs: tensor memory holds [gate_lo|up_lo|gate_hi|up_hi]; the low half of
                       // the tile is handed back to the MMA issuer before the high half has been drained
   int acc_bufs;       // tensor-memory accumulator buffers (2 = epilogue overlaps next tile)
-  int chains;         // 1, 2 or 4 accumulator sets per buffer: consecutive K=16 steps add into different sets (an MMA
-                      // that accumulates into the columns of the one before it issues ~180 cycles after it; narrow
-                      // slabs of the STREAM schedule are bound by that), the epilogue adds the sets in a fixed order
   int wide_store;     // y base and row pitch are 32-byte aligned: 256-bit stores (one full sector per thread)
   const float* row_scale;  // optional [M] fp32: accumulators of row m are multiplied by row_scale[m] before the
                            // epilogue (a fused RMSNorm: 1/rms(x_m), the norm weight being folded into W); null = none
@@ -109,6 +106,15 @@ struct KArgs {
   // k_splits == 1: no scratch is touched.
   int k_splits, kb_per_split;
   float* ws;  // [tile][split][M rows][2*block_n] fp32
+  // Stream-K (tile schedules, with scratch): tiles [0, sk_first_tile) are whole-tile work items dealt round-robin
+  // in full waves; the K-steps of the remaining tiles (one full wave plus the partial one) form one iteration space
+  // cut into equal ranges, one per CTA (pair), so the last wave is never mostly empty.  A range that ends inside a
+  // tile leaves that tile's head piece with this unit (the owner) and its later piece with the next unit, which
+  // parks fp32 partial sums in scratch slot `unit` and raises sk_flags[unit * kCtas + cta_rank] once per epilogue
+  // warp; the owner adds them before its epilogue.  sk_first_tile == number of tiles: off.
+  int sk_first_tile, sk_iters_per_unit, sk_total_iters, sk_min_kb;
+  int* sk_flags;       // [units * kCtas], zeroed by the host before the launch
+  float* sk_partials;  // [units * kCtas][8 epilogue warps][chunks per warp][16 float4][32 lanes] fp32
   int y_tma;  // 1: bf16 Y (or the plain GEMM's C) leaves through shared memory and TMA stores (tm_y is valid)
   long long wait_limit;  // SM cycles after which a wait on an mbarrier gives up (kWaitLimitCycles by default)
 };
@@ -134,6 +140,104 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
     }
   }
 }
+
+// Bounded wait for a counter in global memory that CTAs of the same launch raise (stream-K hand-over).
+__device__ __forceinline__ bool wait_flag_bounded(const int* flag, int target, volatile int* abort_flag, unsigned role,
+                                                  unsigned idx, long long limit) {
+  const long long t0 = clock64();
+  unsigned spins = 0;
+  while (true) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v >= target) return true;
+    if ((++spins & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > limit) {
+        *abort_flag = 1;
+        if (atomicCAS(&g_watchdog[0], 0u, role) == 0u) {
+          g_watchdog[1] = blockIdx.x;
+          g_watchdog[2] = idx;
+          g_watchdog[3] = (unsigned)v;
+        }
+        return false;
+      }
+    }
+  }
+}
+
+// One piece of work of a CTA (pair): a whole tile, one split of a STREAM split-K tile, or a K range of a stream-K tile.
+struct WorkItem {
+  int t;                 // tile index in raster order
+  int kb0, kb1;          // K-steps [kb0, kb1)
+  int zsplit;            // STREAM split-K: which split of the tile
+  int sk_role;           // stream-K: 0 whole tile, 1 head piece (owns the tile), 2 later piece (parks partial sums)
+  int sk_first_peer, sk_peers;  // head piece: units first_peer .. first_peer + peers - 1 hold the tile's other pieces
+};
+
+// First iteration of unit v's stream-K range: v equal shares, moved to a tile boundary when the cut would leave a
+// piece shorter than sk_min_kb K-steps.  Both neighbours evaluate the same function, so ranges tile the space.
+__host__ __device__ __forceinline__ int sk_boundary(const KArgs& a, int v) {
+  const long long raw = (long long)v * a.sk_iters_per_unit;
+  const int x = raw < a.sk_total_iters ? (int)raw : a.sk_total_iters;
+  const int off = x % a.num_k_blocks;
+  if (off == 0) return x;
+  if (off < a.sk_min_kb) return x - off;
+  if (a.num_k_blocks - off < a.sk_min_kb) return x + (a.num_k_blocks - off);
+  return x;
+}
+
+// The sequence of work items of one unit; every role of the CTA walks the same sequence.
+struct WorkIter {
+  const KArgs& a;
+  int unit, units, item, cur, end;
+  bool in_sk;
+  __host__ __device__ __forceinline__ WorkIter(const KArgs& args, int unit_, int units_)
+      : a(args), unit(unit_), units(units_), item(unit_), cur(0), end(0), in_sk(false) {}
+  __host__ __device__ __forceinline__ bool next(WorkItem& w) {
+    if (!in_sk) {
+      const int dp_items = a.sk_first_tile * a.k_splits;
+      if (item < dp_items) {
+        w.t = item / a.k_splits;
+        w.zsplit = item - w.t * a.k_splits;
+        w.kb0 = w.zsplit * a.kb_per_split;
+        w.kb1 = w.kb0 + a.kb_per_split < a.num_k_blocks ? w.kb0 + a.kb_per_split : a.num_k_blocks;
+        w.sk_role = 0;
+        w.sk_first_peer = w.sk_peers = 0;
+        item += units;
+        return true;
+      }
+      in_sk = true;
+      if (a.sk_total_iters > 0) {
+        cur = sk_boundary(a, unit);
+        end = sk_boundary(a, unit + 1);
+      }
+    }
+    if (cur >= end) return false;
+    const int nk = a.num_k_blocks;
+    const int t_rel = cur / nk;
+    const int off = cur - t_rel * nk;
+    const int tile_end = (t_rel + 1) * nk;
+    const int piece_end = end < tile_end ? end : tile_end;
+    w.t = a.sk_first_tile + t_rel;
+    w.kb0 = off;
+    w.kb1 = piece_end - t_rel * nk;
+    w.zsplit = 0;
+    w.sk_first_peer = w.sk_peers = 0;
+    if (off > 0) {
+      w.sk_role = 2;
+    } else if (piece_end == tile_end) {
+      w.sk_role = 0;
+    } else {  // the tile continues in the ranges of the next unit(s)
+      w.sk_role = 1;
+      w.sk_first_peer = unit + 1;
+      int v = unit + 1;
+      while (v < units && sk_boundary(a, v) < tile_end) ++v;
+      w.sk_peers = v - (unit + 1);
+    }
+    cur = piece_end;
+    return true;
+  }
+};
 
 // Exercises the bounded wait by itself: one mbarrier that nothing ever signals, no copy or MMA in flight.  Thread 0
 // waits on it, gives up after `limit` cycles, records {role 7, block 0, index 42, parity 0} in g_watchdog like any
@@ -426,7 +530,6 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     probe_t0 = global_timer_ns();
   }
 
-  const int num_items = a.num_m_tiles * a.num_n_tiles * a.k_splits;  // (tile, K split) work items
   const int acc_cols = 2 * a.block_n;
 
   if (warp == 0 || warp == 3) {
@@ -441,10 +544,10 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int item = unit; item < num_items && ok; item += units) {
-        const int t = item / a.k_splits;
-        const int kb0 = (item - t * a.k_splits) * a.kb_per_split;
-        const int kb1 = min(a.num_k_blocks, kb0 + a.kb_per_split);
+      WorkIter work(a, unit, units);
+      WorkItem wk;
+      while (ok && work.next(wk)) {
+        const int t = wk.t, kb0 = wk.kb0, kb1 = wk.kb1;
         int mt, nt;
         tile_coords(a, t, mt, nt);
         const int row0 = (mt * kCtas + (int)cta_rank) * kBM;
@@ -529,9 +632,10 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int item = unit; item < num_items && ok; item += units, ++it) {
-        const int kb0 = (item % a.k_splits) * a.kb_per_split;  // split-K is never combined with CTA pairs
-        const int kb1 = min(a.num_k_blocks, kb0 + a.kb_per_split);
+      WorkIter work(a, unit, units);
+      WorkItem wk;
+      for (; ok && work.next(wk); ++it) {
+        const int kb0 = wk.kb0, kb1 = wk.kb1;
         const int buf = (a.acc_bufs == 2) ? (it & 1) : 0;
         const uint32_t acc_phase = (a.acc_bufs == 2) ? ((it >> 1) & 1) : (it & 1);
         MAGI_TRACE(0, it == 2);  // issuer starts waiting for the accumulator of tile 2
@@ -542,12 +646,12 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         }
         MAGI_TRACE(1, it == 2);  // accumulator free
         tc_fence_after_sync();
-        const uint32_t d_gate = tmem_base + (uint32_t)(buf * acc_cols * a.chains);
+        const uint32_t d_gate = tmem_base + (uint32_t)(buf * acc_cols);
         int kb = kb0;
         if (kCtas == 2 && a.split) {
           // The low half [gate_lo|up_lo] is free while the epilogue still drains the high half: run the
           // first MMA of as many K-steps as the ring holds, then wait for the high half and catch up.
-          const int ahead = min(a.stages, a.num_k_blocks);
+          const int ahead = min(a.stages, kb1 - kb0);
           int s2 = stage;
           uint32_t p2 = phase;
           for (int j = 0; j < ahead && ok; ++j) {
@@ -581,7 +685,7 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
               phase ^= 1u;
             }
           }
-          kb = ahead;
+          kb = kb0 + ahead;
         }
         // Split mode ends a tile the way it begins one, mirrored: the low-half MMAs of the last K-steps (as many as
         // the ring holds) go first and the low half is handed to the epilogue while the high-half MMAs of those
@@ -606,11 +710,9 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
             const uint32_t sb = sa + kABytes;
 #pragma unroll
             for (int k = 0; k < kBK / 16; ++k) {
-              // K=16 step k of every stage goes to accumulator set k % chains; a set's first MMA overwrites
-              const int set = k & (a.chains - 1);
-              const uint32_t acc = (kb != kb0 || k >= a.chains) ? 1u : 0u;
+              const uint32_t acc = ((kb - kb0) | k) != 0;
               const uint64_t ad = desc_a(sa, k);
-              umma_bf16<kCtas>(d_gate + (uint32_t)(set * acc_cols), ad, desc_b(sb, k), idesc, acc);
+              umma_bf16<kCtas>(d_gate, ad, desc_b(sb, k), idesc, acc);
               if (a.n_mma == 2) umma_bf16<kCtas>(d_gate + a.block_n, ad, desc_b(sb + a.b_second, k), idesc, acc);
             }
             MAGI_TRACE_ADD(10);  // issuer: cycles spent issuing MMAs
@@ -682,9 +784,10 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     const uint32_t stg_base = tiles_base + (uint32_t)a.stages * a.stage_bytes + (uint32_t)(warp - 4) * (2u * kStageOutBytes);
     uint32_t stg_par = 0;
     int it = 0;
-    for (int item = unit; item < num_items; item += units, ++it) {
-      const int t = item / a.k_splits;
-      const int zsplit = item - t * a.k_splits;
+    WorkIter work(a, unit, units);
+    WorkItem wk;
+    for (; work.next(wk); ++it) {
+      const int t = wk.t, zsplit = wk.zsplit;
       const int buf = (a.acc_bufs == 2) ? (it & 1) : 0;
       const uint32_t acc_phase = (a.acc_bufs == 2) ? ((it >> 1) & 1) : (it & 1);
       int mt, nt;
@@ -695,34 +798,33 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       if (!ok) break;
       MAGI_TRACE(5, it == 1 && warp == 4 && lane == 0);  // epilogue sees tile 1 complete
       tc_fence_after_sync();
-
+      if (wk.sk_role == 1) {
+        // Stream-K head piece: the tile's later pieces were the FIRST items of the next units' ranges and were parked
+        // long ago; every epilogue warp of the parking CTA raises the flag once.
+        bool peers_ok = true;
+        if (lane == 0) {
+          for (int pz = 0; pz < wk.sk_peers && peers_ok; ++pz)
+            peers_ok = wait_flag_bounded(a.sk_flags + (wk.sk_first_peer + pz) * kCtas + (int)cta_rank, kEpiWarps,
+                                         &abort_flag, 5u, (unsigned)(wk.sk_first_peer + pz), a.wait_limit);
+        }
+        peers_ok = __all_sync(0xffffffffu, peers_ok);
+        if (!peers_ok) break;
+      }
+      // Stream-K scratch of one CTA: [epilogue warp][chunk of the warp][16 float4 = 8 of gate, 8 of up][lane].  The
+      // parking warp and the owning warp walk the same chunks with the same lanes, so lane l's k-th float4 of a
+      // chunk sits next to lane l+1's: every store and load of a warp is one contiguous 512-byte piece.
+      const int sk_chunks = (kCtas == 2 && a.split ? 2 : 1) * ((a.block_n / (kCtas == 2 && a.split ? 2 : 1) + 63) / 64);
+      const size_t sk_cta_f4 = (size_t)kEpiWarps * sk_chunks * 16 * 32;
+      auto sk_slab = [&](int of_unit) {
+        return reinterpret_cast<uint4*>(a.sk_partials) + ((size_t)(of_unit * kCtas + (int)cta_rank)) * sk_cta_f4 +
+               (size_t)(warp - 4) * sk_chunks * 16 * 32 + lane;
+      };
+      int sk_ck = 0;  // chunks of this tile this warp has dealt with
       const int row = (mt * kCtas + (int)cta_rank) * kBM + q * 32 + lane;
       const bool row_ok = row < a.M;
       const int col0 = nt * a.block_n;
       const int valid_tile = min(a.block_n, a.N - col0);  // multiple of 8
-      const uint32_t t_tile = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * acc_cols * a.chains);
-      // Accumulator sets 1.. of a chained tile are added to the loaded chunk, 16 columns at a time, in set order.
-      auto add_chains = [&](uint32_t (&g)[32], uint32_t (&u)[32], uint32_t t_g, uint32_t t_u, int w) {
-        for (int set = 1; set < a.chains; ++set) {
-          for (int h = 0; h < w; h += 16) {
-            uint32_t tg[16], tu[16];
-            tmem_ld_x16(t_g + (uint32_t)(set * acc_cols + h), tg);
-            tmem_ld_x16(t_u + (uint32_t)(set * acc_cols + h), tu);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              asm volatile("" : "+r"(tg[i]), "+r"(tu[i]));  // uses of the loaded registers stay behind the wait
-              if (h == 0) {
-                g[i] = __float_as_uint(__uint_as_float(g[i]) + __uint_as_float(tg[i]));
-                u[i] = __float_as_uint(__uint_as_float(u[i]) + __uint_as_float(tu[i]));
-              } else {
-                g[16 + i] = __float_as_uint(__uint_as_float(g[16 + i]) + __uint_as_float(tg[i]));
-                u[16 + i] = __float_as_uint(__uint_as_float(u[16 + i]) + __uint_as_float(tu[i]));
-              }
-            }
-          }
-        }
-      };
+      const uint32_t t_tile = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * acc_cols);
       __nv_bfloat16* yrow_tile = a.y + (long long)row * a.ldy + col0;
       const bool wide = a.wide_store != 0;  // every 16-column group of every row starts on a 32-byte boundary
       const float row_scale_m = (a.row_scale != nullptr && row_ok) ? __ldg(a.row_scale + row) : 1.0f;
@@ -749,7 +851,6 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
           tmem_ld_wait();
           tmem_regs_ready(g);
           tmem_regs_ready(u);
-          if (a.chains > 1) add_chains(g, u, t_tile + c, t_tile + a.block_n + c, w);
           if (!chunk_w(c + 64)) {  // last read of the accumulator: hand it back before the stores
             tc_fence_before_sync();
             __syncwarp();
@@ -833,6 +934,17 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
           MAGI_TRACE_ADD_IF(27, warp == 4 && lane == 0);  // staging + TMA store issue of one box
         };
         auto process = [&](uint32_t (&g)[32], uint32_t (&u)[32], int c, int w) {
+          if (wk.sk_role == 2) {  // stream-K later piece: park the raw fp32 sums of this chunk (all 128 rows)
+            uint4* dst = sk_slab(unit) + (size_t)sk_ck * 16 * 32;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (4 * j < w) {
+                __stcg(dst + j * 32, make_uint4(g[4 * j], g[4 * j + 1], g[4 * j + 2], g[4 * j + 3]));
+                __stcg(dst + (8 + j) * 32, make_uint4(u[4 * j], u[4 * j + 1], u[4 * j + 2], u[4 * j + 3]));
+              }
+            }
+            return;
+          }
           if (a.row_scale != nullptr) {  // 1 for rows past M
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
@@ -938,7 +1050,26 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
             tmem_ld_wait();
             tmem_regs_ready(g);
             tmem_regs_ready(u);
-            if (a.chains > 1) add_chains(g, u, t_gate + c, t_up + c, w);
+            if (wk.sk_role == 1) {  // add the parked sums of the tile's later pieces, in unit order
+              for (int pz = 0; pz < wk.sk_peers; ++pz) {
+                const uint4* src = sk_slab(wk.sk_first_peer + pz) + (size_t)sk_ck * 16 * 32;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  if (4 * j < w) {
+                    const uint4 pg = __ldcg(src + j * 32);
+                    const uint4 pu = __ldcg(src + (8 + j) * 32);
+                    g[4 * j] = __float_as_uint(__uint_as_float(g[4 * j]) + __uint_as_float(pg.x));
+                    g[4 * j + 1] = __float_as_uint(__uint_as_float(g[4 * j + 1]) + __uint_as_float(pg.y));
+                    g[4 * j + 2] = __float_as_uint(__uint_as_float(g[4 * j + 2]) + __uint_as_float(pg.z));
+                    g[4 * j + 3] = __float_as_uint(__uint_as_float(g[4 * j + 3]) + __uint_as_float(pg.w));
+                    u[4 * j] = __float_as_uint(__uint_as_float(u[4 * j]) + __uint_as_float(pu.x));
+                    u[4 * j + 1] = __float_as_uint(__uint_as_float(u[4 * j + 1]) + __uint_as_float(pu.y));
+                    u[4 * j + 2] = __float_as_uint(__uint_as_float(u[4 * j + 2]) + __uint_as_float(pu.z));
+                    u[4 * j + 3] = __float_as_uint(__uint_as_float(u[4 * j + 3]) + __uint_as_float(pu.w));
+                  }
+                }
+              }
+            }
             MAGI_TRACE_ADD_IF(24, warp == 4 && lane == 0);  // epilogue warp 4: tensor-memory loads and their wait
           }
           const int c2 = c + 64, w2 = width_at(c2);
@@ -953,12 +1084,20 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
             process(g, u, c, w);
             MAGI_TRACE_ADD_IF(26, warp == 4 && lane == 0);  // arithmetic + stores of one chunk
           }
+          ++sk_ck;
           c = c2;
           w = w2;
         }
         if (!released) release();
       }
       if (!seg_ok) break;
+      if (wk.sk_role == 2) {  // this warp's share of the parked sums is written: publish it
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence();
+          atomicAdd(a.sk_flags + unit * kCtas + (int)cta_rank, 1);
+        }
+      }
     }
     if (a.y_tma && lane == 0) bulk_wait_group_read<0>();  // shared memory stays valid until the last store has read it
   }

@@ -34,13 +34,13 @@ static int fail_cuda(cudaError_t e, const char* what) {
 //   MAGI_SWIGLU_K_SPLITS=z    force z-way split-K in the STREAM schedule
 //   MAGI_SWIGLU_NO_SPLIT=1    drain pair tiles in one piece instead of two separately released halves
 //   MAGI_SWIGLU_Y_TMA=0|1     force Y through direct stores (0) or shared memory + TMA stores (1) in the tile schedules
-//   MAGI_SWIGLU_CHAINS=c      at most c (1, 2, 4) accumulator sets per slab in the STREAM schedule
+//   MAGI_SWIGLU_STREAM_K=0|1  never / whenever possible: balance the last waves of the tile schedules by K ranges
 struct Tuning {
   int hints[3] = {-1, -1, -1};
   int k_splits = 0;
   int no_split = 0;
   int y_tma = -1;
-  int chains = 0;  // 0 = choose; 1, 2, 4 = at most that many accumulator sets in the STREAM schedule
+  int stream_k = -1;  // -1 choose, 0 never, 1 whenever it is possible
 };
 static Tuning& tuning() {
   static Tuning t = [] {
@@ -52,7 +52,7 @@ static Tuning& tuning() {
     if (const char* env = getenv("MAGI_SWIGLU_K_SPLITS")) v.k_splits = atoi(env);
     if (getenv("MAGI_SWIGLU_NO_SPLIT")) v.no_split = 1;
     if (const char* env = getenv("MAGI_SWIGLU_Y_TMA")) v.y_tma = atoi(env) != 0;
-    if (const char* env = getenv("MAGI_SWIGLU_CHAINS")) v.chains = atoi(env);
+    if (const char* env = getenv("MAGI_SWIGLU_STREAM_K")) v.stream_k = atoi(env) != 0;
     return v;
   }();
   return t;
@@ -60,7 +60,6 @@ static Tuning& tuning() {
 
 struct Plan {
   int variant, block_n, stages, grid, tiles, smem_bytes, acc_bufs, n_mma;
-  int chains;  // accumulator sets per buffer (STREAM schedule, narrow slabs): 1, 2 or 4
   int num_m_tiles, num_n_tiles, num_k_blocks, group_m;
   int ctas;  // CTAs per tile: 1, or 2 for the CTA-pair schedule
   int split; // CTA pairs with two MMAs per step and block_n % 32 == 0: two separately released half tiles
@@ -68,6 +67,9 @@ struct Plan {
   int64_t ws_bytes;                    // fp32 partial sums of a split-K plan (0 = none)
   uint32_t stage_bytes, b_second;
   int y_tma;  // tile schedules: Y leaves through per-warp staging boxes in shared memory and TMA stores
+  // stream-K (tile schedules with scratch): tiles from sk_first_tile on are cut into equal K ranges, one per worker
+  int sk_first_tile, sk_iters_per_unit, sk_total_iters, sk_min_kb;
+  int64_t sk_flag_bytes;
 };
 
 static inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
@@ -89,15 +91,67 @@ static inline double stream_cost_ns(int64_t N, int64_t num_kb, int bn, int z, in
   return (double)waves * ((double)kpz * (step_ns > 533.0 ? step_ns : 533.0) + 1500.0 + 6.0 * bn + (z > 1 ? 2500.0 : 0.0));
 }
 
-// Cheapest tile width for a persistent grid of `units` workers on tiles of `rows` x bn: whole waves of tiles, one
-// tile of width bn costing (bn + 146) x `unit_cost` (fixed part: epilogue, pipeline refill, lower operand reuse of
-// narrow tiles; measured on B200).  Widths are multiples of 32 from bn_max down to 128.
-static double tile_wave_cost(int64_t M, int64_t N, int rows, int64_t units, int bn_max, double unit_cost, int* bn_out) {
+constexpr int kSkMinKb = 8;  // shortest piece of a split tile in K-steps: a shorter one costs more to hand over than it balances
+
+// Scratch of a stream-K plan for `units` workers of `ctas` CTAs each: one flag and one slab of fp32 partial sums per CTA.
+static inline int64_t sk_flag_bytes(int units, int ctas) { return ((int64_t)units * ctas * 4 + 255) / 256 * 256; }
+static inline int64_t sk_bytes(int units, int ctas, int bn) {
+  // per CTA: 8 epilogue warps x chunks per warp x (16 float4 x 32 lanes); a warp takes every other 32-column chunk
+  // of a tile half (pairs with two separately released halves) or of the whole tile
+  const bool halves = ctas == 2 && 2 * bn > 256 && bn % 32 == 0;
+  const int chunks = (halves ? 2 : 1) * ((bn / (halves ? 2 : 1) + 63) / 64);
+  return sk_flag_bytes(units, ctas) + (int64_t)units * ctas * kEpiWarps * chunks * 16 * 32 * 16;
+}
+
+// Whether `tiles` tiles of num_kb K-steps on `units` workers should end in a stream-K phase (scratch permitting).
+// In that phase neighbouring workers sit at K offsets one remainder-fraction of a tile apart, so tiles that share an
+// operand panel stop reading it at the same time once the fraction grows: measured on B200 the phase pays up to a
+// quarter of a wave of remainder (a last wave at most a quarter full) and costs more than it saves beyond that.
+static inline bool sk_wanted(int64_t tiles, int num_kb, int units, int ctas, int bn, int64_t ws_limit) {
+  if (tuning().stream_k == 0 || units < 2 || tiles < 1) return false;
+  const int64_t waves = tiles / units, rem = tiles - waves * units;
+  if (rem == 0) return false;
+  if (tuning().stream_k != 1 && rem * 4 > (int64_t)units) return false;
+  const int64_t sk_tiles = waves >= 1 ? units + rem : tiles;
+  const int64_t total = sk_tiles * num_kb, q = (total + units - 1) / units;
+  if (q < 2 * kSkMinKb || 4 * q < num_kb || total > 0x3fffffffLL) return false;  // pieces too short / too many per tile
+  return sk_bytes(units, ctas, bn) <= ws_limit;
+}
+
+// Fills the plan's stream-K fields for `units` workers; returns the scratch bytes (0 = plain whole-tile schedule).
+static int64_t sk_setup(Plan* p, int units, int64_t ws_limit) {
+  p->sk_first_tile = p->tiles;
+  p->sk_iters_per_unit = p->sk_total_iters = 0;
+  p->sk_min_kb = kSkMinKb;
+  p->sk_flag_bytes = 0;
+  if (p->variant != MAGI_SWIGLU_VARIANT_MMA && p->variant != MAGI_SWIGLU_VARIANT_MMA2) return 0;
+  if (p->k_splits != 1 || !sk_wanted(p->tiles, p->num_k_blocks, units, p->ctas, p->block_n, ws_limit)) return 0;
+  const int waves = p->tiles / units, rem = p->tiles - waves * units;
+  const int sk_tiles = waves >= 1 ? units + rem : p->tiles;
+  p->sk_first_tile = p->tiles - sk_tiles;
+  p->sk_total_iters = sk_tiles * p->num_k_blocks;
+  p->sk_iters_per_unit = (p->sk_total_iters + units - 1) / units;
+  p->sk_flag_bytes = sk_flag_bytes(units, p->ctas);
+  return sk_bytes(units, p->ctas, p->block_n);
+}
+
+// Cheapest tile width for a persistent grid of `units` workers on tiles of `rows` x bn.  One tile of width bn costs
+// (bn + 146) x `unit_cost` (fixed part: epilogue, pipeline refill, lower operand reuse of narrow tiles; measured on
+// B200).  Without scratch the grid runs whole waves of tiles; with enough of it (ws_limit) and a last wave that
+// would be mostly empty, the last waves are balanced by K ranges and only the total work counts, plus a hand-over.
+// Widths are multiples of 32 down to 128.
+static double tile_wave_cost(int64_t M, int64_t N, int64_t K, int rows, int64_t units, int bn_max, double unit_cost,
+                             int64_t ws_limit, int* bn_out) {
   double best = -1.0;
   if (units < 1) units = 1;
+  const int num_kb = (int)((K + kBK - 1) / kBK);
   for (int bn = bn_max; bn >= 128; bn -= 32) {
     const int64_t tiles = ((M + rows - 1) / rows) * ((N + bn - 1) / bn);
-    const double cost = (double)((tiles + units - 1) / units) * (bn + 146) * unit_cost;
+    double cost;
+    if (sk_wanted(tiles, num_kb, (int)units, rows / kBM, bn, ws_limit))  // only the total work counts, plus a hand-over
+      cost = ((double)tiles / (double)units * (bn + 146) + 60.0) * unit_cost;
+    else
+      cost = (double)((tiles + units - 1) / units) * (bn + 146) * unit_cost;
     if (best < 0 || cost < best) {
       best = cost;
       *bn_out = bn;
@@ -122,8 +176,8 @@ static int make_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
     if (M > kBM && N >= 128 && block_n == 0 && sm_count >= 2 && (max_ctas <= 0 || max_ctas >= 2)) {
       const int avail = (max_ctas > 0 && max_ctas < sm_count) ? max_ctas : sm_count;
       int bn_pair = 0, bn_single = 0;
-      const double cost_pair = tile_wave_cost(M, N, 2 * kBM, avail / 2, 256, 1.0, &bn_pair);
-      const double cost_single = tile_wave_cost(M, N, kBM, avail, 224, 1.12, &bn_single);
+      const double cost_pair = tile_wave_cost(M, N, K, 2 * kBM, avail / 2, 256, 1.0, ws_limit, &bn_pair);
+      const double cost_single = tile_wave_cost(M, N, K, kBM, avail, 224, 1.12, ws_limit, &bn_single);
       if (cost_single < 0.95 * cost_pair) {  // 5 %: the pair schedule is the better-measured default
         variant = MAGI_SWIGLU_VARIANT_MMA;
         block_n = bn_single;
@@ -160,7 +214,7 @@ static int make_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
         block_n = round_up((int)N, 16);
       } else {
         // multiples of 32: both half tiles stay multiples of 16
-        tile_wave_cost(M, N, 2 * kBM, ctas / 2, 256, 1.0, &block_n);
+        tile_wave_cost(M, N, K, 2 * kBM, ctas / 2, 256, 1.0, ws_limit, &block_n);
       }
     } else if (variant == MAGI_SWIGLU_VARIANT_MMA) {
       block_n = (N >= 128) ? 128 : round_up((int)N, 16);
@@ -201,18 +255,6 @@ static int make_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
   p->block_n = block_n;
   p->n_mma = (2 * block_n <= 256) ? 1 : 2;
   p->acc_bufs = (4 * block_n <= kTmemCols) ? 2 : 1;
-  p->chains = 1;
-  if (variant == MAGI_SWIGLU_VARIANT_STREAM && tuning().chains != 1) {
-    // A narrow slab leaves most of tensor memory empty: spread the K=16 steps of a stage over 2 or 4 accumulator sets
-    // so that no MMA waits for the one before it.  One buffer then (a slab per CTA is the rule in this schedule).
-    const int fit_sets = kTmemCols / (2 * block_n);
-    int c = fit_sets >= 4 ? 4 : (fit_sets >= 2 ? 2 : 1);
-    if (tuning().chains > 0 && tuning().chains < c) c = tuning().chains;
-    if (c > 1) {
-      p->chains = c;
-      p->acc_bufs = 1;
-    }
-  }
   // weight rows per CTA and stage: gate + up rows of the tile, split between the CTAs of a pair
   p->stage_bytes = kABytes + 2u * (uint32_t)block_n * 128u / (uint32_t)pair;
   p->b_second = (uint32_t)block_n * 128u / (uint32_t)pair;
@@ -253,6 +295,8 @@ static int make_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
   if (k_splits > 1) p->ws_bytes = splitk_bytes(p->tiles, k_splits, M, block_n);
   const int64_t items = (int64_t)p->tiles * pair * k_splits;
   p->grid = (items < ctas) ? (int)items : ctas;
+  if (k_splits == 1) p->ws_bytes = sk_setup(p, p->grid / pair, ws_limit);
+  else sk_setup(p, 0, 0);
   return 0;
 }
 }  // namespace magi

@@ -254,7 +254,6 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   a.b_second = p.b_second;
   a.split = p.split;
   a.acc_bufs = p.acc_bufs;
-  a.chains = p.chains;
   a.wide_store = (((uintptr_t)y & 31u) == 0 && ldy % 16 == 0 && (!plain || N % 16 == 0)) ? 1 : 0;
   a.plain = plain;
   a.a_mn = a_mn;
@@ -276,6 +275,19 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   a.ws = p.k_splits > 1 ? static_cast<float*>(workspace) : nullptr;
   a.y_tma = y_tma;
   a.wait_limit = kWaitLimitCycles;
+  auto fill_stream_k = [&]() {
+    a.sk_first_tile = p.sk_first_tile;
+    a.sk_iters_per_unit = p.sk_iters_per_unit;
+    a.sk_total_iters = p.sk_total_iters;
+    a.sk_min_kb = p.sk_min_kb;
+    a.sk_flags = p.sk_total_iters > 0 ? static_cast<int*>(workspace) : nullptr;
+    a.sk_partials = p.sk_total_iters > 0 ? reinterpret_cast<float*>(static_cast<char*>(workspace) + p.sk_flag_bytes) : nullptr;
+  };
+  fill_stream_k();
+  // the hand-over flags of a stream-K launch start at zero (a memset node: nothing is allocated, nothing synchronises)
+  auto clear_flags = [&]() -> cudaError_t {
+    return p.sk_total_iters > 0 ? cudaMemsetAsync(workspace, 0, (size_t)p.sk_flag_bytes, stream) : cudaSuccess;
+  };
   // Default L2 priorities (ncu, DRAM bytes per launch).  X: a band of X rows is re-read by every column tile ->
   // keep.  Y: written once -> evict first.  W: in the tile schedules a W tile is shared by all row units of the band
   // that run at the same time, and marking it evict-first makes late CTAs miss it (+25..70 % DRAM reads) -> normal;
@@ -289,6 +301,8 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   if (tune.hints[2] >= 0) a.y_hint = tune.hints[2];
 
   if (p.ctas == 1) {
+    e = clear_flags();
+    if (e != cudaSuccess) return fail_cuda(e, "cudaMemsetAsync(stream-K flags)");
     swiglu_tc_kernel<1><<<p.grid, kThreads, p.smem_bytes, stream>>>(tm_x, tm_w, tm_y, a);
     e = cudaGetLastError();
     if (e != cudaSuccess) return fail_cuda(e, "launch of swiglu_tc_kernel<1>");
@@ -313,7 +327,13 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   }
   if (pair_clusters <= 0) return fail(MAGI_SWIGLU_ERR_VARIANT, "this device cannot co-schedule 2-CTA clusters of the pair kernel");
   int grid = p.grid;
-  if (grid > 2 * pair_clusters) grid = 2 * pair_clusters;  // persistent: never more pairs than fit at once
+  if (grid > 2 * pair_clusters) {  // persistent: never more pairs than fit at once
+    grid = 2 * pair_clusters;
+    sk_setup(&p, grid / 2, workspace ? workspace_bytes : 0);  // the K ranges are cut for the workers that really run
+    fill_stream_k();
+  }
+  e = clear_flags();
+  if (e != cudaSuccess) return fail_cuda(e, "cudaMemsetAsync(stream-K flags)");
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -624,7 +644,7 @@ int magi_swiglu_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
   out[10] = p.split;
   out[11] = p.k_splits;
   out[12] = p.y_tma;
-  out[13] = p.chains;
+  out[13] = p.tiles - p.sk_first_tile;
   out[14] = out[15] = 0;
   return 0;
 }
@@ -650,6 +670,39 @@ int magi_swiglu_device_status(int device, int32_t out[4]) {
   return 0;
 }
 
+int magi_swiglu_schedule(int64_t M, int64_t N, int64_t K, int variant, int block_n, int stages, int group_m, int max_ctas,
+                         int sm_count, int64_t workspace_bytes, int unit, int32_t* out, int max_items) {
+  magi::g_err[0] = 0;
+  if (!out || max_items < 0) return magi::fail(MAGI_SWIGLU_ERR_NULL, "out is null");
+  if (sm_count <= 0) return magi::fail(MAGI_SWIGLU_ERR_DEVICE, "sm_count must be positive");
+  magi::Plan p;
+  int rc = magi::make_plan(M, N, K, variant, block_n, stages, group_m, max_ctas, sm_count, workspace_bytes, &p);
+  if (rc) return rc;
+  if (p.variant == MAGI_SWIGLU_VARIANT_SIMT) return 0;
+  magi::KArgs a;
+  memset(&a, 0, sizeof(a));
+  a.num_k_blocks = p.num_k_blocks;
+  a.k_splits = p.k_splits;
+  a.kb_per_split = p.kb_per_split;
+  a.sk_first_tile = p.sk_first_tile;
+  a.sk_iters_per_unit = p.sk_iters_per_unit;
+  a.sk_total_iters = p.sk_total_iters;
+  a.sk_min_kb = p.sk_min_kb;
+  const int units = p.grid / p.ctas;
+  if (unit < 0 || unit >= units) return 0;
+  magi::WorkIter it(a, unit, units);
+  magi::WorkItem w;
+  int n = 0;
+  while (it.next(w)) {
+    if (n < max_items) {
+      int32_t* o = out + 6 * n;
+      o[0] = w.t, o[1] = w.kb0, o[2] = w.kb1, o[3] = w.sk_role, o[4] = w.sk_first_peer, o[5] = w.sk_peers;
+    }
+    ++n;
+  }
+  return n;
+}
+
 int magi_swiglu_tuning(int knob, int value) {
   magi::g_err[0] = 0;
   magi::Tuning& t = magi::tuning();
@@ -667,9 +720,9 @@ int magi_swiglu_tuning(int knob, int value) {
       prev = t.y_tma;
       t.y_tma = value < 0 ? -1 : (value != 0);
       return prev;
-    case MAGI_SWIGLU_TUNE_CHAINS:
-      prev = t.chains;
-      t.chains = (value == 1 || value == 2 || value == 4) ? value : 0;
+    case MAGI_SWIGLU_TUNE_STREAM_K:
+      prev = t.stream_k;
+      t.stream_k = value < 0 ? -1 : (value != 0);
       return prev;
     case MAGI_SWIGLU_TUNE_L2_HINTS: {
       prev = t.hints[0] < 0 ? -1 : t.hints[0] * 100 + t.hints[1] * 10 + t.hints[2];

@@ -114,16 +114,16 @@ def gemm_swiglu_out(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor 
     dev = x.device.index if x.device.index is not None else torch.cuda.current_device()
     stream = _raw_stream(dev)
     ldx = x2.stride(0) if M > 1 else K
+    # scratch: the small-M schedules split K through it, the tile schedules balance their last waves through it
     ws_ptr, ws_len = None, 0
-    if M <= 128:  # only the small-M schedules ever split K
-        key = (M, N, K, v, block_n, stages, group_m, max_ctas, dev, _split_env())
-        need = _ws_need.get(key)
-        if need is None:
-            need = lib.magi_swiglu_workspace_bytes(M, N, K, v, block_n, stages, group_m, max_ctas, dev, 0)
-            _ws_need[key] = need
-        if need > 0:
-            ws = _workspace(x.device, need)
-            ws_ptr, ws_len = ws.data_ptr(), ws.numel()
+    key = (M, N, K, v, block_n, stages, group_m, max_ctas, dev, _split_env())
+    need = _ws_need.get(key)
+    if need is None:
+        need = lib.magi_swiglu_workspace_bytes(M, N, K, v, block_n, stages, group_m, max_ctas, dev, 0)
+        _ws_need[key] = need
+    if need > 0:
+        ws = _workspace(x.device, need)
+        ws_ptr, ws_len = ws.data_ptr(), ws.numel()
     rc = lib.magi_swiglu_forward_bf16_ws(x2.data_ptr(), w2.data_ptr(), y.data_ptr(), M, N, K, ldx, w2.stride(0),
                                          y.stride(0), dev, stream, v, block_n, stages, group_m, max_ctas,
                                          ws_ptr, ws_len)

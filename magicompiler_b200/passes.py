@@ -259,7 +259,10 @@ class FuseSwiGLUPass(_PassBase):
                 wg, wu = gate.args[1], up.args[1]
                 if not (isinstance(wg, torch.fx.Node) and isinstance(wu, torch.fx.Node)):
                     continue
-                if not _is_bf16_on(self.allowed_devices, gate.args[0], wg, wu):
+                # the activations decide where the op runs; weights may be traced on the host when an offload executor
+                # brings them to the GPU call by call (magi_compiler/offload/offload_warpper.py:100-131)
+                if not _is_bf16_on(self.allowed_devices, gate.args[0]) or \
+                        not _is_bf16_on(self.allowed_devices + ("cpu",), wg, wu):
                     continue
                 evg, evu = _example(wg), _example(wu)
                 if isinstance(evg, torch.Tensor) and isinstance(evu, torch.Tensor):
@@ -296,7 +299,8 @@ class FuseSwiGLUPass(_PassBase):
                 inner = set(helpers) | {gate, up}
                 if any(u not in inner for u in lin.users) or any(u not in (gate, up) for hn in helpers for u in hn.users):
                     continue  # the merged projection (or a piece of it) is used elsewhere: it must stay
-                if not _is_bf16_on(self.allowed_devices, lin.args[0], lin.args[1]):
+                if not _is_bf16_on(self.allowed_devices, lin.args[0]) or \
+                        not _is_bf16_on(self.allowed_devices + ("cpu",), lin.args[1]):
                     continue
                 evw = _example(lin.args[1])
                 if isinstance(evw, torch.Tensor) and (evw.dim() != 2 or evw.shape[0] % 16 or evw.shape[1] % 8):

@@ -143,7 +143,10 @@ _GRAPHS = _PRELUDE + textwrap.dedent('''
     print("RESULT " + json.dumps(res))
 ''')
 
-_OFFLOAD = _PRELUDE + textwrap.dedent('''
+# Under the offload executor the module is traced with its tensors on the host (the executor brings them to the GPU
+# call by call), so the pass is told that host-traced graphs are fine here; a tensor that really reaches the op on the
+# host still raises (the op has no CPU path).
+_OFFLOAD = _PRELUDE.replace('allowed_devices=("cuda", "meta") if on_gpu', 'allowed_devices=("cuda", "meta", "cpu") if on_gpu') + textwrap.dedent('''
     from tests.model_definition import TransformerConfig, TransformerMLP
     cfg = TransformerConfig(vocab_size=128, hidden_size=256, intermediate_size=512, num_hidden_layers=1,
                             num_attention_heads=4, num_key_value_heads=4, max_position_embeddings=128)
@@ -152,24 +155,50 @@ _OFFLOAD = _PRELUDE + textwrap.dedent('''
     conf = get_compile_config()
     conf.offload_config.model_cpu_offload = True        # the decorator reads the global config when it wraps the class
     conf.offload_config.gpu_resident_weight_ratio = 0.0  # nothing stays resident: every call brings the weights in anew
-    OffloadMLP = magi_compile(dynamic_arg_dims={"x": 0}, config_patch=patch_backend)(type("OffloadMLP", (TransformerMLP,), {}))
-    model = OffloadMLP(cfg)
-    model.load_state_dict(eager.state_dict())
-    model.cuda() if on_gpu else None
-    res["weights_stay_on_host"] = model.gate_proj.weight.device.type == "cpu"
-    ok, before = [], calls["n"]
-    calls["weights"].clear()
+
+    class MergedMLP(torch.nn.Module):                   # the op called directly on a merged gate/up weight
+        def __init__(self, cfg):
+            super().__init__()
+            self.w_gate_up = torch.nn.Parameter(torch.empty(2 * cfg.intermediate_size, cfg.hidden_size, dtype=torch.bfloat16))
+            self.down_proj = torch.nn.Linear(cfg.intermediate_size, cfg.hidden_size, bias=False, dtype=torch.bfloat16)
+        def forward(self, x):
+            return self.down_proj(mb.gemm_swiglu(x * 1.0, self.w_gate_up))
+
+    def run(model, packed_now):
+        model.cuda() if on_gpu else None
+        out = {"weights_stay_on_host": next(model.parameters()).device.type == "cpu"}
+        ok, before = [], calls["n"]
+        calls["weights"].clear()
+        with torch.no_grad():
+            for rows, seed in ((192, 1), (192, 2), (64, 3), (192, 4)):
+                x = torch.randn(rows, 256, device=dev, generator=torch.Generator(device=dev).manual_seed(seed)).to(torch.bfloat16)
+                ok.append(close(model(x), eager(x)))
+        # what the kernel was handed on every call is the CURRENT host weight, packed (never a stale copy), even though
+        # the executor brings the weights to the GPU as new tensors call after call
+        current = packed_now().to(dev)
+        out["weight_fed_is_current"] = [bool(torch.equal(w.to(dev), current)) for w in calls["weights"]]
+        out["close"] = ok
+        out["calls"] = calls["n"] - before
+        return out
+
+    Merged = magi_compile(dynamic_arg_dims={"x": 0}, config_patch=patch_backend)(MergedMLP)
+    merged = Merged(cfg)
     with torch.no_grad():
-        for rows, seed in ((192, 1), (192, 2), (64, 3), (192, 4)):
-            x = torch.randn(rows, 256, device=dev, generator=torch.Generator(device=dev).manual_seed(seed)).to(torch.bfloat16)
-            ok.append(close(model(x), eager(x)))
-    # what the kernel was handed on every call is the CURRENT host weights, packed (never a stale packed copy), even
-    # though the executor brings the two weights to the GPU as new tensors call after call
-    current = torch.cat([model.gate_proj.weight, model.up_proj.weight]).to(dev)
-    res["weight_fed_is_current"] = [bool(torch.equal(w.to(dev), current)) for w in calls["weights"]]
-    res["distinct_weight_tensors"] = len({id(w) for w in calls["weights"]})
-    res["close"] = ok
-    res["calls"] = calls["n"] - before
+        merged.w_gate_up.copy_(torch.cat([eager.gate_proj.weight, eager.up_proj.weight]).cpu())
+        merged.down_proj.weight.copy_(eager.down_proj.weight.cpu())
+    try:
+        res["merged"] = run(merged, lambda: merged.w_gate_up.detach())
+    except Exception as exc:
+        res["merged"] = {"error": repr(exc)[:600]}
+    # the UNMODIFIED reference module under the same executor: its weights are traced on the host and the rewrite
+    # pass still turns its SwiGLU into the op (the two weights are packed on every call: they are new tensors each time)
+    OffloadMLP = magi_compile(dynamic_arg_dims={"x": 0}, config_patch=patch_backend)(type("OffloadMLP", (TransformerMLP,), {}))
+    plain = OffloadMLP(cfg)
+    plain.load_state_dict(eager.state_dict())
+    try:
+        res["rewritten"] = run(plain, lambda: torch.cat([plain.gate_proj.weight, plain.up_proj.weight]).detach())
+    except Exception as exc:
+        res["rewritten"] = {"error": repr(exc)[:600]}
     print("RESULT " + json.dumps(res))
 ''')
 
@@ -213,8 +242,11 @@ def test_cuda_graph_manager_piecewise_and_full(tmp_path):
 def test_offload_executor_brings_new_weight_pointers_every_call(tmp_path):
     res = _run_child(tmp_path, _OFFLOAD)
     assert res["through_ref"] and res["on_gpu"], res
-    assert res["weights_stay_on_host"] and all(res["close"]) and res["calls"] == 4, res
-    assert res["weight_fed_is_current"] == [True] * 4, res
+    for form in ("merged", "rewritten"):
+        got = res[form]
+        assert "error" not in got, (form, got)
+        assert got["weights_stay_on_host"] and all(got["close"]) and got["calls"] == 4, (form, got)
+        assert got["weight_fed_is_current"] == [True] * 4, (form, got)
 
 
 @needs_reference

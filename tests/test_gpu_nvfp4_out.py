@@ -94,3 +94,45 @@ def test_nvfp4_full_size_runs_in_every_tile_and_matches_the_bf16_path():
     # every block's largest magnitude maps to a code of at least 4 (|q| in (3.5, 6]) unless the block is all zero
     blk = (val.abs().reshape(M, N // 16, 16).amax(dim=-1))
     assert ((blk >= 4.0) | (sf.float() == 0)).float().mean().item() >= 0.999
+
+
+def test_nvfp4_output_against_vllm_silu_and_mul_nvfp4_quant():
+    """The op the reference's pass names (fix_functionalization.py:113-120), run for real when vLLM's compiled ops are
+    present: vLLM quantises the bf16-rounded projections and rounds the activation to bf16 before scaling, the fused
+    kernel quantises its fp32 accumulators directly, so most scale bytes and codes are identical and the rest are
+    neighbours.  Scales are compared in vLLM's own layout (128 x 4 tiles, int32-packed)."""
+    try:
+        import vllm._C  # noqa: F401
+    except Exception as exc:  # not installed, or built without this device
+        pytest.skip(f"vLLM compiled ops unavailable: {exc}")
+    if not hasattr(torch.ops._C, "silu_and_mul_nvfp4_quant"):
+        pytest.skip("this vLLM build has no silu_and_mul_nvfp4_quant")
+    for M, K, N in ((256, 512, 384), (1000, 1024, 2816), (128, 256, 64)):
+        x, w = make_inputs(M, K, N, seed=N + 1)
+        x, w = x.cuda(), w.cuda()
+        h = mb.gemm_nt(x, w)  # [M, 2N] bf16 = the merged gate/up linear's output
+        gs = torch.tensor([448.0 * 6.0 / mb.gemm_swiglu(x, w).float().abs().max().item()], dtype=torch.float32,
+                          device="cuda")
+        rows_pad, blocks_pad = -(-M // 128) * 128, -(-(N // 16) // 4) * 4
+        ref_codes = torch.empty(M, N // 2, dtype=torch.uint8, device="cuda")
+        ref_sf = torch.zeros(rows_pad, blocks_pad // 4, dtype=torch.int32, device="cuda")
+        torch.ops._C.silu_and_mul_nvfp4_quant(ref_codes, ref_sf, h, gs)
+        codes, sf = mb.gemm_swiglu_nvfp4(x, w, gs, True)
+        torch.cuda.synchronize()
+        off = nvfp4_swizzled_offsets(M, N)  # where the scale of (row, block) sits in the tiled layout
+        ours = sf.cpu().view(torch.uint8)[off]
+        theirs = ref_sf.cpu().view(torch.uint8).reshape(-1)[off]
+        same_sf = ours == theirs
+        assert same_sf.float().mean().item() >= 0.97, same_sf.float().mean().item()
+        assert ((ours.int() - theirs.int()).abs() <= 1).all()  # a differing scale is the neighbouring e4m3 value
+        got, ref = _unpack(codes), _unpack(ref_codes)
+        in_same_block = same_sf.repeat_interleave(16, dim=1)
+        agree = _same_code(got, ref)[in_same_block]
+        assert agree.float().mean().item() >= 0.93, agree.float().mean().item()
+        # codes that differ are neighbours on the e2m1 grid
+        lut = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+        va = torch.where((got & 8) != 0, -lut[(got & 7).long()], lut[(got & 7).long()])
+        vb = torch.where((ref & 8) != 0, -lut[(ref & 7).long()], lut[(ref & 7).long()])
+        idx_a = torch.bucketize(va, torch.tensor([-6.0, -4.0, -3.0, -2.0, -1.5, -1.0, -0.5, 0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0]))
+        idx_b = torch.bucketize(vb, torch.tensor([-6.0, -4.0, -3.0, -2.0, -1.5, -1.0, -0.5, 0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0]))
+        assert ((idx_a - idx_b).abs()[in_same_block] <= 1).all()

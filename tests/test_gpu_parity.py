@@ -2,6 +2,7 @@
 Every case goes through the C-ABI library (directly with ctypes, or through the registered op, which is one
 ctypes call).  Tolerance of the path (bf16 output, fp32 accumulation), against the fp32-accumulated gold:
     max|y-gold|/max|gold| <= 1e-2,  ||y-gold||_F/||gold||_F <= 5e-3,  allclose(rtol=1e-2, atol=1e-2*max|gold|)."""
+import contextlib
 import ctypes
 
 import numpy as np
@@ -23,6 +24,18 @@ def _require_b200():
     yield
     st = mb.device_status(0)
     assert st["code"] == 0, f"a kernel wait timed out during the tests: {st}"
+
+
+@contextlib.contextmanager
+def whole_tile_schedules():
+    """Stream-K off: every output is accumulated over K in one piece, whatever the schedule, so results can be
+    compared bit for bit across schedules, tile widths and column shards.  (With stream-K on, the tiles whose K range
+    is shared between two workers add two fp32 partial sums instead: same tolerance, not the same bits.)"""
+    prev = _loader.set_tuning("stream_k", 0)
+    try:
+        yield
+    finally:
+        _loader.set_tuning("stream_k", prev)
 
 
 def assert_parity(y, gold, what=""):
@@ -177,8 +190,9 @@ def test_decode_shapes_full_size(M):
     xd, wd = x.cuda(), w.cuda()
     y = mb.gemm_swiglu(xd, wd)
     assert_parity(y, gold_fp32_gpu(xd, wd), f"decode M={M}")
-    assert torch.equal(y, mb.gemm_swiglu_out(xd, wd, variant="mma")), "both schedules accumulate in the same order"
-    assert torch.equal(y, mb.gemm_swiglu_out(xd, wd, variant="mma2"))
+    with whole_tile_schedules():
+        assert torch.equal(y, mb.gemm_swiglu_out(xd, wd, variant="mma")), "both schedules accumulate in the same order"
+        assert torch.equal(y, mb.gemm_swiglu_out(xd, wd, variant="mma2"))
 
 
 def test_llama_ffn_full_size_properties():
@@ -186,21 +200,41 @@ def test_llama_ffn_full_size_properties():
     M, K, N = 8192, 4096, 14336
     x, w = make_inputs(M, K, N, seed=0)
     xd, wd = x.cuda(), w.cuda()
-    y = mb.gemm_swiglu(xd, wd)
     rows = torch.randperm(M, generator=torch.Generator().manual_seed(1))[:384].cuda()
-    assert_parity(y[rows], gold_fp32_gpu(xd[rows], wd), "llama ffn sample")
-    for variant in ("mma", "mma2"):  # one CTA per tile and CTA pairs: same K order per output, same bits
-        assert torch.equal(mb.gemm_swiglu_out(xd, wd, variant=variant), y), variant
-    # (1) doubling the up weights doubles every output exactly (power-of-two scaling commutes with rounding)
+    gold = gold_fp32_gpu(xd[rows], wd)
+    y_auto = mb.gemm_swiglu(xd, wd)  # the schedule a caller gets (stream-K balances its last waves)
+    assert_parity(y_auto[rows], gold, "llama ffn sample")
+    with whole_tile_schedules():
+        y = mb.gemm_swiglu(xd, wd)
+        assert_parity(y[rows], gold, "llama ffn sample, whole tiles")
+        for variant in ("mma", "mma2"):  # one CTA per tile and CTA pairs: same K order per output, same bits
+            assert torch.equal(mb.gemm_swiglu_out(xd, wd, variant=variant), y), variant
+        # (1) doubling the up weights doubles every output exactly (power-of-two scaling commutes with rounding)
+        w2 = wd.clone()
+        w2[N:] *= 2
+        assert torch.equal(mb.gemm_swiglu(xd, w2), y * 2)
+        # (2) permuting the rows of X permutes the rows of Y bit for bit (no dependence on tile position)
+        perm = torch.randperm(M, generator=torch.Generator().manual_seed(2)).cuda()
+        assert torch.equal(mb.gemm_swiglu(xd[perm].contiguous(), wd), y[perm])
+        # (3) column shards are independent units: 8 shards side by side are the unsharded result bit for bit
+        parts = [mb.gemm_swiglu(xd, mb.shard_gate_up(wd, r, 8)) for r in range(8)]
+        assert torch.equal(torch.cat(parts, dim=1), y)
+    # the balanced schedule differs from the whole-tile one only where a tile's K range was shared, and there by a
+    # rounding of the fp32 sum: at most one bf16 step
+    assert_close_to_whole_tiles(y_auto, y)
     w2 = wd.clone()
     w2[N:] *= 2
-    assert torch.equal(mb.gemm_swiglu(xd, w2), y * 2)
-    # (2) permuting the rows of X permutes the rows of Y bit for bit (no dependence on tile position)
-    perm = torch.randperm(M, generator=torch.Generator().manual_seed(2)).cuda()
-    assert torch.equal(mb.gemm_swiglu(xd[perm].contiguous(), wd), y[perm])
-    # (3) column shards are independent units: 8 shards side by side are the unsharded result bit for bit
-    parts = [mb.gemm_swiglu(xd, mb.shard_gate_up(wd, r, 8)) for r in range(8)]
-    assert torch.equal(torch.cat(parts, dim=1), y)
+    assert torch.equal(mb.gemm_swiglu(xd, w2), y_auto * 2)  # exact scaling holds in every schedule
+
+
+def assert_close_to_whole_tiles(y_sk, y_wt):
+    """Two schedules that add the same fp32 products in a different order: few outputs change, none by more than one
+    bf16 step at the scale of the data, and the change as a whole is far below the rounding noise of the output."""
+    a, b = y_sk.float(), y_wt.float()
+    diff = (a - b).abs()
+    assert (diff > 0).float().mean().item() < 0.05
+    assert diff.max().item() <= 2.0 ** -7 * b.abs().max().item()
+    assert (diff.norm() / b.norm()).item() <= 5e-4
 
 
 def test_video_dit_ffn_sampled():
@@ -212,8 +246,63 @@ def test_video_dit_ffn_sampled():
     rows = torch.cat([torch.arange(M - 130, M), torch.randperm(M - 130, generator=torch.Generator().manual_seed(3))[:254]]).cuda()
     assert_parity(y[rows], gold_fp32_gpu(xd[rows], wd), "video dit sample")
     shard = mb.shard_gate_up(wd, 7, 8)  # 1728 columns: 13.5 tiles of 128
-    for variant in ("mma", "mma2"):
-        assert torch.equal(mb.gemm_swiglu_out(xd, shard, variant=variant), y[:, 7 * 1728:]), variant
+    with whole_tile_schedules():
+        y_wt = mb.gemm_swiglu(xd, wd)
+        for variant in ("mma", "mma2"):
+            assert torch.equal(mb.gemm_swiglu_out(xd, shard, variant=variant), y_wt[:, 7 * 1728:]), variant
+    assert_close_to_whole_tiles(y, y_wt)
+    y_shard = mb.gemm_swiglu(xd, shard)  # the shard under its own balanced schedule
+    assert_parity(y_shard[rows], gold_fp32_gpu(xd[rows], shard), "video dit shard sample")
+    assert_close_to_whole_tiles(y_shard, y_wt[:, 7 * 1728:])
+
+
+# ---------------------------------------------------------------- stream-K (tile schedules, balanced last waves)
+@pytest.mark.parametrize("shape,knobs", [
+    ((8192, 1792, 4096), {}),                       # 1/8 column shard of the Llama FFN: 224 tiles on 74 CTA pairs
+    ((8192, 1792, 4096), dict(block_n=224)),        # 256 tiles
+    ((4096, 1792, 1024), {}),                       # short K: pieces of a dozen K-steps
+    ((4096, 3584, 1024), {}),
+    ((32760, 1728, 5120), {}),                      # ragged rows, 6.75 column tiles
+    ((640, 4096, 2048), dict(variant="mma")),       # one CTA per tile
+    ((2560, 2816, 1024), dict(max_ctas=24)),        # twelve workers
+])
+def test_stream_k_matches_whole_tiles_and_gold(shape, knobs):
+    """The last waves of a tile schedule are dealt to the workers as equal K ranges; a tile shared by two workers is
+    finished by the one that holds its first K-steps, from fp32 partial sums parked in scratch.  Against the fp32 gold,
+    against the whole-tile schedule (at most one bf16 step apart), and run to run (bit-identical)."""
+    M, N, K = shape
+    prev = _loader.set_tuning("stream_k", 1)
+    try:
+        plan = mb.plan(M, N, K, **knobs)
+        assert plan["sk_tiles"] > 0 and mb.workspace_bytes(M, N, K, **knobs) > 0, plan
+        x, w = make_inputs(M, K, N, seed=M + N)
+        xd, wd = x.cuda(), w.cuda()
+        y = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        mb.gemm_swiglu_out(xd, wd, out=y, **knobs)
+        again = mb.gemm_swiglu_out(xd, wd, **knobs)
+    finally:
+        _loader.set_tuning("stream_k", prev)
+    assert torch.equal(y, again), "two launches of the same stream-K schedule differ"
+    rows = torch.randperm(M, generator=torch.Generator().manual_seed(4))[:512].cuda()
+    assert_parity(y[rows], gold_fp32_gpu(xd[rows], wd), f"stream-K {shape}")
+    with whole_tile_schedules():
+        assert mb.plan(M, N, K, **knobs)["sk_tiles"] == 0
+        y_wt = mb.gemm_swiglu_out(xd, wd, **knobs)
+    assert_close_to_whole_tiles(y, y_wt)
+
+
+def test_stream_k_needs_scratch_and_is_refused_nothing_without_it():
+    """Through the C entry point without a workspace the same problem runs whole tiles (no scratch, no flags)."""
+    lib = _loader.load_library()
+    M, N, K = 2048, 1792, 512
+    x, w = make_inputs(M, K, N, seed=9)
+    xd, wd = x.cuda(), w.cuda()
+    y0 = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    rc = lib.magi_swiglu_forward_bf16(xd.data_ptr(), wd.data_ptr(), y0.data_ptr(), M, N, K, K, K, N, 0,
+                                      ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), 0)
+    assert rc == 0, _loader.last_error()
+    with whole_tile_schedules():
+        assert torch.equal(y0, mb.gemm_swiglu(xd, wd))
 
 
 # ---------------------------------------------------------------- split-K (narrow weights, M <= 128)

@@ -90,14 +90,22 @@ def test_plan_for_cta_pairs():
 
 
 def test_plan_uses_single_cta_tiles_when_the_last_row_pair_is_half_empty():
-    # M = 384 is three 128-row granules: CTA pairs would run four (two 256-row units), single CTAs run three
-    for M in (288, 320, 384):
-        p = _loader.plan(M, 28672, 8192, sm_count=148)
-        assert p["variant"] == _loader.VARIANT_MMA and p["ctas"] == 1 and p["block_n"] <= 224 and p["stages"] >= 3
-        assert p["tiles"] == 3 * -(-28672 // p["block_n"])
-    # full units, or many of them: pairs stay
-    for M in (256, 512, 640, 1024, 8192 + 128):
-        assert _loader.plan(M, 28672, 8192, sm_count=148)["variant"] == _loader.VARIANT_MMA2
+    # M = 384 is three 128-row granules: CTA pairs would run four (two 256-row units), single CTAs run three.
+    # That holds for whole-tile schedules (no scratch, or stream-K switched off) ...
+    prev = _loader.set_tuning("stream_k", 0)
+    try:
+        for M in (288, 320, 384):
+            p = _loader.plan(M, 28672, 8192, sm_count=148)
+            assert p["variant"] == _loader.VARIANT_MMA and p["ctas"] == 1 and p["block_n"] <= 224 and p["stages"] >= 3
+            assert p["tiles"] == 3 * -(-28672 // p["block_n"])
+        # full units, or many of them: pairs stay
+        for M in (256, 512, 640, 1024, 8192 + 128):
+            assert _loader.plan(M, 28672, 8192, sm_count=148)["variant"] == _loader.VARIANT_MMA2
+    finally:
+        _loader.set_tuning("stream_k", prev)
+    # ... with scratch the pairs' 224 tiles are balanced over the 74 pairs by K ranges, which beats both
+    p = _loader.plan(384, 28672, 8192, sm_count=148)
+    assert p["variant"] == _loader.VARIANT_MMA2 and p["sk_tiles"] > 0
     # an explicit width or variant is never overridden
     assert _loader.plan(384, 28672, 8192, block_n=256, sm_count=148)["variant"] == _loader.VARIANT_MMA2
     assert _loader.plan(384, 28672, 8192, variant="mma2", sm_count=148)["variant"] == _loader.VARIANT_MMA2
@@ -190,8 +198,11 @@ def test_split_k_plans_and_workspace_sizes():
     need = _loader.workspace_bytes(64, 3584, 8192, sm_count=148)
     assert need == p["tiles"] * p["k_splits"] * 64 * 2 * p["block_n"] * 4  # fp32 partial sums, nothing else
     assert need <= 64 << 20
-    # large-M schedules never ask for scratch
-    assert _loader.workspace_bytes(8192, 14336, 4096, sm_count=148) == 0
+    # large-M schedules ask for scratch only to balance a last wave that would be at most a quarter full (stream-K):
+    # one flag and one 256 KiB slab per CTA; a problem that fills its waves asks for none
+    assert _loader.workspace_bytes(8192, 14336, 4096, sm_count=148) == 256 * 3 + 148 * (256 << 10)
+    assert _loader.workspace_bytes(32760, 13824, 5120, sm_count=148) == 0      # 93.4 waves: the last one is 40 % full
+    assert _loader.workspace_bytes(8192, 4736 * 2, 4096, sm_count=148) == 0    # 37 x 32 tiles: whole waves
     assert _loader.workspace_bytes(0, 64, 64, sm_count=148) == 0
     with pytest.raises(ValueError):
         _loader.workspace_bytes(16, 100, 64, sm_count=148)

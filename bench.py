@@ -58,7 +58,10 @@ SETTLE_S = 0.5  # idle time before each workload: lets the power-cap controller 
 # DRAM bytes (read + write) of ONE launch of the dominant kernel as an earlier one-launch ncu capture RECORDED them;
 # not measured in this run, and reported only while the schedule is still the one that was profiled.
 RECORDED_TRAFFIC = {
-    # workload@gpus: (bytes, {plan keys that must match})
+    # workload@gpus: (bytes, {plan keys that must match}); the captures are summarised under profiles/
+    "llama3_8b_ffn@1": (1088.0e6, {"variant": 4, "block_n": 256, "stages": 4, "group_m": 16, "y_tma": 1, "sk_tiles": 90}),
+    "video_dit_ffn@1": (9330.3e6, {"variant": 4, "block_n": 256, "stages": 4, "group_m": 12, "y_tma": 1, "sk_tiles": 0}),
+    "decode_m64@1": (946.6e6, {"variant": 2, "block_n": 208, "stages": 3, "k_splits": 1}),
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 L2_FLUSH_BYTES = 256 << 20
@@ -599,6 +602,38 @@ def copy_rates(b, host_in, dev_out_like, host_out):
     return res
 
 
+def run_single_kernel(b, mb, args):
+    """--only: one of the library's other kernels by itself, for launch lists and counter captures."""
+    dev = b.dev
+    g = torch.Generator(device=dev)
+    g.manual_seed(0)
+
+    def rnd(r, c, scale):
+        return (torch.randn(r, c, generator=g, device=dev) * scale).to(torch.bfloat16)
+
+    if args.only == "gemm_nt":       # down projection of the MLP block on one GPU: [16384, 28672] x [8192, 28672]^T
+        a, w = rnd(16384, 28672, 1.0), rnd(8192, 28672, 0.02)
+        out = torch.empty(16384, 8192, dtype=torch.bfloat16, device=dev)
+        fn, flops, nbytes = (lambda: mb.gemm_nt_out(a, w, out=out)), 2.0 * 16384 * 28672 * 8192, None
+    elif args.only == "backward_dh":  # recomputing backward of the op, Llama-3-8B FFN shape: dH from x, W and dY
+        M, K, N = WORKLOADS["llama3_8b_ffn"][:3]
+        x, w, dy = rnd(M, K, 1.0), rnd(2 * N, K, 0.02), rnd(M, N, 1.0)
+        fn, flops, nbytes = (lambda: mb.swiglu_backward_dh(x, w, dy)), flops_of(M, K, N), None
+    else:                             # 1/8 column shard of the decode weight, M = 64: split-K tile kernel + ordered reduce
+        M, K, N = 64, 8192, 3584
+        x, w = rnd(M, K, 1.0), rnd(2 * N, K, 0.02)
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        fn, flops, nbytes = (lambda: mb.gemm_swiglu_out(x, w, out=out)), None, bytes_of(M, K, N)
+    ms, per_step, _ = b.time_steps(fn, args.steps, args.warmup)
+    b.check_status(mb)
+    line = {"only": args.only, "ms_per_step": ms, "ms_median": statistics.median(per_step), "steps": args.steps}
+    if flops:
+        line["tflops"] = flops / (ms * 1e-3) / 1e12
+    if nbytes:
+        line["gbs"] = nbytes / (ms * 1e-3) / 1e9
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -621,6 +656,10 @@ def main():
     ap.add_argument("--train", action="store_true",
                     help="also time forward + backward of the op (both autograd forms) against the eager expression")
     ap.add_argument("--no-flush", action="store_true", help="profiling runs only: skip the L2 flush kernels")
+    ap.add_argument("--only", default=None, choices=["gemm_nt", "backward_dh", "decode_shard"],
+                    help="profiling runs only: time one of the other kernels of the library by itself (1 GPU) and print a "
+                         "short JSON line: the down projection of the MLP block (gemm_nt), the recomputing backward "
+                         "(backward_dh, Llama shape), or a 1/8 decode column shard (split-K tile kernel + ordered reduce)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" and not args.no_flush else args.warmup
 
@@ -649,6 +688,9 @@ def main():
     sub_steps = max(5, min(args.steps, 20))
     sub_warmup = max(3, min(args.warmup, 5))
 
+    if args.only:
+        run_single_kernel(b, mb, args)
+        return
     if args.workload == "mlp_block":  # the MLP block alone, as the line's headline
         rec = run_mlp_block(b, mb, args.steps, args.warmup, args.chunks, args.reduce, args.down)
         if rank == 0:

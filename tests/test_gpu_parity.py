@@ -182,6 +182,26 @@ def test_special_values():
     assert torch.allclose(y.float(), exp, rtol=1e-2, atol=1e-6)
 
 
+def test_non_finite_values():
+    """NaN and +inf pre-activations behave like the eager expression; -inf stays non-finite (eager: NaN)."""
+    M, N, K = 32, 64, 64
+    inf, nan = float("inf"), float("nan")
+    x = torch.zeros(M, K, dtype=torch.bfloat16)
+    w = torch.zeros(2 * N, K, dtype=torch.bfloat16)
+    x[:, 0] = 1.0
+    w[:N, 0] = 1.0
+    w[N:, 0] = 3.0
+    w[0, 0], w[1, 0], w[2, 0] = inf, -inf, nan   # gate columns 0, 1, 2
+    w[N + 3, 0], w[N + 4, 0] = inf, nan          # up columns 3, 4
+    w[5, 0], w[N + 5, 0] = 0.0, inf              # 0 * inf
+    y = mb.gemm_swiglu(x.cuda(), w.cuda()).cpu().float()
+    ref = (torch.nn.functional.silu(w[:N, 0].float()) * w[N:, 0].float()).expand(M, N)
+    same = [c for c in range(N) if c != 1]
+    assert torch.equal(torch.isnan(y[:, same]), torch.isnan(ref[:, same]))
+    assert torch.allclose(y[:, same], ref[:, same], rtol=1e-2, atol=1e-6, equal_nan=True)
+    assert not torch.isfinite(y[:, 1]).any()
+
+
 # ---------------------------------------------------------------- benchmark sizes: properties + sampled gold
 @pytest.mark.parametrize("M", [16, 64, 128])
 def test_decode_shapes_full_size(M):

@@ -487,7 +487,7 @@ def run_mlp_block(b, mb, steps, warmup, chunks, reduce, down):
     finally:
         torch.backends.cuda.matmul.allow_tf32 = prev
     out = out_box[0]
-    if reduce == "reduce_scatter" and b.world > 1:  # this rank holds only its rows of the sum: check those
+    if reduce in ("reduce_scatter", "peer_scatter") and b.world > 1:  # this rank holds only its rows of the sum: check those
         own = mlp.owned_rows(M).to(b.dev)
         pos = torch.arange(0, own.numel(), max(1, own.numel() // PARITY_ROWS), device=b.dev)[:PARITY_ROWS]
         rows = own[pos]
@@ -504,13 +504,16 @@ def run_mlp_block(b, mb, steps, warmup, chunks, reduce, down):
         "ms_median": b.reduce(statistics.median(per_step)), "ms_min": b.reduce(min(per_step)),
         "value": value, "unit": "TFLOP/s", "chunks": chunks, "reduce": reduce,
         "down_projection": "magi_swiglu_gemm_nt_bf16 (own tile kernel)" if down == "own" else "torch.matmul (library GEMM)",
-        "parallelism": f"tp{b.world}: column-parallel gate/up, row-parallel down, NCCL {reduce.replace('_', '-')} of "
-                       f"[{M},{K}] bf16" if b.world > 1 else "1 GPU: no reduction",
+        "parallelism": (f"tp{b.world}: column-parallel gate/up, row-parallel down, " +
+                        ("row blocks of the partial products stored by the down projection's epilogue into their owner's "
+                         "memory over NVLink (no collective kernel), barrier, slot sum" if reduce == "peer_scatter"
+                         else f"NCCL {reduce.replace('_', '-')}") + f" of [{M},{K}] bf16") if b.world > 1 else "1 GPU: no reduction",
         "l2": "inputs (1.7 GB) larger than L2, back-to-back steps",
         "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s", "frac": per_gpu / peak,
                      "nominal_frac": per_gpu / 2250.0, "algorithmic_flops": flops / b.world, "traffic": None,
                      "peak_kind": f"{b.peak_kind} cuBLAS bf16 sustained (kernels timed inside a long step)"},
-        "gpu_launches": steps * chunks * (2 if down == "own" else 1), "parity": parity,
+        "gpu_launches": steps * (3 if reduce == "peer_scatter" and b.world > 1 else chunks * (2 if down == "own" else 1)),
+        "parity": parity,
     }
     del mlp, x, w, wd
     return rec
@@ -646,7 +649,7 @@ def main():
     ap.add_argument("--stages", type=int, default=0)
     ap.add_argument("--group-m", type=int, default=0)
     ap.add_argument("--chunks", type=int, default=4, help="mlp_block: row chunks whose reduction overlaps the next chunk")
-    ap.add_argument("--reduce", default="all_reduce", choices=["all_reduce", "reduce_scatter"],
+    ap.add_argument("--reduce", default="all_reduce", choices=["all_reduce", "reduce_scatter", "peer_scatter"],
                     help="mlp_block: all ranks get the whole result, or each keeps its rows of the sum")
     ap.add_argument("--down", default="own", choices=["own", "library"], help="mlp_block: kernel of the down projection")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -656,6 +659,8 @@ def main():
     ap.add_argument("--train", action="store_true",
                     help="also time forward + backward of the op (both autograd forms) against the eager expression")
     ap.add_argument("--no-flush", action="store_true", help="profiling runs only: skip the L2 flush kernels")
+    ap.add_argument("--no-peer-scatter", action="store_true",
+                    help="N > 1: skip the MLP block variant whose down projection stores into the other GPUs' memory")
     ap.add_argument("--only", default=None, choices=["gemm_nt", "backward_dh", "decode_shard"],
                     help="profiling runs only: time one of the other kernels of the library by itself (1 GPU) and print a "
                          "short JSON line: the down projection of the MLP block (gemm_nt), the recomputing backward "
@@ -831,6 +836,9 @@ def main():
                 if world > 1:  # the same block with each rank keeping only its rows of the sum (half the link bytes)
                     alt = run_mlp_block(b, mb, sub_steps, sub_warmup, 1, "reduce_scatter", args.down)
                     subs[name]["reduce_scatter"] = {k: alt[k] for k in ("ms_per_step", "value", "unit", "chunks", "parity")}
+                    if not args.no_peer_scatter:  # ... and with the reduce-scatter's transfer fused into the down projection
+                        alt = run_mlp_block(b, mb, sub_steps, sub_warmup, 1, "peer_scatter", "own")
+                        subs[name]["peer_scatter"] = {k: alt[k] for k in ("ms_per_step", "value", "unit", "parallelism", "parity")}
                 continue
             sM, sK, sN, _, _ = WORKLOADS[name]
             xs, ws = make_inputs_cuda(sM, sK, sN, dev, seed=0)
@@ -839,7 +847,7 @@ def main():
             subs[name] = time_op_workload(b, mb, name, xs, ws, sub_steps, sub_warmup)[0]
             del xs, ws
     ok = head["parity"]["ok"] and all(r["parity"]["ok"] and r.get("reduce_scatter", {}).get("parity", {}).get("ok", True)
-                                      for r in subs.values())
+                                      and r.get("peer_scatter", {}).get("parity", {}).get("ok", True) for r in subs.values())
 
     if rank != 0:
         if world > 1:

@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define MAGI_SWIGLU_ABI_VERSION 4
+#define MAGI_SWIGLU_ABI_VERSION 5
 
 /* variant selector of magi_swiglu_forward_bf16 */
 #define MAGI_SWIGLU_VARIANT_AUTO   0  /* M <= 128 -> STREAM, else MMA2           */
@@ -176,6 +176,36 @@ int magi_swiglu_forward_nvfp4(const void* x, const void* w_gate_up, void* y_fp4,
  * (example/training/llama3.py:169,173), which the reference runs through a library GEMM. */
 int magi_swiglu_gemm_nt_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,
                       int64_t lda, int64_t ldb, int64_t ldc, int device, void* cuda_stream);
+
+/* The row-parallel down projection with the reduction's first half fused into its epilogue: the plain GEMM above,
+ * but block o of C's rows ([o * rows_per_owner, (o + 1) * rows_per_owner)) is written by the epilogue's TMA stores
+ * straight into dst[o], a [rows_per_owner, N] bf16 matrix (row stride ldc) that may live in ANOTHER GPU's memory
+ * mapped into this process (peer access, e.g. a symmetric-memory allocation).  With every GPU of a tensor-parallel
+ * group pointing dst[o] at "its own slot in owner o's receive buffer", each owner ends up with one partial product
+ * per GPU for its rows and finishes with magi_swiglu_sum_slots_bf16 - a reduce-scatter whose data movement is the
+ * GEMM's own output stores, overlapped with the tensor work tile by tile, with no copy of C in between.
+ *
+ * magi_swiglu_scatter_setup encodes the destinations' tensor maps into one of two sets kept in the library's constant
+ * memory for `device` (set-up time: it copies synchronously; do not call it while a scattered GEMM of that set may be
+ * running).  world <= 8, rows_per_owner % 32 == 0, N % 64 == 0.  magi_swiglu_gemm_nt_bf16_scatter then runs
+ * C = A[M,K] · B[N,K]^T with M == world * rows_per_owner and N as set up, M > 128.  The call orders nothing between
+ * GPUs: the caller makes sure the destinations are free before the launch and that all writers have finished (a
+ * barrier across the GPUs on the streams involved) before anyone reads them.  Scratch as in
+ * magi_swiglu_forward_bf16_ws (optional).
+ * Replaces: the all-reduce after fairscale's RowParallelLinear w2 (example/training/llama3.py:169,173); the reference
+ * has no fused form of it. */
+int magi_swiglu_scatter_setup(int device, int set, void* const* dst, int world, int64_t rows_per_owner, int64_t N,
+                              int64_t ldc);
+int magi_swiglu_gemm_nt_bf16_scatter(const void* a, const void* b, int set, int64_t M, int64_t N, int64_t K,
+                                     int64_t lda, int64_t ldb, int device, void* cuda_stream, void* workspace,
+                                     int64_t workspace_bytes);
+
+/* out[i] = sum over s < slots of src[s * slot_stride + i], i < n: bf16 in, fp32 sums in slot order, one rounding to
+ * bf16.  n % 8 == 0, slot_stride % 8 == 0, 16-byte aligned pointers.  The last step of the scattered down projection
+ * (slot s = what GPU s wrote for this GPU's rows); HBM-bound, element-wise.  It has no counterpart in the reference
+ * (NCCL's reduction kernel does this inside the all-reduce). */
+int magi_swiglu_sum_slots_bf16(const void* src, void* out, int slots, int64_t slot_stride, int64_t n, int device,
+                               void* cuda_stream);
 
 /* The same plain GEMM with either operand stored the other way round, C[M,N] = op(A) · op(B)^T in bf16:
  *   a_layout 0: A is [M, K] (row stride lda);  1: A is stored [K, M] (its transpose, row stride lda, M % 8 == 0);

@@ -43,6 +43,11 @@ constexpr long long kWaitLimitCycles = 6000000000LL;  // default wait limit: thr
 constexpr int kStageOutBytes = 2048;   // one 32-row x 32-column bf16 box of Y on its way to a TMA store
 constexpr int kStagingBytes = kEpiWarps * 2 * kStageOutBytes;  // two boxes per epilogue warp
 
+constexpr int kMaxScatterOwners = 8;  // GPUs of one NVLink domain a scattered plain GEMM can write to
+// Tensor maps of a scattered plain GEMM's destinations: [set][owner], one per GPU that owns a block of C's rows
+// (this GPU included), written once by magi_swiglu_scatter_setup.  Two sets so that consecutive steps can alternate.
+__constant__ CUtensorMap g_scatter_maps[2][kMaxScatterOwners];
+
 __device__ unsigned int g_watchdog[4];  // {role that gave up, block, stage/buffer, parity}
 // {SM cycles, nanoseconds} block 0 of the most recent tile kernel spent between set-up and teardown: the
 // SM clock the kernel really ran at (power capping moves it within a millisecond; nvidia-smi cannot see that)
@@ -116,6 +121,9 @@ struct KArgs {
   int* sk_flags;       // [units * kCtas], zeroed by the host before the launch
   float* sk_partials;  // [units * kCtas][8 epilogue warps][chunks per warp][16 float4][32 lanes] fp32
   int y_tma;  // 1: bf16 Y (or the plain GEMM's C) leaves through shared memory and TMA stores (tm_y is valid)
+  // Scattered plain GEMM: rows [o * scatter_rows, (o + 1) * scatter_rows) of C go to the buffer of owner o through
+  // g_scatter_maps[scatter_set][o] (TMA stores only; y is null).  0: off.
+  int scatter_rows, scatter_set;
   long long wait_limit;  // SM cycles after which a wait on an mbarrier gives up (kWaitLimitCycles by default)
 };
 
@@ -927,7 +935,12 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
           __syncwarp();
           const int box_row0 = (mt * kCtas + (int)cta_rank) * kBM + q * 32;
           if (lane == 0 && box_row0 < a.M) {
-            tma_store_3d_hint(buf, &tm_y, col, half, box_row0, y_policy);
+            if (a.scatter_rows) {  // this box belongs to one owner (scatter_rows is a multiple of 32)
+              const int owner = box_row0 / a.scatter_rows;
+              tma_store_3d(buf, &g_scatter_maps[a.scatter_set][owner], col, half, box_row0 - owner * a.scatter_rows);
+            } else {
+              tma_store_3d_hint(buf, &tm_y, col, half, box_row0, y_policy);
+            }
             bulk_commit_group();
           }
           stg_par ^= 1u;
@@ -978,7 +991,7 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
             }
             return;
           }
-          if (!row_ok) return;
+          if (!row_ok || a.scatter_rows) return;  // a scattered GEMM has no direct-store path (the host only plans whole boxes)
           if (a.h != nullptr) {  // training forward: keep the pre-activations for the backward
             __nv_bfloat16* hrow = a.h + (long long)row * a.ldh + col0 + seg * seg_cols + c;
             if (w == 32) {
@@ -1099,7 +1112,12 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         }
       }
     }
-    if (a.y_tma && lane == 0) bulk_wait_group_read<0>();  // shared memory stays valid until the last store has read it
+    if (a.y_tma && lane == 0) {
+      if (a.scatter_rows)
+        bulk_wait_group<0>();  // stores into other GPUs' memory: complete, not just read, before this CTA retires
+      else
+        bulk_wait_group_read<0>();  // shared memory stays valid until the last store has read it
+    }
   }
 
   // ------------------------------------------------------------ teardown (also the abort path)
@@ -1142,12 +1160,29 @@ swiglu_splitk_reduce_kernel(const float* __restrict__ ws, __nv_bfloat16* __restr
     if (col >= N) continue;  // N is a multiple of 8: a group is inside or outside as a whole
     const float* p = ws + (((size_t)t * k_splits) * M + row) * (2 * block_n) + cg * 8;
     float g[8] = {0, 0, 0, 0, 0, 0, 0, 0}, u[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int z = 0; z < k_splits; ++z, p += (size_t)M * 2 * block_n) {
-      const float4 g0 = __ldcg(reinterpret_cast<const float4*>(p)), g1 = __ldcg(reinterpret_cast<const float4*>(p + 4));
-      const float4 u0 = __ldcg(reinterpret_cast<const float4*>(p + block_n));
-      const float4 u1 = __ldcg(reinterpret_cast<const float4*>(p + block_n + 4));
-      g[0] += g0.x; g[1] += g0.y; g[2] += g0.z; g[3] += g0.w; g[4] += g1.x; g[5] += g1.y; g[6] += g1.z; g[7] += g1.w;
-      u[0] += u0.x; u[1] += u0.y; u[2] += u0.z; u[3] += u0.w; u[4] += u1.x; u[5] += u1.y; u[6] += u1.z; u[7] += u1.w;
+    const size_t z_stride = (size_t)M * 2 * block_n;
+    for (int z0 = 0; z0 < k_splits; z0 += 4, p += 4 * z_stride) {
+      // four splits' loads are issued before the first add so their latencies overlap; the adds keep split order
+      float4 v[4][4];
+#pragma unroll
+      for (int zz = 0; zz < 4; ++zz) {
+        if (z0 + zz < k_splits) {
+          const float* q = p + zz * z_stride;
+          v[zz][0] = __ldcg(reinterpret_cast<const float4*>(q));
+          v[zz][1] = __ldcg(reinterpret_cast<const float4*>(q + 4));
+          v[zz][2] = __ldcg(reinterpret_cast<const float4*>(q + block_n));
+          v[zz][3] = __ldcg(reinterpret_cast<const float4*>(q + block_n + 4));
+        }
+      }
+#pragma unroll
+      for (int zz = 0; zz < 4; ++zz) {
+        if (z0 + zz < k_splits) {
+          g[0] += v[zz][0].x; g[1] += v[zz][0].y; g[2] += v[zz][0].z; g[3] += v[zz][0].w;
+          g[4] += v[zz][1].x; g[5] += v[zz][1].y; g[6] += v[zz][1].z; g[7] += v[zz][1].w;
+          u[0] += v[zz][2].x; u[1] += v[zz][2].y; u[2] += v[zz][2].z; u[3] += v[zz][2].w;
+          u[4] += v[zz][3].x; u[5] += v[zz][3].y; u[6] += v[zz][3].z; u[7] += v[zz][3].w;
+        }
+      }
     }
     const float rs = row_scale != nullptr ? __ldg(row_scale + row) : 1.0f;
     uint32_t gb[8], ub[8];
@@ -1157,6 +1192,35 @@ swiglu_splitk_reduce_kernel(const float* __restrict__ ws, __nv_bfloat16* __restr
       ub[j] = __float_as_uint(u[j] * rs);
     }
     st_global_v4_hint(y + (long long)row * ldy + col, swiglu_pack8(gb, ub), policy);
+  }
+}
+
+// out[i] = sum over slots of src[slot * slot_stride + i], added in slot order in fp32 and rounded once to bf16: the
+// last step of a scattered row-parallel GEMM, where slot r holds what GPU r's epilogue wrote for this GPU's rows.
+// Element-wise, HBM-bound; 8 elements per thread with 16-byte accesses (n % 8 == 0).
+__global__ void __launch_bounds__(256)
+swiglu_sum_slots_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ out, int slots,
+                        long long slot_stride, long long n) {
+  const long long groups = n / 8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < groups; i += (long long)gridDim.x * blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int sl = 0; sl < slots; ++sl) {
+      const uint4 v = __ldcs(reinterpret_cast<const uint4*>(src + sl * slot_stride + 8 * i));
+      const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(v2[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    *reinterpret_cast<uint4*>(out + 8 * i) = o;
   }
 }
 

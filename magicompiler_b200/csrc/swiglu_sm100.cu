@@ -34,6 +34,11 @@ struct DeviceInfo {
   int pair_clusters = 0;  // co-resident 2-CTA clusters of the pair kernel (0 = not queried yet, -1 = none)
 };
 static DeviceInfo g_dev[kMaxDevices];
+struct ScatterSet {  // what magi_swiglu_scatter_setup last wrote into g_scatter_maps[set] of a device
+  int world = 0;
+  int64_t rows = 0, n = 0;
+};
+static ScatterSet g_scatter[kMaxDevices][2];
 static std::mutex g_dev_mutex;
 
 static const DeviceInfo* device_info(int device) {
@@ -149,10 +154,10 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
                         int group_m, int max_ctas, void* workspace, int64_t workspace_bytes, int plain = 0,
                         const float* row_scale = nullptr, const float* out_scale = nullptr, const void* dy = nullptr,
                         int64_t lddy = 0, void* h = nullptr, int64_t ldh = 0, void* sf = nullptr, int64_t ld_sf = 0,
-                        int sf_swizzled = 0, int a_mn = 0, int b_mn = 0) {
+                        int sf_swizzled = 0, int a_mn = 0, int b_mn = 0, int64_t scatter_rows = 0, int scatter_set = 0) {
   g_err[0] = 0;
   if (M == 0 && N > 0 && K > 0) return 0;
-  if (!x || !w || !y) return fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
+  if (!x || !w || (!y && !scatter_rows)) return fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
   // an operand stored [K, cols] has rows of `cols` elements; an nvfp4 output row is N/2 bytes
   if (ldx < (a_mn ? M : K) || ldw < (b_mn ? 2 * N : K) || ldy < (plain ? 2 * N : (sf ? N / 2 : N)))
     return fail(MAGI_SWIGLU_ERR_SHAPE, "row strides too small: ldx=%lld ldw=%lld (K=%lld) ldy=%lld (N=%lld)",
@@ -200,7 +205,14 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   rc = encode_maps(x, w, M, N, K, ldx, ldw, p, &tm_x, &tm_w, a_mn, b_mn);
   if (rc) return rc;
   // a Y layout the tensor-map encoder refuses simply keeps the direct stores (the staging boxes stay unused)
-  const int y_tma = (p.y_tma && encode_y_map(y, M, N, plain ? 2 : 1, ldy, &tm_y) == 0) ? 1 : 0;
+  int y_tma = 0;
+  if (scatter_rows) {  // the destinations' maps are in constant memory already; only whole 32 x 32 boxes can leave
+    if (!p.y_tma || p.ctas != 2 || p.block_n % 64 != 0 || N % 32 != 0)
+      return fail(MAGI_SWIGLU_ERR_VARIANT, "this shape cannot be scattered (pair tiles with staged stores and whole 32-column boxes are needed; tile width %d)", p.block_n);
+    y_tma = 1;
+  } else {
+    y_tma = (p.y_tma && encode_y_map(y, M, N, plain ? 2 : 1, ldy, &tm_y) == 0) ? 1 : 0;
+  }
   g_err[0] = 0;
 
   int pair_clusters = 0;
@@ -274,6 +286,8 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   a.kb_per_split = p.kb_per_split;
   a.ws = p.k_splits > 1 ? static_cast<float*>(workspace) : nullptr;
   a.y_tma = y_tma;
+  a.scatter_rows = (int)scatter_rows;
+  a.scatter_set = scatter_set;
   a.wait_limit = kWaitLimitCycles;
   auto fill_stream_k = [&]() {
     a.sk_first_tile = p.sk_first_tile;
@@ -544,6 +558,88 @@ int magi_swiglu_gemm_nt_bf16(const void* a, const void* b, void* c, int64_t M, i
   // (the streaming schedule's split-K reduce applies the activation).
   const int variant = (M <= 128) ? MAGI_SWIGLU_VARIANT_MMA : MAGI_SWIGLU_VARIANT_MMA2;
   return magi::forward_impl(a, b, c, M, N / 2, K, lda, ldb, ldc, device, cuda_stream, variant, 0, 0, 0, 0, nullptr, 0, 1);
+}
+
+int magi_swiglu_scatter_setup(int device, int set, void* const* dst, int world, int64_t rows_per_owner, int64_t N,
+                              int64_t ldc) {
+  magi::g_err[0] = 0;
+  if (set < 0 || set > 1) return magi::fail(MAGI_SWIGLU_ERR_VARIANT, "destination set must be 0 or 1 (got %d)", set);
+  if (world < 1 || world > magi::kMaxScatterOwners)
+    return magi::fail(MAGI_SWIGLU_ERR_SHAPE, "a scattered GEMM writes to 1..%d owners (got %d)", magi::kMaxScatterOwners, world);
+  if (!dst) return magi::fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
+  if (rows_per_owner <= 0 || rows_per_owner % 32 != 0 || rows_per_owner > 0x7fffff00LL / world)
+    return magi::fail(MAGI_SWIGLU_ERR_SHAPE, "rows per owner (%lld) must be a positive multiple of 32", (long long)rows_per_owner);
+  if (N <= 0 || N % 64 != 0 || ldc < N || ldc % 8 != 0)
+    return magi::fail(MAGI_SWIGLU_ERR_SHAPE, "a scattered GEMM needs N (%lld) to be a multiple of 64 and ldc (%lld) >= N, a multiple of 8",
+                      (long long)N, (long long)ldc);
+  const magi::DeviceInfo* di = magi::device_info(device);
+  if (!di) return magi::fail(MAGI_SWIGLU_ERR_DEVICE, "device %d is not available", device);
+  if (di->cc_major != 10 || di->cc_minor != 0)
+    return magi::fail(MAGI_SWIGLU_ERR_DEVICE, "device %d is not sm_100 (B200)", device);
+  magi::DeviceGuard guard;
+  cudaError_t e = guard.set(device);
+  if (e != cudaSuccess) return magi::fail_cuda(e, "cudaSetDevice");
+  CUtensorMap maps[magi::kMaxScatterOwners];
+  memset(maps, 0, sizeof(maps));
+  for (int o = 0; o < world; ++o) {
+    if (!dst[o] || ((uintptr_t)dst[o] & 15u))
+      return magi::fail(MAGI_SWIGLU_ERR_ALIGN, "destination %d must be a 16-byte aligned device pointer", o);
+    const int rc = magi::encode_y_map(dst[o], rows_per_owner, N / 2, 2, ldc, &maps[o]);
+    if (rc) return rc;
+  }
+  // a plain synchronous copy into the module's constant memory: set-up time, not the data path
+  e = cudaMemcpyToSymbol(magi::g_scatter_maps, maps, sizeof(maps), (size_t)set * sizeof(maps), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) return magi::fail_cuda(e, "cudaMemcpyToSymbol(scatter maps)");
+  std::lock_guard<std::mutex> lock(magi::g_dev_mutex);
+  magi::ScatterSet& ss = magi::g_scatter[device][set];
+  ss.world = world;
+  ss.rows = rows_per_owner;
+  ss.n = N;
+  return 0;
+}
+
+int magi_swiglu_gemm_nt_bf16_scatter(const void* a, const void* b, int set, int64_t M, int64_t N, int64_t K, int64_t lda,
+                                     int64_t ldb, int device, void* cuda_stream, void* workspace,
+                                     int64_t workspace_bytes) {
+  magi::g_err[0] = 0;
+  if (set < 0 || set > 1) return magi::fail(MAGI_SWIGLU_ERR_VARIANT, "destination set must be 0 or 1 (got %d)", set);
+  if (device < 0 || device >= magi::kMaxDevices) return magi::fail(MAGI_SWIGLU_ERR_DEVICE, "device %d is not available", device);
+  magi::ScatterSet ss;
+  {
+    std::lock_guard<std::mutex> lock(magi::g_dev_mutex);
+    ss = magi::g_scatter[device][set];
+  }
+  if (ss.world == 0) return magi::fail(MAGI_SWIGLU_ERR_VARIANT, "destination set %d of device %d has not been set up", set, device);
+  if (N != ss.n || M != ss.rows * ss.world)
+    return magi::fail(MAGI_SWIGLU_ERR_SHAPE, "destination set %d was set up for C[%lld, %lld], not [%lld, %lld]", set,
+                      (long long)(ss.rows * ss.world), (long long)ss.n, (long long)M, (long long)N);
+  if (M <= 128) return magi::fail(MAGI_SWIGLU_ERR_VARIANT, "a scattered GEMM needs more than 128 rows (pair tiles)");
+  const int block_n = (N / 2) % 256 == 0 ? 256 : ((N / 2) % 128 == 0 ? 128 : 64);
+  return magi::forward_impl(a, b, nullptr, M, N / 2, K, lda, ldb, N, device, cuda_stream, MAGI_SWIGLU_VARIANT_MMA2, block_n,
+                            0, 0, 0, workspace, workspace_bytes, 1, nullptr, nullptr, nullptr, 0, nullptr, 0, nullptr, 0, 0,
+                            0, 0, ss.rows, set);
+}
+
+int magi_swiglu_sum_slots_bf16(const void* src, void* out, int slots, int64_t slot_stride, int64_t n, int device,
+                               void* cuda_stream) {
+  magi::g_err[0] = 0;
+  if (n == 0) return 0;
+  if (!src || !out) return magi::fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
+  if (slots < 1 || slots > 64 || n < 0 || n % 8 != 0 || slot_stride < n || slot_stride % 8 != 0)
+    return magi::fail(MAGI_SWIGLU_ERR_SHAPE, "bad slots=%d n=%lld slot_stride=%lld (n and the stride must be multiples of 8)", slots,
+                      (long long)n, (long long)slot_stride);
+  if (((uintptr_t)src | (uintptr_t)out) & 15u) return magi::fail(MAGI_SWIGLU_ERR_ALIGN, "pointers must be 16-byte aligned");
+  const magi::DeviceInfo* di = magi::device_info(device);
+  if (!di) return magi::fail(MAGI_SWIGLU_ERR_DEVICE, "device %d is not available", device);
+  magi::DeviceGuard guard;
+  cudaError_t e = guard.set(device);
+  if (e != cudaSuccess) return magi::fail_cuda(e, "cudaSetDevice");
+  const long long want = (n / 8 + 255) / 256;
+  const int blocks = (int)(want < 16LL * di->sm_count ? want : 16LL * di->sm_count);
+  magi::swiglu_sum_slots_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      static_cast<const __nv_bfloat16*>(src), static_cast<__nv_bfloat16*>(out), slots, (long long)slot_stride, (long long)n);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : magi::fail_cuda(e, "launch of swiglu_sum_slots_kernel");
 }
 
 int magi_swiglu_gemm_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,

@@ -20,6 +20,7 @@ the output is bf16 on that device.  There is no fp16/fp32 path, no CPU path and 
 """
 from __future__ import annotations
 
+import ctypes
 import os
 
 import torch
@@ -220,6 +221,57 @@ def gemm_nt_out(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = Non
 
 
 gemm_nt_out.supports_out = True  # TensorParallelSwiGLUMLP passes its result slice as out=
+
+
+def scatter_setup(dest_set: int, dst_ptrs: list[int], rows_per_owner: int, n: int, ldc: int | None = None,
+                  device: int | None = None) -> None:
+    """Tell the library where block ``o`` of a scattered GEMM's rows goes (``magi_swiglu_scatter_setup``): ``dst_ptrs[o]``
+    is the address, valid in this process, of a ``[rows_per_owner, n]`` bf16 matrix that may live on another GPU."""
+    dev = torch.cuda.current_device() if device is None else device
+    arr = (ctypes.c_void_p * len(dst_ptrs))(*dst_ptrs)
+    rc = _loader.load_library().magi_swiglu_scatter_setup(dev, dest_set, arr, len(dst_ptrs), rows_per_owner, n,
+                                                           n if ldc is None else ldc)
+    if rc != 0:
+        msg = f"magi_swiglu_scatter_setup failed ({rc}): {_loader.last_error()}"
+        raise (ValueError(msg) if rc < 0 else RuntimeError(msg))
+
+
+def gemm_nt_scatter(a: torch.Tensor, b: torch.Tensor, dest_set: int) -> None:
+    """``F.linear(a, b)`` whose row blocks leave the epilogue straight into the destinations of ``dest_set``
+    (``magi_swiglu_gemm_nt_bf16_scatter``); nothing is returned and nothing is ordered between GPUs."""
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or not (a.is_cuda and b.is_cuda) or a.device != b.device:
+        raise TypeError("gemm_nt_scatter computes in bf16 on CUDA tensors of one device")
+    if b.dim() != 2 or a.dim() != 2 or a.shape[1] != b.shape[1]:
+        raise ValueError(f"shapes do not fit: a {tuple(a.shape)}, b {tuple(b.shape)} (need [M,K], [N,K])")
+    n, k = b.shape
+    a2, b2 = _rows_view(a, k), _rows_view(b, k)
+    m = a2.shape[0]
+    dev = a.device.index if a.device.index is not None else torch.cuda.current_device()
+    rc = _loader.load_library().magi_swiglu_gemm_nt_bf16_scatter(
+        a2.data_ptr(), b2.data_ptr(), dest_set, m, n, k, a2.stride(0), b2.stride(0), dev,
+        torch.cuda.current_stream(a.device).cuda_stream, None, 0)  # whole tiles, like gemm_nt: no scratch
+    if rc != 0:
+        msg = f"magi_swiglu_gemm_nt_bf16_scatter failed ({rc}): {_loader.last_error()}"
+        raise (ValueError(msg) if rc < 0 else RuntimeError(msg))
+
+
+def sum_slots(src: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``src[0] + src[1] + ...`` over the first dimension (bf16, contiguous), fp32 sums in slot order, one rounding
+    (``magi_swiglu_sum_slots_bf16``)."""
+    if src.dtype != torch.bfloat16 or not src.is_cuda or not src.is_contiguous() or src.dim() < 2:
+        raise TypeError("sum_slots takes a contiguous bf16 CUDA tensor [slots, ...]")
+    slots, n = src.shape[0], src[0].numel()
+    if out is None:
+        out = torch.empty(src.shape[1:], dtype=torch.bfloat16, device=src.device)
+    elif out.dtype != torch.bfloat16 or out.device != src.device or out.numel() != n or not out.is_contiguous():
+        raise ValueError("out must be a contiguous bf16 tensor of one slot's size on src's device")
+    dev = src.device.index if src.device.index is not None else torch.cuda.current_device()
+    rc = _loader.load_library().magi_swiglu_sum_slots_bf16(src.data_ptr(), out.data_ptr(), slots, n, n, dev,
+                                                            torch.cuda.current_stream(src.device).cuda_stream)
+    if rc != 0:
+        msg = f"magi_swiglu_sum_slots_bf16 failed ({rc}): {_loader.last_error()}"
+        raise (ValueError(msg) if rc < 0 else RuntimeError(msg))
+    return out
 
 
 @magi_register_custom_op(name=GEMM_NT_OP_NAME, mutates_args=(),

@@ -5,12 +5,16 @@ Layout follows the reference's Llama example (example/training/llama3.py:168-170
 column-parallel with ``gather_output=False`` (rank r owns output columns ``[r*N/P, (r+1)*N/P)``), ``w2``
 is row-parallel with ``input_is_parallel=True`` (rank r owns the matching input columns and the partial
 products are summed with one all-reduce).  The fused op needs no collective: rank r multiplies the
-replicated activations by its own packed shard ``cat(Wg[rows_r], Wu[rows_r])``.  No GPU ever reads
-another GPU's memory; the only exchange is the NCCL all-reduce after the down-projection.
+replicated activations by its own packed shard ``cat(Wg[rows_r], Wu[rows_r])``.  The only exchange is the
+reduction after the down-projection: NCCL's all-reduce or reduce-scatter, or ``reduce="peer_scatter"``, where
+the down projection's own epilogue stores each row block into the memory of the GPU that owns it
+(``PeerScatterReducer``).  No GPU ever READS another GPU's memory.
 """
 from __future__ import annotations
 
 from typing import Callable
+
+import os
 
 import torch
 import torch.distributed as dist
@@ -72,6 +76,67 @@ class ColumnParallelSwiGLU(torch.nn.Module):
         return fn(x, self.weight)
 
 
+class PeerScatterReducer:
+    """Reduce-scatter of a row-parallel GEMM whose data movement is the GEMM's own epilogue.
+
+    Every rank holds a receive buffer ``[2 sets][world slots][M/world rows][n_out]`` in symmetric memory (mapped into
+    all ranks of the group).  ``linear_reduce_scatter(h, w_down)`` runs ``h @ w_down.T`` on the tile kernels with the
+    epilogue's TMA stores aimed at slot ``rank`` of the buffer of whichever GPU owns the row block
+    (``magi_swiglu_gemm_nt_bf16_scatter``), waits for all ranks on the stream (a one-element NCCL all-reduce: it
+    starts after this rank's GEMM has completed and ends only when every rank has joined, and a rank that never joins
+    ends it with the process group's timeout error instead of an endless wait), and adds the ``world`` slots of its own buffer in rank order (``magi_swiglu_sum_slots_bf16``): deterministic, and the partial
+    products cross NVLink while the tensor cores are still busy with later tiles instead of in a collective afterwards.
+    Consecutive calls alternate between the two sets, so one barrier per call is enough: a peer can only start
+    overwriting set s two calls later, which needs the barrier of the call in between, which this rank enters after
+    its sum over set s.  Collective: all ranks of ``group`` construct it and call it in the same order.
+    """
+
+    _active: "PeerScatterReducer | None" = None  # whose destinations the library's two sets currently describe
+
+    def __init__(self, m: int, n_out: int, group=None, device: torch.device | None = None):
+        # plain peer stores only: never bind the buffers to an NVLink multicast object
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if m % (self.world * 32) or n_out % 64:
+            raise ValueError(f"peer scatter needs M ({m}) to be a multiple of {self.world * 32} and the output width "
+                             f"({n_out}) a multiple of 64")
+        self.m, self.n_out, self.rows = m, n_out, m // self.world
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        self.recv = symm_mem.empty((2, self.world, self.rows, n_out), dtype=torch.bfloat16, device=self.device)
+        self.handle = symm_mem.rendezvous(self.recv, self.group)
+        self._token = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.step = 0
+
+    def _activate(self) -> None:
+        if PeerScatterReducer._active is self:
+            return
+        from .ops import scatter_setup
+
+        torch.cuda.current_stream(self.device).synchronize()  # no scattered GEMM may be running on the old sets
+        slot_bytes = self.rows * self.n_out * 2
+        bases = [int(p) for p in self.handle.buffer_ptrs]
+        for dest_set in (0, 1):
+            scatter_setup(dest_set, [bases[o] + (dest_set * self.world + self.rank) * slot_bytes for o in range(self.world)],
+                          self.rows, self.n_out, device=self.device.index)
+        PeerScatterReducer._active = self
+
+    def linear_reduce_scatter(self, h: torch.Tensor, w_down: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """Rows ``[rank * M/world, (rank + 1) * M/world)`` of ``sum over ranks of h_r @ w_down_r.T``."""
+        from .ops import gemm_nt_scatter, sum_slots
+
+        if h.shape[0] != self.m or w_down.shape[0] != self.n_out:
+            raise ValueError(f"built for [{self.m}, *] x [{self.n_out}, *], got {tuple(h.shape)} x {tuple(w_down.shape)}")
+        self._activate()
+        dest_set = self.step & 1
+        self.step += 1
+        gemm_nt_scatter(h, w_down, dest_set)
+        dist.all_reduce(self._token, group=self.group)  # every rank's stores into every buffer have completed
+        return sum_slots(self.recv[dest_set], out)
+
+
 class TensorParallelSwiGLUMLP(torch.nn.Module):
     """Full SwiGLU MLP over ``world`` ranks: fused column-parallel gate/up, row-parallel down, one reduction.
 
@@ -81,7 +146,9 @@ class TensorParallelSwiGLUMLP(torch.nn.Module):
     ``reduce``: ``"all_reduce"`` (every rank gets the whole ``[M, K]`` result, fairscale's ``RowParallelLinear`` of
     example/training/llama3.py:169) or ``"reduce_scatter"`` (each rank keeps the rows ``owned_rows(M)`` of the sum —
     half the bytes on the links; the next layer all-gathers them or works row-sharded).  With reduce-scatter every
-    slice's row count must be a multiple of ``world``.
+    slice's row count must be a multiple of ``world``.  ``"peer_scatter"`` gives the same rows with no collective
+    kernel at all: the down projection's epilogue stores each row block into its owner's memory
+    (``PeerScatterReducer``; ``chunks`` must be 1, M a multiple of ``32 * world``, the output width of 64).
 
     ``down_fn(h, w_down)`` returns the partial down projection; if it has a true ``supports_out`` attribute it is
     called as ``down_fn(h, w_down, out=...)`` and writes straight into the result (``gemm_nt_out``).
@@ -91,8 +158,11 @@ class TensorParallelSwiGLUMLP(torch.nn.Module):
                  group=None, chunks: int = 1, swiglu_fn: Callable | None = None, down_fn: Callable | None = None,
                  reduce: str = "all_reduce"):
         super().__init__()
-        if reduce not in ("all_reduce", "reduce_scatter"):
-            raise ValueError(f"reduce must be 'all_reduce' or 'reduce_scatter', got {reduce!r}")
+        if reduce not in ("all_reduce", "reduce_scatter", "peer_scatter"):
+            raise ValueError(f"reduce must be 'all_reduce', 'reduce_scatter' or 'peer_scatter', got {reduce!r}")
+        if reduce == "peer_scatter" and max(1, int(chunks)) != 1:
+            raise ValueError("peer_scatter overlaps the transfer inside the kernel; chunks must be 1")
+        self._peer: dict[int, PeerScatterReducer] = {}
         self.rank, self.world, self.group, self.chunks = rank, world, group, max(1, int(chunks))
         self.reduce = reduce
         self._down = down_fn  # (h [m, N/P], w_down [K_out, N/P]) -> [m, K_out]; None = library GEMM (torch.matmul)
@@ -123,7 +193,12 @@ class TensorParallelSwiGLUMLP(torch.nn.Module):
         lead = x.shape[:-1]
         x2 = x.reshape(-1, x.shape[-1])
         m, k_out = x2.shape[0], self.w_down.shape[0]
-        scatter = self.reduce == "reduce_scatter" and self.world > 1
+        if self.reduce == "peer_scatter" and self.world > 1:
+            red = self._peer.get(m)
+            if red is None:
+                red = self._peer[m] = PeerScatterReducer(m, k_out, self.group, x.device)
+            return red.linear_reduce_scatter(self.gate_up(x2), self.w_down)
+        scatter = self.reduce in ("reduce_scatter", "peer_scatter") and self.world > 1
         slices = self._slices(m)
         if scatter and any((hi - lo) % self.world for lo, hi in slices):
             raise ValueError(f"reduce_scatter needs every row slice to be a multiple of {self.world} rows "

@@ -837,8 +837,11 @@ def main():
                     alt = run_mlp_block(b, mb, sub_steps, sub_warmup, 1, "reduce_scatter", args.down)
                     subs[name]["reduce_scatter"] = {k: alt[k] for k in ("ms_per_step", "value", "unit", "chunks", "parity")}
                     if not args.no_peer_scatter:  # ... and with the reduce-scatter's transfer fused into the down projection
-                        alt = run_mlp_block(b, mb, sub_steps, sub_warmup, 1, "peer_scatter", "own")
-                        subs[name]["peer_scatter"] = {k: alt[k] for k in ("ms_per_step", "value", "unit", "parallelism", "parity")}
+                        try:
+                            alt = run_mlp_block(b, mb, sub_steps, sub_warmup, 1, "peer_scatter", "own")
+                            subs[name]["peer_scatter"] = {k: alt[k] for k in ("ms_per_step", "value", "unit", "parallelism", "parity")}
+                        except (RuntimeError, ValueError, ImportError) as exc:  # e.g. no symmetric memory on this machine
+                            subs[name]["peer_scatter"] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
                 continue
             sM, sK, sN, _, _ = WORKLOADS[name]
             xs, ws = make_inputs_cuda(sM, sK, sN, dev, seed=0)

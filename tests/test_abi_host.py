@@ -180,6 +180,33 @@ def test_other_entry_points_reject_bad_arguments_on_the_host(lib):
     assert bwd(b, b, b, b, 8, 8, 8, 8, 8, 8, 16, 1000, None) == -5
 
 
+def test_scatter_entry_points_reject_bad_arguments_on_the_host(lib):
+    """The scattered down projection and the slot sum validate before any device is touched."""
+    buf = (ctypes.c_char * 8192)()
+    b = ctypes.addressof(buf)
+    b += (-b) % 16
+    setup, gemm, sums = lib.magi_swiglu_scatter_setup, lib.magi_swiglu_gemm_nt_bf16_scatter, lib.magi_swiglu_sum_slots_bf16
+    dst = (ctypes.c_void_p * 9)(*([b] * 9))
+    assert setup(0, 2, dst, 2, 64, 128, 128) == -4 and "set" in _loader.last_error()
+    assert setup(0, 0, dst, 0, 64, 128, 128) == -2
+    assert setup(0, 0, dst, 9, 64, 128, 128) == -2 and "owners" in _loader.last_error()
+    assert setup(0, 0, None, 2, 64, 128, 128) == -1
+    assert setup(0, 0, dst, 2, 48, 128, 128) == -2 and "multiple of 32" in _loader.last_error()
+    assert setup(0, 0, dst, 2, 64, 96, 96) == -2       # N % 64
+    assert setup(0, 0, dst, 2, 64, 128, 64) == -2      # ldc < N
+    assert setup(1000, 0, dst, 2, 64, 128, 128) == -5
+    assert gemm(b, b, 3, 128, 128, 64, 64, 64, 0, None, None, 0) == -4
+    assert gemm(b, b, 0, 128, 128, 64, 64, 64, 1000, None, None, 0) == -5
+    assert gemm(b, b, 0, 128, 128, 64, 64, 64, 0, None, None, 0) == -4 and "not been set up" in _loader.last_error()
+    assert sums(None, b, 2, 64, 64, 0, None) == -1
+    assert sums(b, b, 0, 64, 64, 0, None) == -2
+    assert sums(b, b, 2, 64, 60, 0, None) == -2        # n % 8
+    assert sums(b, b, 2, 32, 64, 0, None) == -2        # slots overlap
+    assert sums(b + 8, b, 2, 64, 64, 0, None) == -3
+    assert sums(b, b, 2, 64, 0, 0, None) == 0          # nothing to add
+    assert sums(b, b, 2, 64, 64, 1000, None) == -5
+
+
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_loader, "_lib", None)
     monkeypatch.setattr(_loader, "LIB_PATH", tmp_path / "libmagi_swiglu.so")

@@ -110,7 +110,7 @@ struct KArgs {
   // parks its fp32 partial sums in `ws`; swiglu_splitk_reduce_kernel adds them in split order and writes Y.
   // k_splits == 1: no scratch is touched.
   int k_splits, kb_per_split;
-  float* ws;  // [tile][split][M rows][2*block_n] fp32
+  float* ws;  // [tile][split][lane quarter < ceil(M/32)][chunk][gate float4s | up float4s][32 lanes] fp32
   // Stream-K (tile schedules, with scratch): tiles [0, sk_first_tile) are whole-tile work items dealt round-robin
   // in full waves; the K-steps of the remaining tiles (one full wave plus the partial one) form one iteration space
   // cut into equal ranges, one per CTA (pair), so the last wave is never mostly empty.  A range that ends inside a
@@ -840,12 +840,14 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       const float out_inv_scale = 1.0f / out_gs;
 
       if (kCtas == 1 && a.k_splits > 1) {
-        // ---- split-K: park this CTA's fp32 partial sums; swiglu_splitk_reduce_kernel finishes the tile
+        // ---- split-K: park this CTA's fp32 partial sums; swiglu_splitk_reduce_kernel finishes the tile.
+        // Scratch of one (tile, split): [lane quarter < ceil(M/32)][chunk][gate float4s, then up float4s][32 lanes]:
+        // lane l's k-th float4 of a chunk sits next to lane l+1's, so each store of a warp is one 512-byte piece.
         const int slot = warp - 4;
-        const int ws_ld = 2 * a.block_n;
-        const int r_loc = q * 32 + lane;
-        float* part = a.ws + ((size_t)(t * a.k_splits + zsplit) * a.M + r_loc) * ws_ld;
+        const int quarters = (a.M + 31) >> 5;
         auto chunk_w = [&](int c) { return (c + 32 <= a.block_n) ? 32 : ((c + 16 == a.block_n) ? 16 : 0); };
+        uint4* part = reinterpret_cast<uint4*>(a.ws) +
+                      ((size_t)(t * a.k_splits + zsplit) * quarters + q) * (size_t)(a.block_n / 2) * 32 + lane;
         uint32_t g[32], u[32];
         bool released = false;
         for (int c = 32 * (slot >> 2), w = chunk_w(c); w; c += 64, w = chunk_w(c)) {
@@ -866,12 +868,13 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
             released = true;
           }
           if (row_ok) {
+            uint4* dst = part + (size_t)(c / 32) * 16 * 32;  // every chunk before this one is 32 columns wide
+            const int nv = w / 4;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              if (4 * j < w) {
-                *reinterpret_cast<uint4*>(part + c + 4 * j) = make_uint4(g[4 * j], g[4 * j + 1], g[4 * j + 2], g[4 * j + 3]);
-                *reinterpret_cast<uint4*>(part + a.block_n + c + 4 * j) =
-                    make_uint4(u[4 * j], u[4 * j + 1], u[4 * j + 2], u[4 * j + 3]);
+              if (j < nv) {
+                __stcg(dst + j * 32, make_uint4(g[4 * j], g[4 * j + 1], g[4 * j + 2], g[4 * j + 3]));
+                __stcg(dst + (nv + j) * 32, make_uint4(u[4 * j], u[4 * j + 1], u[4 * j + 2], u[4 * j + 3]));
               }
             }
           }
@@ -1143,35 +1146,43 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
 }
 
 // Second step of a split-K launch: Y[row, tile columns] = silu(sum_z g_z) * (sum_z u_z), partial sums added in
-// split order (bit-identical from run to run).  One thread per 8 output columns, coalesced along a row.
+// split order (bit-identical from run to run).  One thread per row and 8 output columns; consecutive threads take
+// consecutive rows of a lane quarter, which are consecutive float4s of the scratch (see the parking code).
 __global__ void __launch_bounds__(256)
 swiglu_splitk_reduce_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ y, int M, int N, long long ldy,
                             int block_n, int num_n_tiles, int k_splits, const float* __restrict__ row_scale) {
   const int groups = block_n / 8;
-  const long long total = (long long)num_n_tiles * M * groups;
+  const int quarters = (M + 31) >> 5;
+  const long long total = (long long)num_n_tiles * quarters * groups * 32;
+  const size_t quarter_f4 = (size_t)(block_n / 2) * 32;      // float4s of one (tile, split, quarter)
+  const size_t z_stride = (size_t)quarters * quarter_f4;      // ... of one (tile, split)
   const uint64_t policy = l2_policy_evict_first();
   asm volatile("griddepcontrol.wait;" ::: "memory");  // the partial sums of the tile kernel are complete and visible
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
-    const int cg = (int)(i % groups);
-    const int row = (int)((i / groups) % M);
-    const int t = (int)(i / ((long long)groups * M));
+    const int lane = (int)(i & 31);
+    const int cg = (int)((i >> 5) % groups);
+    const int q = (int)((i / (32LL * groups)) % quarters);
+    const int t = (int)(i / (32LL * groups * quarters));
+    const int row = q * 32 + lane;
     const int col = t * block_n + cg * 8;
-    if (col >= N) continue;  // N is a multiple of 8: a group is inside or outside as a whole
-    const float* p = ws + (((size_t)t * k_splits) * M + row) * (2 * block_n) + cg * 8;
+    if (row >= M || col >= N) continue;  // N is a multiple of 8: a group is inside or outside as a whole
+    const int ci = cg >> 2, jp = cg & 3;                       // 32-column chunk and pair of float4s inside it
+    const int nv = (block_n - 32 * ci >= 32) ? 8 : 4;          // float4s of gate (and of up) in this chunk
+    const float4* p = reinterpret_cast<const float4*>(ws) + ((size_t)t * k_splits * quarters + q) * quarter_f4 +
+                      (size_t)ci * 16 * 32 + (size_t)(2 * jp) * 32 + lane;
     float g[8] = {0, 0, 0, 0, 0, 0, 0, 0}, u[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    const size_t z_stride = (size_t)M * 2 * block_n;
     for (int z0 = 0; z0 < k_splits; z0 += 4, p += 4 * z_stride) {
       // four splits' loads are issued before the first add so their latencies overlap; the adds keep split order
       float4 v[4][4];
 #pragma unroll
       for (int zz = 0; zz < 4; ++zz) {
         if (z0 + zz < k_splits) {
-          const float* q = p + zz * z_stride;
-          v[zz][0] = __ldcg(reinterpret_cast<const float4*>(q));
-          v[zz][1] = __ldcg(reinterpret_cast<const float4*>(q + 4));
-          v[zz][2] = __ldcg(reinterpret_cast<const float4*>(q + block_n));
-          v[zz][3] = __ldcg(reinterpret_cast<const float4*>(q + block_n + 4));
+          const float4* r = p + zz * z_stride;
+          v[zz][0] = __ldcg(r);
+          v[zz][1] = __ldcg(r + 32);
+          v[zz][2] = __ldcg(r + nv * 32);
+          v[zz][3] = __ldcg(r + nv * 32 + 32);
         }
       }
 #pragma unroll

@@ -76,8 +76,11 @@ static inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
 constexpr int64_t kWorkspaceCap = 64LL << 20;  // never plan for more scratch than this
 
-// Scratch bytes of a split-K plan: per tile k_splits x M x 2*block_n fp32 partial sums.
-static inline int64_t splitk_bytes(int64_t tiles, int64_t z, int64_t M, int64_t bn) { return tiles * z * M * 2 * bn * 4; }
+// Scratch bytes of a split-K plan: per tile k_splits x (M rounded up to whole warps of 32 rows) x 2*block_n fp32
+// partial sums.
+static inline int64_t splitk_bytes(int64_t tiles, int64_t z, int64_t M, int64_t bn) {
+  return tiles * z * ((M + 31) / 32 * 32) * 2 * bn * 4;
+}
 
 // Estimated time (ns) of the STREAM schedule: every CTA runs kb_per_split K-steps; a K-step costs at least
 // ~530 ns of MMA issue (measured) and otherwise its share of HBM bandwidth; split-K adds a reduction.

@@ -321,7 +321,7 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
     e = cudaGetLastError();
     if (e != cudaSuccess) return fail_cuda(e, "launch of swiglu_tc_kernel<1>");
     if (p.k_splits > 1) {
-      const long long work = (long long)p.num_n_tiles * M * (p.block_n / 8);
+      const long long work = (long long)p.num_n_tiles * ((M + 31) / 32) * 32 * (p.block_n / 8);
       const int blocks = (int)((work + 255) / 256 < 4LL * di->sm_count ? (work + 255) / 256 : 4LL * di->sm_count);
       // scheduled while the tile kernel drains (programmatic dependent launch); it waits for that grid itself
       cudaLaunchConfig_t rc_cfg = {};

@@ -55,6 +55,22 @@ def test_single_rank_modules_match_reference_mlp():
     assert torch.allclose(got.float(), ref.float(), rtol=2e-2, atol=2e-2 * ref.float().abs().max().item())
 
 
+def test_peer_scatter_mode_argument_rules():
+    """reduce="peer_scatter": one chunk only; on one rank there is nothing to exchange and the plain path runs; its
+    rows of the result are the ones NCCL's reduce-scatter would leave on the rank."""
+    x, w, wd = make_inputs(64, 64, 128, seed=6, with_down=True)
+    with pytest.raises(ValueError):
+        TensorParallelSwiGLUMLP(w, wd, chunks=2, reduce="peer_scatter", swiglu_fn=_oracle_fn)
+    with pytest.raises(ValueError):
+        TensorParallelSwiGLUMLP(w, wd, reduce="all_gather", swiglu_fn=_oracle_fn)
+    one = TensorParallelSwiGLUMLP(w, wd, reduce="peer_scatter", swiglu_fn=_oracle_fn)
+    ref = reference_mlp(x, w, wd)
+    assert torch.allclose(one(x).float(), ref.float(), rtol=2e-2, atol=2e-2 * ref.float().abs().max().item())
+    a = TensorParallelSwiGLUMLP(w, wd, rank=1, world=4, reduce="peer_scatter", swiglu_fn=_oracle_fn).owned_rows(64)
+    b = TensorParallelSwiGLUMLP(w, wd, rank=1, world=4, reduce="reduce_scatter", swiglu_fn=_oracle_fn).owned_rows(64)
+    assert torch.equal(a, b) and torch.equal(a, torch.arange(16, 32))
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

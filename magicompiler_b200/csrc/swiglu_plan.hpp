@@ -287,10 +287,13 @@ static int make_plan(int64_t M, int64_t N, int64_t K, int variant, int block_n, 
   if ((int64_t)p->num_m_tiles * p->num_n_tiles > 0x7fffffffLL) return fail(MAGI_SWIGLU_ERR_SHAPE, "too many tiles");
   p->tiles = p->num_m_tiles * p->num_n_tiles;
   if (group_m <= 0) {
-    // band height: keep one band of X rows (group_m units x K) around 32 MB so it stays in L2 while W streams by
+    // band height: keep one band of X rows (group_m units x K) around 32 MB so it stays in L2 while W streams by.
+    // With a long K no band fits anyway and what is shared is the K block the CTAs of a wave are working on at the
+    // same time, which wants the wave (74 pair tiles) close to square: at least 12 row units (measured: 4 -> 16 row
+    // units at K = 28672 is +6 % through a higher clock under the power cap; the cycle count does not change).
     const int64_t unit_bytes = (int64_t)kBM * pair * K * 2;
     int64_t g = (32LL << 20) / (unit_bytes > 0 ? unit_bytes : 1);
-    group_m = (int)(g < 4 ? 4 : (g > 64 ? 64 : g));
+    group_m = (int)(g < 12 ? 12 : (g > 64 ? 64 : g));
   }
   p->group_m = group_m;
   p->k_splits = k_splits;

@@ -102,7 +102,7 @@ def test_nvfp4_output_against_vllm_silu_and_mul_nvfp4_quant():
     kernel quantises its fp32 accumulators directly, so most scale bytes and codes are identical and the rest are
     neighbours.  Scales are compared in vLLM's own layout (128 x 4 tiles, int32-packed)."""
     try:
-        import vllm._C  # noqa: F401
+        import vllm._custom_ops  # noqa: F401  (loads every compiled extension vLLM ships, the nvfp4 ops among them)
     except Exception as exc:  # not installed, or built without this device
         pytest.skip(f"vLLM compiled ops unavailable: {exc}")
     if not hasattr(torch.ops._C, "silu_and_mul_nvfp4_quant"):

@@ -506,13 +506,15 @@ def run_mlp_block(b, mb, steps, warmup, chunks, reduce, down):
         "down_projection": "magi_swiglu_gemm_nt_bf16 (own tile kernel)" if down == "own" else "torch.matmul (library GEMM)",
         "parallelism": (f"tp{b.world}: column-parallel gate/up, row-parallel down, " +
                         ("row blocks of the partial products stored by the down projection's epilogue into their owner's "
-                         "memory over NVLink (no collective kernel), barrier, slot sum" if reduce == "peer_scatter"
-                         else f"NCCL {reduce.replace('_', '-')}") + f" of [{M},{K}] bf16") if b.world > 1 else "1 GPU: no reduction",
+                         "memory over NVLink (no collective kernel), barrier, slot sum" +
+                         (" stored into every GPU's result, barrier" if reduce == "peer_all_reduce" else "")
+                         if reduce in ("peer_scatter", "peer_all_reduce") else f"NCCL {reduce.replace('_', '-')}") + f" of [{M},{K}] bf16") if b.world > 1 else "1 GPU: no reduction",
         "l2": "inputs (1.7 GB) larger than L2, back-to-back steps",
         "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s", "frac": per_gpu / peak,
                      "nominal_frac": per_gpu / 2250.0, "algorithmic_flops": flops / b.world, "traffic": None,
                      "peak_kind": f"{b.peak_kind} cuBLAS bf16 sustained (kernels timed inside a long step)"},
-        "gpu_launches": steps * (3 if reduce == "peer_scatter" and b.world > 1 else chunks * (2 if down == "own" else 1)),
+        "gpu_launches": steps * (3 if reduce in ("peer_scatter", "peer_all_reduce") and b.world > 1
+                                 else chunks * (2 if down == "own" else 1)),
         "parity": parity,
     }
     del mlp, x, w, wd
@@ -649,7 +651,7 @@ def main():
     ap.add_argument("--stages", type=int, default=0)
     ap.add_argument("--group-m", type=int, default=0)
     ap.add_argument("--chunks", type=int, default=4, help="mlp_block: row chunks whose reduction overlaps the next chunk")
-    ap.add_argument("--reduce", default="all_reduce", choices=["all_reduce", "reduce_scatter", "peer_scatter"],
+    ap.add_argument("--reduce", default="all_reduce", choices=["all_reduce", "reduce_scatter", "peer_scatter", "peer_all_reduce"],
                     help="mlp_block: all ranks get the whole result, or each keeps its rows of the sum")
     ap.add_argument("--down", default="own", choices=["own", "library"], help="mlp_block: kernel of the down projection")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -840,8 +842,11 @@ def main():
                         try:
                             alt = run_mlp_block(b, mb, sub_steps, sub_warmup, 1, "peer_scatter", "own")
                             subs[name]["peer_scatter"] = {k: alt[k] for k in ("ms_per_step", "value", "unit", "parallelism", "parity")}
+                            alt = run_mlp_block(b, mb, sub_steps, sub_warmup, 1, "peer_all_reduce", "own")
+                            subs[name]["peer_all_reduce"] = {k: alt[k] for k in ("ms_per_step", "value", "unit", "parallelism", "parity")}
                         except (RuntimeError, ValueError, ImportError) as exc:  # e.g. no symmetric memory on this machine
-                            subs[name]["peer_scatter"] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
+                            subs[name].setdefault("peer_scatter", {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"})
+                            subs[name].setdefault("peer_all_reduce", {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"})
                 continue
             sM, sK, sN, _, _ = WORKLOADS[name]
             xs, ws = make_inputs_cuda(sM, sK, sN, dev, seed=0)
@@ -850,7 +855,8 @@ def main():
             subs[name] = time_op_workload(b, mb, name, xs, ws, sub_steps, sub_warmup)[0]
             del xs, ws
     ok = head["parity"]["ok"] and all(r["parity"]["ok"] and r.get("reduce_scatter", {}).get("parity", {}).get("ok", True)
-                                      and r.get("peer_scatter", {}).get("parity", {}).get("ok", True) for r in subs.values())
+                                      and r.get("peer_scatter", {}).get("parity", {}).get("ok", True)
+                                      and r.get("peer_all_reduce", {}).get("parity", {}).get("ok", True) for r in subs.values())
 
     if rank != 0:
         if world > 1:

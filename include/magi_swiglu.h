@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define MAGI_SWIGLU_ABI_VERSION 5
+#define MAGI_SWIGLU_ABI_VERSION 6
 
 /* variant selector of magi_swiglu_forward_bf16 */
 #define MAGI_SWIGLU_VARIANT_AUTO   0  /* M <= 128 -> STREAM, else MMA2           */
@@ -206,6 +206,14 @@ int magi_swiglu_gemm_nt_bf16_scatter(const void* a, const void* b, int set, int6
  * (NCCL's reduction kernel does this inside the all-reduce). */
 int magi_swiglu_sum_slots_bf16(const void* src, void* out, int slots, int64_t slot_stride, int64_t n, int device,
                                void* cuda_stream);
+
+/* The same sum stored to n_dst (<= 8) destinations at once: dst[d] is where this GPU's block of the result lives in
+ * GPU d's copy of the full result (this GPU's own copy included; peers' memory mapped into this process).  With it the
+ * scattered down projection ends as an ALL-reduce: every GPU sums its own rows and writes them into every GPU's
+ * result with plain coalesced 16-byte stores over NVLink; a second barrier across the GPUs then makes the whole
+ * result readable everywhere.  It has no counterpart in the reference (NCCL's all-gather phase does this). */
+int magi_swiglu_sum_slots_bf16_bcast(const void* src, void* const* dst, int n_dst, int slots, int64_t slot_stride,
+                                     int64_t n, int device, void* cuda_stream);
 
 /* The same plain GEMM with either operand stored the other way round, C[M,N] = op(A) · op(B)^T in bf16:
  *   a_layout 0: A is [M, K] (row stride lda);  1: A is stored [K, M] (its transpose, row stride lda, M % 8 == 0);

@@ -1208,10 +1208,16 @@ swiglu_splitk_reduce_kernel(const float* __restrict__ ws, __nv_bfloat16* __restr
 
 // out[i] = sum over slots of src[slot * slot_stride + i], added in slot order in fp32 and rounded once to bf16: the
 // last step of a scattered row-parallel GEMM, where slot r holds what GPU r's epilogue wrote for this GPU's rows.
+// The sums are stored to every destination in dst (one local buffer for a reduce-scatter; this GPU's block of the
+// result in every GPU's memory, peers included, for an all-reduce: plain coalesced 16-byte stores over NVLink).
 // Element-wise, HBM-bound; 8 elements per thread with 16-byte accesses (n % 8 == 0).
+struct SumDst {  // where the sums go: one buffer, or the same place in the memory of every GPU of the group
+  __nv_bfloat16* p[kMaxScatterOwners];
+  int n;
+};
 __global__ void __launch_bounds__(256)
-swiglu_sum_slots_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ out, int slots,
-                        long long slot_stride, long long n) {
+swiglu_sum_slots_kernel(const __nv_bfloat16* __restrict__ src, const SumDst dst, int slots, long long slot_stride,
+                        long long n) {
   const long long groups = n / 8;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < groups; i += (long long)gridDim.x * blockDim.x) {
     float acc[8];
@@ -1231,7 +1237,7 @@ swiglu_sum_slots_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __
     __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
     for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-    *reinterpret_cast<uint4*>(out + 8 * i) = o;
+    for (int d = 0; d < dst.n; ++d) *reinterpret_cast<uint4*>(dst.p[d] + 8 * i) = o;
   }
 }
 

@@ -620,15 +620,26 @@ int magi_swiglu_gemm_nt_bf16_scatter(const void* a, const void* b, int set, int6
                             0, 0, ss.rows, set);
 }
 
-int magi_swiglu_sum_slots_bf16(const void* src, void* out, int slots, int64_t slot_stride, int64_t n, int device,
-                               void* cuda_stream) {
+static int sum_slots_impl(const void* src, void* const* dst, int n_dst, int slots, int64_t slot_stride, int64_t n, int device,
+                          void* cuda_stream) {
   magi::g_err[0] = 0;
+  if (n_dst < 1 || n_dst > magi::kMaxScatterOwners)
+    return magi::fail(MAGI_SWIGLU_ERR_SHAPE, "1..%d destinations (got %d)", magi::kMaxScatterOwners, n_dst);
+  if (!src || !dst) return magi::fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
+  magi::SumDst sd;
+  memset(&sd, 0, sizeof(sd));
+  sd.n = n_dst;
+  uintptr_t bits = (uintptr_t)src;
+  for (int d = 0; d < n_dst; ++d) {
+    if (!dst[d]) return magi::fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
+    sd.p[d] = static_cast<__nv_bfloat16*>(dst[d]);
+    bits |= (uintptr_t)dst[d];
+  }
   if (n == 0) return 0;
-  if (!src || !out) return magi::fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
   if (slots < 1 || slots > 64 || n < 0 || n % 8 != 0 || slot_stride < n || slot_stride % 8 != 0)
     return magi::fail(MAGI_SWIGLU_ERR_SHAPE, "bad slots=%d n=%lld slot_stride=%lld (n and the stride must be multiples of 8)", slots,
                       (long long)n, (long long)slot_stride);
-  if (((uintptr_t)src | (uintptr_t)out) & 15u) return magi::fail(MAGI_SWIGLU_ERR_ALIGN, "pointers must be 16-byte aligned");
+  if (bits & 15u) return magi::fail(MAGI_SWIGLU_ERR_ALIGN, "pointers must be 16-byte aligned");
   const magi::DeviceInfo* di = magi::device_info(device);
   if (!di) return magi::fail(MAGI_SWIGLU_ERR_DEVICE, "device %d is not available", device);
   magi::DeviceGuard guard;
@@ -637,9 +648,24 @@ int magi_swiglu_sum_slots_bf16(const void* src, void* out, int slots, int64_t sl
   const long long want = (n / 8 + 255) / 256;
   const int blocks = (int)(want < 16LL * di->sm_count ? want : 16LL * di->sm_count);
   magi::swiglu_sum_slots_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
-      static_cast<const __nv_bfloat16*>(src), static_cast<__nv_bfloat16*>(out), slots, (long long)slot_stride, (long long)n);
+      static_cast<const __nv_bfloat16*>(src), sd, slots, (long long)slot_stride, (long long)n);
   e = cudaGetLastError();
   return e == cudaSuccess ? 0 : magi::fail_cuda(e, "launch of swiglu_sum_slots_kernel");
+}
+
+int magi_swiglu_sum_slots_bf16(const void* src, void* out, int slots, int64_t slot_stride, int64_t n, int device,
+                               void* cuda_stream) {
+  void* const one[1] = {out};
+  if (!out) {
+    magi::g_err[0] = 0;
+    return magi::fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
+  }
+  return sum_slots_impl(src, one, 1, slots, slot_stride, n, device, cuda_stream);
+}
+
+int magi_swiglu_sum_slots_bf16_bcast(const void* src, void* const* dst, int n_dst, int slots, int64_t slot_stride, int64_t n,
+                                     int device, void* cuda_stream) {
+  return sum_slots_impl(src, dst, n_dst, slots, slot_stride, n, device, cuda_stream);
 }
 
 int magi_swiglu_gemm_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,

@@ -274,6 +274,21 @@ def sum_slots(src: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tenso
     return out
 
 
+def sum_slots_bcast(src: torch.Tensor, dst_ptrs: list[int]) -> None:
+    """``sum_slots`` stored to every address in ``dst_ptrs`` (``magi_swiglu_sum_slots_bf16_bcast``): the same block of
+    the result in the memory of every GPU of a group, peers' memory mapped into this process."""
+    if src.dtype != torch.bfloat16 or not src.is_cuda or not src.is_contiguous() or src.dim() < 2:
+        raise TypeError("sum_slots_bcast takes a contiguous bf16 CUDA tensor [slots, ...]")
+    slots, n = src.shape[0], src[0].numel()
+    arr = (ctypes.c_void_p * len(dst_ptrs))(*dst_ptrs)
+    dev = src.device.index if src.device.index is not None else torch.cuda.current_device()
+    rc = _loader.load_library().magi_swiglu_sum_slots_bf16_bcast(src.data_ptr(), arr, len(dst_ptrs), slots, n, n, dev,
+                                                                  torch.cuda.current_stream(src.device).cuda_stream)
+    if rc != 0:
+        msg = f"magi_swiglu_sum_slots_bf16_bcast failed ({rc}): {_loader.last_error()}"
+        raise (ValueError(msg) if rc < 0 else RuntimeError(msg))
+
+
 @magi_register_custom_op(name=GEMM_NT_OP_NAME, mutates_args=(),
                          infer_output_meta_fn=lambda a, b: a.new_empty((*a.shape[:-1], b.shape[0])),
                          is_compute_sensitive=True)

@@ -107,6 +107,8 @@ class PeerScatterReducer:
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         self.recv = symm_mem.empty((2, self.world, self.rows, n_out), dtype=torch.bfloat16, device=self.device)
         self.handle = symm_mem.rendezvous(self.recv, self.group)
+        self.full = None  # [2 sets][M][n_out] in symmetric memory, made by the first linear_all_reduce
+        self._full_handle = None
         self._token = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.step = 0
 
@@ -136,6 +138,30 @@ class PeerScatterReducer:
         dist.all_reduce(self._token, group=self.group)  # every rank's stores into every buffer have completed
         return sum_slots(self.recv[dest_set], out)
 
+    def linear_all_reduce(self, h: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
+        """The whole ``sum over ranks of h_r @ w_down_r.T`` on every rank: as ``linear_reduce_scatter``, but each rank's
+        slot sum is stored into every rank's copy of the result (peer stores from the sum kernel) and a second barrier
+        makes the whole result readable.  The returned ``[M, n_out]`` tensor is a view of one of two result buffers in
+        symmetric memory: it is overwritten by the call after the next one."""
+        from .ops import gemm_nt_scatter, sum_slots_bcast
+
+        if h.shape[0] != self.m or w_down.shape[0] != self.n_out:
+            raise ValueError(f"built for [{self.m}, *] x [{self.n_out}, *], got {tuple(h.shape)} x {tuple(w_down.shape)}")
+        if self.full is None:  # collective, like the constructor
+            import torch.distributed._symmetric_memory as symm_mem
+
+            self.full = symm_mem.empty((2, self.m, self.n_out), dtype=torch.bfloat16, device=self.device)
+            self._full_handle = symm_mem.rendezvous(self.full, self.group)
+        self._activate()
+        dest_set = self.step & 1
+        self.step += 1
+        gemm_nt_scatter(h, w_down, dest_set)
+        dist.all_reduce(self._token, group=self.group)  # every rank's partial products have arrived
+        block = (dest_set * self.m + self.rank * self.rows) * self.n_out * 2  # this rank's rows in a result buffer
+        sum_slots_bcast(self.recv[dest_set], [int(p) + block for p in self._full_handle.buffer_ptrs])
+        dist.all_reduce(self._token, group=self.group)  # every rank's rows have arrived in every result buffer
+        return self.full[dest_set]
+
 
 class TensorParallelSwiGLUMLP(torch.nn.Module):
     """Full SwiGLU MLP over ``world`` ranks: fused column-parallel gate/up, row-parallel down, one reduction.
@@ -149,6 +175,8 @@ class TensorParallelSwiGLUMLP(torch.nn.Module):
     slice's row count must be a multiple of ``world``.  ``"peer_scatter"`` gives the same rows with no collective
     kernel at all: the down projection's epilogue stores each row block into its owner's memory
     (``PeerScatterReducer``; ``chunks`` must be 1, M a multiple of ``32 * world``, the output width of 64).
+    ``"peer_all_reduce"`` continues from there to the whole result on every rank: each rank's sum kernel stores its rows
+    into every rank's result buffer; the returned tensor is overwritten by the call after the next one.
 
     ``down_fn(h, w_down)`` returns the partial down projection; if it has a true ``supports_out`` attribute it is
     called as ``down_fn(h, w_down, out=...)`` and writes straight into the result (``gemm_nt_out``).
@@ -158,10 +186,11 @@ class TensorParallelSwiGLUMLP(torch.nn.Module):
                  group=None, chunks: int = 1, swiglu_fn: Callable | None = None, down_fn: Callable | None = None,
                  reduce: str = "all_reduce"):
         super().__init__()
-        if reduce not in ("all_reduce", "reduce_scatter", "peer_scatter"):
-            raise ValueError(f"reduce must be 'all_reduce', 'reduce_scatter' or 'peer_scatter', got {reduce!r}")
-        if reduce == "peer_scatter" and max(1, int(chunks)) != 1:
-            raise ValueError("peer_scatter overlaps the transfer inside the kernel; chunks must be 1")
+        if reduce not in ("all_reduce", "reduce_scatter", "peer_scatter", "peer_all_reduce"):
+            raise ValueError("reduce must be 'all_reduce', 'reduce_scatter', 'peer_scatter' or 'peer_all_reduce', "
+                             f"got {reduce!r}")
+        if reduce in ("peer_scatter", "peer_all_reduce") and max(1, int(chunks)) != 1:
+            raise ValueError(f"{reduce} overlaps the transfer inside the kernel; chunks must be 1")
         self._peer: dict[int, PeerScatterReducer] = {}
         self.rank, self.world, self.group, self.chunks = rank, world, group, max(1, int(chunks))
         self.reduce = reduce
@@ -193,11 +222,13 @@ class TensorParallelSwiGLUMLP(torch.nn.Module):
         lead = x.shape[:-1]
         x2 = x.reshape(-1, x.shape[-1])
         m, k_out = x2.shape[0], self.w_down.shape[0]
-        if self.reduce == "peer_scatter" and self.world > 1:
+        if self.reduce in ("peer_scatter", "peer_all_reduce") and self.world > 1:
             red = self._peer.get(m)
             if red is None:
                 red = self._peer[m] = PeerScatterReducer(m, k_out, self.group, x.device)
-            return red.linear_reduce_scatter(self.gate_up(x2), self.w_down)
+            if self.reduce == "peer_scatter":
+                return red.linear_reduce_scatter(self.gate_up(x2), self.w_down)
+            return red.linear_all_reduce(self.gate_up(x2), self.w_down).view(*lead, k_out)
         scatter = self.reduce in ("reduce_scatter", "peer_scatter") and self.world > 1
         slices = self._slices(m)
         if scatter and any((hi - lo) % self.world for lo, hi in slices):

@@ -205,6 +205,12 @@ def test_scatter_entry_points_reject_bad_arguments_on_the_host(lib):
     assert sums(b + 8, b, 2, 64, 64, 0, None) == -3
     assert sums(b, b, 2, 64, 0, 0, None) == 0          # nothing to add
     assert sums(b, b, 2, 64, 64, 1000, None) == -5
+    bcast = lib.magi_swiglu_sum_slots_bf16_bcast
+    assert bcast(b, dst, 9, 2, 64, 64, 0, None) == -2 and "destinations" in _loader.last_error()
+    assert bcast(b, dst, 0, 2, 64, 64, 0, None) == -2
+    assert bcast(b, None, 2, 2, 64, 64, 0, None) == -1
+    assert bcast(b, dst, 2, 2, 64, 60, 0, None) == -2
+    assert bcast(b, dst, 8, 2, 64, 64, 1000, None) == -5
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

@@ -91,6 +91,19 @@ def _rank_peer_scatter(rank, world, port, q):
             ref = reference_mlp(xd, w.to(dev), wd.to(dev)).float()
             ok_ref &= tuple(z.shape) == (M // world, K)
             ok_ref &= bool(torch.allclose(z.float(), ref[rows], rtol=3e-2, atol=3e-2 * ref.abs().max().item()))
+        # ... and continued to an all-reduce: every rank's sum kernel stores its rows into every rank's result
+        full = mb.TensorParallelSwiGLUMLP(w, wd, rank, world, reduce="peer_all_reduce").to(dev)
+        for step in range(3):
+            x, _, _ = make_inputs(M, K, N, seed=40 + step, with_down=True)
+            xd = x.to(dev)
+            z = full(xd).clone()
+            partial = mb.gemm_nt(full.gate_up(xd), full.w_down)
+            parts = [torch.empty_like(partial) for _ in range(world)]
+            dist.all_gather(parts, partial)
+            acc = torch.zeros(M, K, dtype=torch.float32, device=dev)
+            for p in parts:
+                acc += p.float()
+            ok_exact &= tuple(z.shape) == (M, K) and bool(torch.equal(z, acc.to(torch.bfloat16)))
         torch.cuda.synchronize()
         q.put((rank, ok_exact, ok_ref, mb.device_status(rank)["code"]))
     except Exception as exc:  # report instead of leaving the parent to time out

@@ -70,3 +70,16 @@ def test_sum_slots_adds_in_fp32_in_slot_order(slots, shape):
     assert torch.equal(ops.sum_slots(src), acc.to(torch.bfloat16))
     out = torch.empty(shape, dtype=torch.bfloat16, device="cuda")
     assert ops.sum_slots(src, out) is out and torch.equal(out, acc.to(torch.bfloat16))
+
+
+def test_sum_slots_bcast_writes_the_same_sums_everywhere():
+    slots, shape = 4, (256, 512)
+    src = _rand(slots * shape[0], shape[1], 1.0, 8).view(slots, *shape).contiguous()
+    want = ops.sum_slots(src)
+    outs = [torch.full((shape[0] + 2, shape[1]), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(8)]
+    ops.sum_slots_bcast(src, [t[1:].data_ptr() for t in outs])
+    torch.cuda.synchronize()
+    for t in outs:
+        assert torch.equal(t[1:-1], want) and torch.isnan(t[0]).all() and torch.isnan(t[-1]).all()
+    with pytest.raises(ValueError):
+        ops.sum_slots_bcast(src, [t.data_ptr() for t in outs] + [outs[0].data_ptr()])  # nine destinations

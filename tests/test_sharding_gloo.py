@@ -62,6 +62,8 @@ def test_peer_scatter_mode_argument_rules():
     with pytest.raises(ValueError):
         TensorParallelSwiGLUMLP(w, wd, chunks=2, reduce="peer_scatter", swiglu_fn=_oracle_fn)
     with pytest.raises(ValueError):
+        TensorParallelSwiGLUMLP(w, wd, chunks=2, reduce="peer_all_reduce", swiglu_fn=_oracle_fn)
+    with pytest.raises(ValueError):
         TensorParallelSwiGLUMLP(w, wd, reduce="all_gather", swiglu_fn=_oracle_fn)
     one = TensorParallelSwiGLUMLP(w, wd, reduce="peer_scatter", swiglu_fn=_oracle_fn)
     ref = reference_mlp(x, w, wd)

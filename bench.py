@@ -461,7 +461,7 @@ def run_mlp_block(b, mb, steps, warmup, chunks, reduce, down):
     (NCCL), optionally chunked so the reduce of chunk i overlaps the GEMMs of chunk i+1."""
     M, K, N, _, desc = WORKLOADS["mlp_block"]
     x, w, wd = make_inputs_cuda(M, K, N, b.dev, seed=0, with_down=True)
-    mlp = mb.TensorParallelSwiGLUMLP(w, wd, b.rank, b.world, chunks=chunks, reduce=reduce,
+    mlp = mb.TensorParallelSwiGLUMLP(w, wd, b.rank, b.world, chunks=chunks, reduce=reduce, borrow_result=True,
                                      down_fn=mb.gemm_nt_out if down == "own" else None).to(b.dev)
     out_box = [None]
 

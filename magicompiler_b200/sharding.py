@@ -92,6 +92,26 @@ class PeerScatterReducer:
     """
 
     _active: "PeerScatterReducer | None" = None  # whose destinations the library's two sets currently describe
+    _shared: "dict[tuple, PeerScatterReducer]" = {}
+
+    @classmethod
+    def shared(cls, m: int, n_out: int, group=None, device: torch.device | None = None) -> "PeerScatterReducer":
+        """One reducer per (group, shape, device) for all layers of a model: calls from different layers are just
+        consecutive steps of the same reducer, so the buffers exist once and the library's destination sets are
+        written once.  Collective on first use, like the constructor."""
+        grp = group if group is not None else dist.group.WORLD
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        key = (id(grp), m, n_out, dev.index)
+        red = cls._shared.get(key)
+        if red is None:
+            red = cls._shared[key] = cls(m, n_out, grp, dev)
+        return red
+
+    @classmethod
+    def release_shared(cls) -> None:
+        """Drop the shared reducers (before a process group is destroyed, say); their buffers go with them."""
+        cls._shared.clear()
+        cls._active = None
 
     def __init__(self, m: int, n_out: int, group=None, device: torch.device | None = None):
         # plain peer stores only: never bind the buffers to an NVLink multicast object
@@ -176,7 +196,8 @@ class TensorParallelSwiGLUMLP(torch.nn.Module):
     kernel at all: the down projection's epilogue stores each row block into its owner's memory
     (``PeerScatterReducer``; ``chunks`` must be 1, M a multiple of ``32 * world``, the output width of 64).
     ``"peer_all_reduce"`` continues from there to the whole result on every rank: each rank's sum kernel stores its rows
-    into every rank's result buffer; the returned tensor is overwritten by the call after the next one.
+    into every rank's result buffer (shared by all layers of that shape); the module returns a copy unless
+    ``borrow_result=True``, in which case the tensor is overwritten by the second peer all-reduce after this one.
 
     ``down_fn(h, w_down)`` returns the partial down projection; if it has a true ``supports_out`` attribute it is
     called as ``down_fn(h, w_down, out=...)`` and writes straight into the result (``gemm_nt_out``).
@@ -184,14 +205,14 @@ class TensorParallelSwiGLUMLP(torch.nn.Module):
 
     def __init__(self, w_gate_up_full: torch.Tensor, w_down_full: torch.Tensor, rank: int = 0, world: int = 1,
                  group=None, chunks: int = 1, swiglu_fn: Callable | None = None, down_fn: Callable | None = None,
-                 reduce: str = "all_reduce"):
+                 reduce: str = "all_reduce", borrow_result: bool = False):
         super().__init__()
         if reduce not in ("all_reduce", "reduce_scatter", "peer_scatter", "peer_all_reduce"):
             raise ValueError("reduce must be 'all_reduce', 'reduce_scatter', 'peer_scatter' or 'peer_all_reduce', "
                              f"got {reduce!r}")
         if reduce in ("peer_scatter", "peer_all_reduce") and max(1, int(chunks)) != 1:
             raise ValueError(f"{reduce} overlaps the transfer inside the kernel; chunks must be 1")
-        self._peer: dict[int, PeerScatterReducer] = {}
+        self.borrow_result = bool(borrow_result)
         self.rank, self.world, self.group, self.chunks = rank, world, group, max(1, int(chunks))
         self.reduce = reduce
         self._down = down_fn  # (h [m, N/P], w_down [K_out, N/P]) -> [m, K_out]; None = library GEMM (torch.matmul)
@@ -223,12 +244,12 @@ class TensorParallelSwiGLUMLP(torch.nn.Module):
         x2 = x.reshape(-1, x.shape[-1])
         m, k_out = x2.shape[0], self.w_down.shape[0]
         if self.reduce in ("peer_scatter", "peer_all_reduce") and self.world > 1:
-            red = self._peer.get(m)
-            if red is None:
-                red = self._peer[m] = PeerScatterReducer(m, k_out, self.group, x.device)
+            red = PeerScatterReducer.shared(m, k_out, self.group, x.device)
             if self.reduce == "peer_scatter":
                 return red.linear_reduce_scatter(self.gate_up(x2), self.w_down)
-            return red.linear_all_reduce(self.gate_up(x2), self.w_down).view(*lead, k_out)
+            full = red.linear_all_reduce(self.gate_up(x2), self.w_down)
+            # the reducer's result buffer is overwritten two calls later: hand out a copy unless the caller borrows it
+            return (full if self.borrow_result else full.clone()).view(*lead, k_out)
         scatter = self.reduce in ("reduce_scatter", "peer_scatter") and self.world > 1
         slices = self._slices(m)
         if scatter and any((hi - lo) % self.world for lo, hi in slices):

@@ -13,6 +13,7 @@ from .passes import FuseSwiGLUPass, install_into_magi_compiler, pack_gate_up_cac
 from .register import COMPUTE_SENSITIVE_OPS, SPLITTING_OPS, magi_register_custom_op  # noqa: F401
 from .sharding import (  # noqa: F401
     ColumnParallelSwiGLU,
+    PeerScatterReducer,
     TensorParallelSwiGLUMLP,
     pack_gate_up,
     shard_bounds,
@@ -22,7 +23,7 @@ from .sharding import (  # noqa: F401
 
 __all__ = [
     "gemm_swiglu", "gemm_swiglu_auto", "gemm_swiglu_fp8", "gemm_swiglu_nvfp4", "nvfp4_scale_shape", "gemm_swiglu_preact", "gemm_swiglu_train", "gemm_swiglu_out", "gemm_bf16", "gemm_nt", "gemm_nt_out", "swiglu_backward_act", "swiglu_backward_dh", "set_gradient_gemms", "rmsnorm_gemm_swiglu", "fold_rmsnorm_weight", "OP_NAME", "pack_gate_up", "shard_gate_up", "shard_down", "shard_bounds",
-    "ColumnParallelSwiGLU", "TensorParallelSwiGLUMLP", "FuseSwiGLUPass", "install_into_magi_compiler",
+    "ColumnParallelSwiGLU", "TensorParallelSwiGLUMLP", "PeerScatterReducer", "FuseSwiGLUPass", "install_into_magi_compiler",
     "pack_gate_up_cached", "magi_register_custom_op", "SPLITTING_OPS",
     "COMPUTE_SENSITIVE_OPS", "build_library", "load_library", "plan", "workspace_bytes", "device_status", "kernel_clock", "MagiSwigluLibraryError",
 ]

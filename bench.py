@@ -7,7 +7,10 @@ line carries, under "workloads", one sub-record for each of the other benchmark 
 three decode shapes, the full SwiGLU MLP block), each with its own timing, roofline and output check.  On N > 1 GPUs
 the packed weight is column-sharded along N (rank r owns N/P gate and N/P up rows), X is replicated and no collective
 is on the op's data path; the job's work is the whole problem, so scaling is "strong".  Only the MLP block has an
-exchange step (the row-parallel down projection's all-reduce, NCCL over NVLink).
+exchange step: the reduction after the row-parallel down projection.  Its record times NCCL's all-reduce (row chunks
+overlapped with the next chunk's GEMMs) and carries three more timings of the same block: NCCL reduce-scatter, and
+the two forms in which the down projection's epilogue stores each row block straight into its owner GPU's memory
+("peer_scatter": reduce-scatter; "peer_all_reduce": the owners then store their sums into every GPU's result).
 
 Timing: W warm-up steps, then exactly K steps, each bracketed by its own pair of CUDA events on the launch stream
 with an L2 flush (256 MiB written, then 256 MiB read, so no dirty lines remain) before it; a barrier and a device

@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define MAGI_SWIGLU_ABI_VERSION 6
+#define MAGI_SWIGLU_ABI_VERSION 7
 
 /* variant selector of magi_swiglu_forward_bf16 */
 #define MAGI_SWIGLU_VARIANT_AUTO   0  /* M <= 128 -> STREAM, else MMA2           */
@@ -308,12 +308,14 @@ int magi_swiglu_schedule(int64_t M, int64_t N, int64_t K, int variant, int block
  *   STREAM_K  0 / 1: never / whenever possible, balance the last waves of the tile schedules by K ranges (-1 = choose)
  *   L2_HINTS  three decimal digits xwy, each 0 normal / 1 evict-first / 2 evict-last, for X tiles, W tiles and Y
  *             stores (-1 = defaults)
+ *   SCATTER_WIDE 0 / 1: the scattered GEMM stores 32-column boxes always / 64-column boxes where the tile allows
  * Replaces: nothing in the reference. */
 #define MAGI_SWIGLU_TUNE_K_SPLITS 0
 #define MAGI_SWIGLU_TUNE_NO_SPLIT 1
 #define MAGI_SWIGLU_TUNE_Y_TMA    2
 #define MAGI_SWIGLU_TUNE_L2_HINTS 3
 #define MAGI_SWIGLU_TUNE_STREAM_K 4
+#define MAGI_SWIGLU_TUNE_SCATTER_WIDE 5
 int magi_swiglu_tuning(int knob, int value);
 
 /* Runs the kernels' bounded wait by itself: a one-block kernel whose thread 0 waits on an mbarrier that nothing

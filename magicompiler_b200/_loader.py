@@ -25,7 +25,7 @@ NVCC_FLAGS = [
     "-shared", "-Xcompiler", "-fPIC",
 ]
 
-ABI_VERSION = 6
+ABI_VERSION = 7
 VARIANT_AUTO, VARIANT_MMA, VARIANT_STREAM, VARIANT_SIMT, VARIANT_MMA2 = 0, 1, 2, 3, 4
 VARIANTS = {"auto": VARIANT_AUTO, "mma": VARIANT_MMA, "stream": VARIANT_STREAM, "simt": VARIANT_SIMT,
             "mma2": VARIANT_MMA2}
@@ -150,7 +150,7 @@ def load_library() -> ctypes.CDLL:
     return lib
 
 
-TUNING_KNOBS = {"k_splits": 0, "no_split": 1, "y_tma": 2, "l2_hints": 3, "stream_k": 4}
+TUNING_KNOBS = {"k_splits": 0, "no_split": 1, "y_tma": 2, "l2_hints": 3, "stream_k": 4, "scatter_wide": 5}
 _tuning_epoch = 0  # bumped by set_tuning so host-side caches keyed on the schedule notice
 
 

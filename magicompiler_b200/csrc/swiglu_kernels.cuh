@@ -47,6 +47,9 @@ constexpr int kMaxScatterOwners = 8;  // GPUs of one NVLink domain a scattered p
 // Tensor maps of a scattered plain GEMM's destinations: [set][owner], one per GPU that owns a block of C's rows
 // (this GPU included), written once by magi_swiglu_scatter_setup.  Two sets so that consecutive steps can alternate.
 __constant__ CUtensorMap g_scatter_maps[2][kMaxScatterOwners];
+// The same destinations as boxes of 32 rows x 64 columns (128-byte rows, 128-byte swizzle): half as many, twice as
+// large writes on the links.  Used when the tile width allows (scatter_wide).
+__constant__ CUtensorMap g_scatter_maps_wide[2][kMaxScatterOwners];
 
 __device__ unsigned int g_watchdog[4];  // {role that gave up, block, stage/buffer, parity}
 // {SM cycles, nanoseconds} block 0 of the most recent tile kernel spent between set-up and teardown: the
@@ -124,6 +127,7 @@ struct KArgs {
   // Scattered plain GEMM: rows [o * scatter_rows, (o + 1) * scatter_rows) of C go to the buffer of owner o through
   // g_scatter_maps[scatter_set][o] (TMA stores only; y is null).  0: off.
   int scatter_rows, scatter_set;
+  int scatter_wide;  // 1: CTA pairs in split mode with half-tiles that are multiples of 64 columns: 64-column boxes
   long long wait_limit;  // SM cycles after which a wait on an mbarrier gives up (kWaitLimitCycles by default)
 };
 
@@ -839,6 +843,61 @@ swiglu_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       const float out_gs = (a.out_kind != 0) ? __ldg(a.out_scale) : 1.0f;
       const float out_inv_scale = 1.0f / out_gs;
 
+      if (kCtas == 2 && a.scatter_wide) {
+        // ---- scattered plain GEMM, wide boxes.  Tensor memory holds [lo: first | second][hi: first | second] halves
+        // of B's two row blocks, each seg_cols wide; the two warps of a lane quarter take one block each and drain it
+        // in groups of 64 columns: two tensor-memory loads, one 32-row x 64-column box (128-byte rows, 128-byte
+        // swizzle) in this warp's 4 KiB of staging memory, one TMA store through the map of the GPU that owns the rows.
+        const int blk = (warp - 4) >> 2;  // 0: rows [0, N) of B (output columns n), 1: rows [N, 2N) (columns N + n)
+        const int seg_cols = a.block_n / 2;
+        const uint32_t stage_buf = stg_base;
+        const int box_row0 = (mt * kCtas + (int)cta_rank) * kBM + q * 32;
+        const int owner = box_row0 / a.scatter_rows;
+        const CUtensorMap* dst_map = &g_scatter_maps_wide[a.scatter_set][owner];
+        bool seg_ok = true;
+        for (int seg = 0; seg < 2; ++seg) {
+          if (seg == 1) {
+            seg_ok = wait_bounded(acc_full_bar(1), acc_phase, &abort_flag, 3u, 1, a.wait_limit);
+            seg_ok = __all_sync(0xffffffffu, seg_ok);
+            if (!seg_ok) break;
+            tc_fence_after_sync();
+          }
+          const uint32_t t_src0 = t_tile + (uint32_t)(seg * a.block_n + blk * seg_cols);
+          const int valid = max(0, min(seg_cols, valid_tile - seg * seg_cols));
+          for (int c = 0; c < seg_cols; c += 64) {
+            uint32_t v0[32], v1[32];
+            tmem_ld_x32(t_src0 + c, v0);
+            tmem_ld_x32(t_src0 + c + 32, v1);
+            tmem_ld_wait();
+            tmem_regs_ready(v0);
+            tmem_regs_ready(v1);
+            if (c + 64 >= seg_cols) {  // last read of this half: hand it back before the stores
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive_cluster_relaxed(acc_empty_remote0 + 8u * seg);
+            }
+            if (c >= valid) continue;  // columns past N (whole boxes: N is a multiple of 64 here)
+            if (lane == 0) bulk_wait_group_read<0>();  // the previous box has left the staging memory
+            __syncwarp();
+            const uint32_t rowaddr = stage_buf + (uint32_t)lane * 128u;
+            const uint32_t sw = (uint32_t)lane & 7u;
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) {
+              const uint4 lo = plain_pack8(v0 + 8 * j), hi = plain_pack8(v1 + 8 * j);
+              st_shared_v4(rowaddr + ((j ^ sw) << 4), lo.x, lo.y, lo.z, lo.w);
+              st_shared_v4(rowaddr + (((j + 4) ^ sw) << 4), hi.x, hi.y, hi.z, hi.w);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0 && box_row0 < a.M) {
+              tma_store_3d(stage_buf, dst_map, col0 + seg * seg_cols + c, blk, box_row0 - owner * a.scatter_rows);
+              bulk_commit_group();
+            }
+          }
+        }
+        if (!seg_ok) break;
+        continue;
+      }
       if (kCtas == 1 && a.k_splits > 1) {
         // ---- split-K: park this CTA's fp32 partial sums; swiglu_splitk_reduce_kernel finishes the tile.
         // Scratch of one (tile, split): [lane quarter < ceil(M/32)][chunk][gate float4s, then up float4s][32 lanes]:

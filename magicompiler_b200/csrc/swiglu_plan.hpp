@@ -41,6 +41,7 @@ struct Tuning {
   int no_split = 0;
   int y_tma = -1;
   int stream_k = -1;  // -1 choose, 0 never, 1 whenever it is possible
+  int scatter_wide = 1;  // scattered GEMM: 64-column store boxes where the tile allows (0: always 32-column boxes)
 };
 static Tuning& tuning() {
   static Tuning t = [] {

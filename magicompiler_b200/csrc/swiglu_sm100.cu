@@ -116,17 +116,18 @@ static int encode_maps(const void* x, const void* w, int64_t M, int64_t N, int64
 // Y (or the plain GEMM's C) as a 3-D tensor [rows][halves][cols] for the epilogue's TMA stores: boxes of 32 rows x 32
 // columns (64-byte rows, 64-byte swizzle).  `halves` is 1 for the fused op and 2 for the plain GEMM, whose two
 // accumulator halves land `cols` columns apart; a box never spills from one half into the other.
-static int encode_y_map(const void* y, int64_t rows, int64_t cols, int64_t halves, int64_t ldy, CUtensorMap* tm) {
+static int encode_y_map(const void* y, int64_t rows, int64_t cols, int64_t halves, int64_t ldy, CUtensorMap* tm,
+                        int box_cols = 32) {
   EncodeTiledFn enc = tensor_map_encoder();
   if (!enc) return fail(MAGI_SWIGLU_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from the driver");
   const cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)halves, (cuuint64_t)rows};
   // a dimension of extent 1 is never stepped along: give it the row pitch so the strides stay multiples of each other
   const cuuint64_t strides[2] = {(cuuint64_t)(halves > 1 ? cols : ldy) * 2, (cuuint64_t)ldy * 2};
-  const cuuint32_t box[3] = {32, 1, 32};
+  const cuuint32_t box[3] = {(cuuint32_t)box_cols, 1, 32};  // 64- or 128-byte rows, swizzled over the same width
   const cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(y), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(MAGI_SWIGLU_ERR_DRIVER, "tensor map for Y rejected by the driver (CUresult %d)", (int)r);
   return 0;
 }
@@ -288,6 +289,8 @@ static int forward_impl(const void* x, const void* w, void* y, int64_t M, int64_
   a.y_tma = y_tma;
   a.scatter_rows = (int)scatter_rows;
   a.scatter_set = scatter_set;
+  // 64-column boxes when both half-tiles are whole numbers of them and no box can straddle the end of a row block
+  a.scatter_wide = (scatter_rows && p.split && p.block_n % 128 == 0 && N % 64 == 0 && tuning().scatter_wide != 0) ? 1 : 0;
   a.wait_limit = kWaitLimitCycles;
   auto fill_stream_k = [&]() {
     a.sk_first_tile = p.sk_first_tile;
@@ -579,16 +582,20 @@ int magi_swiglu_scatter_setup(int device, int set, void* const* dst, int world, 
   magi::DeviceGuard guard;
   cudaError_t e = guard.set(device);
   if (e != cudaSuccess) return magi::fail_cuda(e, "cudaSetDevice");
-  CUtensorMap maps[magi::kMaxScatterOwners];
+  CUtensorMap maps[magi::kMaxScatterOwners], wide[magi::kMaxScatterOwners];
   memset(maps, 0, sizeof(maps));
+  memset(wide, 0, sizeof(wide));
   for (int o = 0; o < world; ++o) {
     if (!dst[o] || ((uintptr_t)dst[o] & 15u))
       return magi::fail(MAGI_SWIGLU_ERR_ALIGN, "destination %d must be a 16-byte aligned device pointer", o);
-    const int rc = magi::encode_y_map(dst[o], rows_per_owner, N / 2, 2, ldc, &maps[o]);
+    int rc = magi::encode_y_map(dst[o], rows_per_owner, N / 2, 2, ldc, &maps[o]);
+    if (rc == 0) rc = magi::encode_y_map(dst[o], rows_per_owner, N / 2, 2, ldc, &wide[o], 64);
     if (rc) return rc;
   }
-  // a plain synchronous copy into the module's constant memory: set-up time, not the data path
+  // plain synchronous copies into the module's constant memory: set-up time, not the data path
   e = cudaMemcpyToSymbol(magi::g_scatter_maps, maps, sizeof(maps), (size_t)set * sizeof(maps), cudaMemcpyHostToDevice);
+  if (e == cudaSuccess)
+    e = cudaMemcpyToSymbol(magi::g_scatter_maps_wide, wide, sizeof(wide), (size_t)set * sizeof(wide), cudaMemcpyHostToDevice);
   if (e != cudaSuccess) return magi::fail_cuda(e, "cudaMemcpyToSymbol(scatter maps)");
   std::lock_guard<std::mutex> lock(magi::g_dev_mutex);
   magi::ScatterSet& ss = magi::g_scatter[device][set];
@@ -841,6 +848,10 @@ int magi_swiglu_tuning(int knob, int value) {
     case MAGI_SWIGLU_TUNE_Y_TMA:
       prev = t.y_tma;
       t.y_tma = value < 0 ? -1 : (value != 0);
+      return prev;
+    case MAGI_SWIGLU_TUNE_SCATTER_WIDE:
+      prev = t.scatter_wide;
+      t.scatter_wide = value != 0;
       return prev;
     case MAGI_SWIGLU_TUNE_STREAM_K:
       prev = t.stream_k;

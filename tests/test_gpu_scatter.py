@@ -16,10 +16,24 @@ def _rand(rows, cols, scale, seed):
 
 
 @pytest.mark.parametrize("world,rows,n,k", [(1, 512, 512, 256), (2, 256, 512, 1024), (4, 96, 128, 512),
-                                            (8, 32, 1024, 320), (3, 1024, 2048, 512)])
-def test_scattered_gemm_equals_gemm_nt_row_blocks(world, rows, n, k):
+                                            (8, 32, 1024, 320), (3, 1024, 2048, 512), (2, 160, 768, 192),
+                                            (8, 2048, 8192, 448)])
+@pytest.mark.parametrize("wide", [1, 0])
+def test_scattered_gemm_equals_gemm_nt_row_blocks(world, rows, n, k, wide):
+    """Both store-box widths (64 columns where the tile allows, 32 otherwise) against the plain GEMM, bit for bit."""
+    from magicompiler_b200 import _loader
+
     a, b = _rand(world * rows, k, 1.0, 1), _rand(n, k, 0.05, 2)
     want = mb.gemm_nt(a, b)
+    prev = _loader.set_tuning("scatter_wide", wide)
+    try:
+        _scatter_and_compare(a, b, want, world, rows, n)
+    finally:
+        _loader.set_tuning("scatter_wide", prev)
+    assert mb.device_status(0)["code"] == 0
+
+
+def _scatter_and_compare(a, b, want, world, rows, n):
     for dest_set in (0, 1):
         bufs = [torch.full((rows + 2, n), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
         ops.scatter_setup(dest_set, [t[1:].data_ptr() for t in bufs], rows, n)  # one guard row on either side
@@ -28,7 +42,6 @@ def test_scattered_gemm_equals_gemm_nt_row_blocks(world, rows, n, k):
         for o, t in enumerate(bufs):
             assert torch.equal(t[1:-1], want[o * rows:(o + 1) * rows]), (dest_set, o)
             assert torch.isnan(t[0]).all() and torch.isnan(t[-1]).all(), "rows outside the owner's block were written"
-    assert mb.device_status(0)["code"] == 0
 
 
 def test_scattered_gemm_with_padded_rows_of_the_destination():

@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define MAGI_SWIGLU_ABI_VERSION 8
+#define MAGI_SWIGLU_ABI_VERSION 7
 
 /* variant selector of magi_swiglu_forward_bf16 */
 #define MAGI_SWIGLU_VARIANT_AUTO   0  /* M <= 128 -> STREAM, else MMA2           */
@@ -214,14 +214,6 @@ int magi_swiglu_sum_slots_bf16(const void* src, void* out, int slots, int64_t sl
  * result readable everywhere.  It has no counterpart in the reference (NCCL's all-gather phase does this). */
 int magi_swiglu_sum_slots_bf16_bcast(const void* src, void* const* dst, int n_dst, int slots, int64_t slot_stride,
                                      int64_t n, int device, void* cuda_stream);
-
-/* The same with ONE destination address that belongs to an NVLink multicast object (e.g. the multicast pointer of a
- * symmetric-memory allocation): every 16-byte result leaves this GPU once (multimem.st) and the switch writes it into
- * every GPU's copy, so the second phase of the fused all-reduce moves 1/(P-1) of the bytes of the _bcast form.  The
- * caller makes the result readable with a barrier across the GPUs, as for _bcast.
- * It has no counterpart in the reference (NCCL's NVLS all-gather does this). */
-int magi_swiglu_sum_slots_bf16_mcast(const void* src, void* mc_dst, int slots, int64_t slot_stride, int64_t n,
-                                     int device, void* cuda_stream);
 
 /* The same plain GEMM with either operand stored the other way round, C[M,N] = op(A) · op(B)^T in bf16:
  *   a_layout 0: A is [M, K] (row stride lda);  1: A is stored [K, M] (its transpose, row stride lda, M % 8 == 0);

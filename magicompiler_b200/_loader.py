@@ -25,7 +25,7 @@ NVCC_FLAGS = [
     "-shared", "-Xcompiler", "-fPIC",
 ]
 
-ABI_VERSION = 8
+ABI_VERSION = 7
 VARIANT_AUTO, VARIANT_MMA, VARIANT_STREAM, VARIANT_SIMT, VARIANT_MMA2 = 0, 1, 2, 3, 4
 VARIANTS = {"auto": VARIANT_AUTO, "mma": VARIANT_MMA, "stream": VARIANT_STREAM, "simt": VARIANT_SIMT,
             "mma2": VARIANT_MMA2}
@@ -105,8 +105,6 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.magi_swiglu_sum_slots_bf16.argtypes = [vp, vp, i32, i64, i64, i32, vp]
     lib.magi_swiglu_sum_slots_bf16_bcast.restype = i32
     lib.magi_swiglu_sum_slots_bf16_bcast.argtypes = [vp, ctypes.POINTER(vp), i32, i32, i64, i64, i32, vp]
-    lib.magi_swiglu_sum_slots_bf16_mcast.restype = i32
-    lib.magi_swiglu_sum_slots_bf16_mcast.argtypes = [vp, vp, i32, i64, i64, i32, vp]
     lib.magi_swiglu_backward_act_bf16.restype = i32
     lib.magi_swiglu_backward_act_bf16.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i32, vp]
     lib.magi_swiglu_workspace_bytes.restype = i64

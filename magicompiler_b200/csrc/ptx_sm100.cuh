@@ -149,13 +149,6 @@ __device__ __forceinline__ void tma_store_3d_hint(uint32_t src, const void* tmap
       ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(c0), "r"(c1), "r"(c2), "l"(policy)
       : "memory");
 }
-// One 16-byte store to the same offset in every GPU's memory that is bound to the multicast object behind `mc_ptr`
-// (NVLink SHARP: the switch replicates it).  The four words are stored as they are.
-__device__ __forceinline__ void multimem_st_v4(void* mc_ptr, uint4 v) {
-  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_ptr), "f"(__uint_as_float(v.x)),
-               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
-               : "memory");
-}
 // The same store without an L2 priority (stores into another GPU's memory).
 __device__ __forceinline__ void tma_store_3d(uint32_t src, const void* tmap, int c0, int c1, int c2) {
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"

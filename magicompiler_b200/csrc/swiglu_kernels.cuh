@@ -1273,7 +1273,6 @@ swiglu_splitk_reduce_kernel(const float* __restrict__ ws, __nv_bfloat16* __restr
 struct SumDst {  // where the sums go: one buffer, or the same place in the memory of every GPU of the group
   __nv_bfloat16* p[kMaxScatterOwners];
   int n;
-  __nv_bfloat16* mc;  // non-null: ONE multicast address that reaches every GPU's copy (p is not used then)
 };
 __global__ void __launch_bounds__(256)
 swiglu_sum_slots_kernel(const __nv_bfloat16* __restrict__ src, const SumDst dst, int slots, long long slot_stride,
@@ -1297,11 +1296,7 @@ swiglu_sum_slots_kernel(const __nv_bfloat16* __restrict__ src, const SumDst dst,
     __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
     for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-    if (dst.mc != nullptr) {
-      multimem_st_v4(dst.mc + 8 * i, o);
-    } else {
-      for (int d = 0; d < dst.n; ++d) *reinterpret_cast<uint4*>(dst.p[d] + 8 * i) = o;
-    }
+    for (int d = 0; d < dst.n; ++d) *reinterpret_cast<uint4*>(dst.p[d] + 8 * i) = o;
   }
 }
 

@@ -628,17 +628,16 @@ int magi_swiglu_gemm_nt_bf16_scatter(const void* a, const void* b, int set, int6
 }
 
 static int sum_slots_impl(const void* src, void* const* dst, int n_dst, int slots, int64_t slot_stride, int64_t n, int device,
-                          void* cuda_stream, void* mc_dst = nullptr) {
+                          void* cuda_stream) {
   magi::g_err[0] = 0;
-  if (!mc_dst && (n_dst < 1 || n_dst > magi::kMaxScatterOwners))
+  if (n_dst < 1 || n_dst > magi::kMaxScatterOwners)
     return magi::fail(MAGI_SWIGLU_ERR_SHAPE, "1..%d destinations (got %d)", magi::kMaxScatterOwners, n_dst);
-  if (!src || (!dst && !mc_dst)) return magi::fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
+  if (!src || !dst) return magi::fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
   magi::SumDst sd;
   memset(&sd, 0, sizeof(sd));
-  sd.n = mc_dst ? 0 : n_dst;
-  sd.mc = static_cast<__nv_bfloat16*>(mc_dst);
-  uintptr_t bits = (uintptr_t)src | (uintptr_t)mc_dst;
-  for (int d = 0; d < sd.n; ++d) {
+  sd.n = n_dst;
+  uintptr_t bits = (uintptr_t)src;
+  for (int d = 0; d < n_dst; ++d) {
     if (!dst[d]) return magi::fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
     sd.p[d] = static_cast<__nv_bfloat16*>(dst[d]);
     bits |= (uintptr_t)dst[d];
@@ -674,15 +673,6 @@ int magi_swiglu_sum_slots_bf16(const void* src, void* out, int slots, int64_t sl
 int magi_swiglu_sum_slots_bf16_bcast(const void* src, void* const* dst, int n_dst, int slots, int64_t slot_stride, int64_t n,
                                      int device, void* cuda_stream) {
   return sum_slots_impl(src, dst, n_dst, slots, slot_stride, n, device, cuda_stream);
-}
-
-int magi_swiglu_sum_slots_bf16_mcast(const void* src, void* mc_dst, int slots, int64_t slot_stride, int64_t n, int device,
-                                     void* cuda_stream) {
-  if (!mc_dst) {
-    magi::g_err[0] = 0;
-    return magi::fail(MAGI_SWIGLU_ERR_NULL, "null pointer argument");
-  }
-  return sum_slots_impl(src, nullptr, 0, slots, slot_stride, n, device, cuda_stream, mc_dst);
 }
 
 int magi_swiglu_gemm_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,

@@ -289,20 +289,6 @@ def sum_slots_bcast(src: torch.Tensor, dst_ptrs: list[int]) -> None:
         raise (ValueError(msg) if rc < 0 else RuntimeError(msg))
 
 
-def sum_slots_mcast(src: torch.Tensor, mc_ptr: int) -> None:
-    """``sum_slots`` stored through ONE multicast address (``magi_swiglu_sum_slots_bf16_mcast``): the switch writes
-    every result into every GPU's copy."""
-    if src.dtype != torch.bfloat16 or not src.is_cuda or not src.is_contiguous() or src.dim() < 2:
-        raise TypeError("sum_slots_mcast takes a contiguous bf16 CUDA tensor [slots, ...]")
-    slots, n = src.shape[0], src[0].numel()
-    dev = src.device.index if src.device.index is not None else torch.cuda.current_device()
-    rc = _loader.load_library().magi_swiglu_sum_slots_bf16_mcast(src.data_ptr(), mc_ptr, slots, n, n, dev,
-                                                                  torch.cuda.current_stream(src.device).cuda_stream)
-    if rc != 0:
-        msg = f"magi_swiglu_sum_slots_bf16_mcast failed ({rc}): {_loader.last_error()}"
-        raise (ValueError(msg) if rc < 0 else RuntimeError(msg))
-
-
 @magi_register_custom_op(name=GEMM_NT_OP_NAME, mutates_args=(),
                          infer_output_meta_fn=lambda a, b: a.new_empty((*a.shape[:-1], b.shape[0])),
                          is_compute_sensitive=True)

@@ -158,16 +158,12 @@ class PeerScatterReducer:
         dist.all_reduce(self._token, group=self.group)  # every rank's stores into every buffer have completed
         return sum_slots(self.recv[dest_set], out)
 
-    def linear_all_reduce(self, h: torch.Tensor, w_down: torch.Tensor, multicast: bool = False) -> torch.Tensor:
+    def linear_all_reduce(self, h: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
         """The whole ``sum over ranks of h_r @ w_down_r.T`` on every rank: as ``linear_reduce_scatter``, but each rank's
         slot sum is stored into every rank's copy of the result (peer stores from the sum kernel) and a second barrier
         makes the whole result readable.  The returned ``[M, n_out]`` tensor is a view of one of two result buffers in
-        symmetric memory: it is overwritten by the call after the next one.
-
-        ``multicast=True`` sends each sum ONCE, to the result buffers' NVLink multicast address (``multimem.st``; the
-        switch replicates it), instead of once per peer.  It needs symmetric memory that torch bound to a multicast
-        object: start the process with ``TORCH_SYMM_MEM_DISABLE_MULTICAST=0`` (this class otherwise sets it to 1)."""
-        from .ops import gemm_nt_scatter, sum_slots_bcast, sum_slots_mcast
+        symmetric memory: it is overwritten by the call after the next one."""
+        from .ops import gemm_nt_scatter, sum_slots_bcast
 
         if h.shape[0] != self.m or w_down.shape[0] != self.n_out:
             raise ValueError(f"built for [{self.m}, *] x [{self.n_out}, *], got {tuple(h.shape)} x {tuple(w_down.shape)}")
@@ -182,14 +178,7 @@ class PeerScatterReducer:
         gemm_nt_scatter(h, w_down, dest_set)
         dist.all_reduce(self._token, group=self.group)  # every rank's partial products have arrived
         block = (dest_set * self.m + self.rank * self.rows) * self.n_out * 2  # this rank's rows in a result buffer
-        if multicast:
-            mc = int(self._full_handle.multicast_ptr or 0)
-            if not mc:
-                raise RuntimeError("the result buffers have no multicast address (TORCH_SYMM_MEM_DISABLE_MULTICAST=0 "
-                                   "must be set before the first symmetric allocation, and the GPUs must support it)")
-            sum_slots_mcast(self.recv[dest_set], mc + block)
-        else:
-            sum_slots_bcast(self.recv[dest_set], [int(p) + block for p in self._full_handle.buffer_ptrs])
+        sum_slots_bcast(self.recv[dest_set], [int(p) + block for p in self._full_handle.buffer_ptrs])
         dist.all_reduce(self._token, group=self.group)  # every rank's rows have arrived in every result buffer
         return self.full[dest_set]
 
@@ -216,7 +205,7 @@ class TensorParallelSwiGLUMLP(torch.nn.Module):
 
     def __init__(self, w_gate_up_full: torch.Tensor, w_down_full: torch.Tensor, rank: int = 0, world: int = 1,
                  group=None, chunks: int = 1, swiglu_fn: Callable | None = None, down_fn: Callable | None = None,
-                 reduce: str = "all_reduce", borrow_result: bool = False, multicast: bool = False):
+                 reduce: str = "all_reduce", borrow_result: bool = False):
         super().__init__()
         if reduce not in ("all_reduce", "reduce_scatter", "peer_scatter", "peer_all_reduce"):
             raise ValueError("reduce must be 'all_reduce', 'reduce_scatter', 'peer_scatter' or 'peer_all_reduce', "
@@ -224,7 +213,6 @@ class TensorParallelSwiGLUMLP(torch.nn.Module):
         if reduce in ("peer_scatter", "peer_all_reduce") and max(1, int(chunks)) != 1:
             raise ValueError(f"{reduce} overlaps the transfer inside the kernel; chunks must be 1")
         self.borrow_result = bool(borrow_result)
-        self.multicast = bool(multicast)  # peer_all_reduce only: second phase through the NVLink multicast address
         self.rank, self.world, self.group, self.chunks = rank, world, group, max(1, int(chunks))
         self.reduce = reduce
         self._down = down_fn  # (h [m, N/P], w_down [K_out, N/P]) -> [m, K_out]; None = library GEMM (torch.matmul)
@@ -259,7 +247,7 @@ class TensorParallelSwiGLUMLP(torch.nn.Module):
             red = PeerScatterReducer.shared(m, k_out, self.group, x.device)
             if self.reduce == "peer_scatter":
                 return red.linear_reduce_scatter(self.gate_up(x2), self.w_down)
-            full = red.linear_all_reduce(self.gate_up(x2), self.w_down, multicast=self.multicast)
+            full = red.linear_all_reduce(self.gate_up(x2), self.w_down)
             # the reducer's result buffer is overwritten two calls later: hand out a copy unless the caller borrows it
             return (full if self.borrow_result else full.clone()).view(*lead, k_out)
         scatter = self.reduce in ("reduce_scatter", "peer_scatter") and self.world > 1

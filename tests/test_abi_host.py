@@ -211,11 +211,6 @@ def test_scatter_entry_points_reject_bad_arguments_on_the_host(lib):
     assert bcast(b, None, 2, 2, 64, 64, 0, None) == -1
     assert bcast(b, dst, 2, 2, 64, 60, 0, None) == -2
     assert bcast(b, dst, 8, 2, 64, 64, 1000, None) == -5
-    mcast = lib.magi_swiglu_sum_slots_bf16_mcast
-    assert mcast(b, None, 2, 64, 64, 0, None) == -1
-    assert mcast(b, b, 2, 64, 60, 0, None) == -2
-    assert mcast(b, b + 8, 2, 64, 64, 0, None) == -3
-    assert mcast(b, b, 2, 64, 64, 1000, None) == -5
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

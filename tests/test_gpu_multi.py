@@ -129,67 +129,6 @@ def test_two_ranks_down_projection_scattered_by_its_epilogue():
         assert ok_exact and ok_ref and status == 0, res
 
 
-def _rank_peer_multicast(rank, world, port, q):
-    """The fused all-reduce whose second phase goes through the result buffers' NVLink multicast address, twenty
-    steps with fresh inputs, each bit for bit against the fp32 rank-order sum of the all-gathered partial products."""
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), TORCH_SYMM_MEM_DISABLE_MULTICAST="0")
-    import torch.distributed as dist
-
-    import magicompiler_b200 as mb
-    from oracle import make_inputs
-
-    torch.cuda.set_device(rank)
-    dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-    try:
-        M, K, N = 1024, 512, 2048
-        _, w, wd = make_inputs(M, K, N, seed=23, with_down=True)
-        mlp = mb.TensorParallelSwiGLUMLP(w, wd, rank, world, reduce="peer_all_reduce", multicast=True).to(dev)
-        ok, note = True, ""
-        for step in range(20):
-            x, _, _ = make_inputs(M, K, N, seed=50 + step, with_down=True)
-            xd = x.to(dev)
-            try:
-                z = mlp(xd)
-            except RuntimeError as exc:
-                if "no multicast address" in str(exc):  # this machine's symmetric memory has no multicast binding
-                    note = "no multicast"
-                    break
-                raise
-            partial = mb.gemm_nt(mlp.gate_up(xd), mlp.w_down)
-            parts = [torch.empty_like(partial) for _ in range(world)]
-            dist.all_gather(parts, partial)
-            acc = torch.zeros(M, K, dtype=torch.float32, device=dev)
-            for p in parts:
-                acc += p.float()
-            ok &= bool(torch.equal(z, acc.to(torch.bfloat16)))
-        torch.cuda.synchronize()
-        q.put((rank, ok, note, mb.device_status(rank)["code"]))
-    except Exception as exc:  # report instead of leaving the parent to time out
-        q.put((rank, False, repr(exc), -1))
-    finally:
-        dist.destroy_process_group()
-
-
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_ranks_fused_all_reduce_through_the_multicast_address():
-    import torch.multiprocessing as mp
-
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_rank_peer_multicast, args=(r, 2, port, q)) for r in range(2)]
-    for p in procs:
-        p.start()
-    res = sorted(q.get(timeout=300) for _ in procs)
-    for p in procs:
-        p.join(timeout=60)
-    if all(note == "no multicast" for _, _, note, _ in res):
-        pytest.skip("symmetric memory on this machine has no multicast address")
-    for rank, ok, note, status in res:
-        assert ok and status == 0, res
-
-
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_ranks_column_shards_and_tensor_parallel_mlp():
     import torch.multiprocessing as mp

@@ -627,6 +627,18 @@ def run_single_kernel(b, mb, args):
         M, K, N = WORKLOADS["llama3_8b_ffn"][:3]
         x, w, dy = rnd(M, K, 1.0), rnd(2 * N, K, 0.02), rnd(M, N, 1.0)
         fn, flops, nbytes = (lambda: mb.swiglu_backward_dh(x, w, dy)), flops_of(M, K, N), None
+    elif args.only == "scatter":      # the 8-GPU rank's down projection with its row blocks scattered to eight buffers
+        from magicompiler_b200 import ops  # (all on this GPU here) + the slot sum that finishes the reduce-scatter
+        a, w = rnd(16384, 3584, 1.0), rnd(8192, 3584, 0.02)
+        recv = torch.empty(8, 2048, 8192, dtype=torch.bfloat16, device=dev)
+        out = torch.empty(2048, 8192, dtype=torch.bfloat16, device=dev)
+        ops.scatter_setup(0, [recv[o].data_ptr() for o in range(8)], 2048, 8192)
+
+        def fn():
+            ops.gemm_nt_scatter(a, w, 0)
+            ops.sum_slots(recv, out)
+
+        flops, nbytes = 2.0 * 16384 * 3584 * 8192, None
     else:                             # 1/8 column shard of the decode weight, M = 64: split-K tile kernel + ordered reduce
         M, K, N = 64, 8192, 3584
         x, w = rnd(M, K, 1.0), rnd(2 * N, K, 0.02)
@@ -666,10 +678,11 @@ def main():
     ap.add_argument("--no-flush", action="store_true", help="profiling runs only: skip the L2 flush kernels")
     ap.add_argument("--no-peer-scatter", action="store_true",
                     help="N > 1: skip the MLP block variant whose down projection stores into the other GPUs' memory")
-    ap.add_argument("--only", default=None, choices=["gemm_nt", "backward_dh", "decode_shard"],
+    ap.add_argument("--only", default=None, choices=["gemm_nt", "backward_dh", "decode_shard", "scatter"],
                     help="profiling runs only: time one of the other kernels of the library by itself (1 GPU) and print a "
                          "short JSON line: the down projection of the MLP block (gemm_nt), the recomputing backward "
-                         "(backward_dh, Llama shape), or a 1/8 decode column shard (split-K tile kernel + ordered reduce)")
+                         "(backward_dh, Llama shape), a 1/8 decode column shard (split-K tile kernel + ordered reduce), or "
+                         "the scattered down projection of an 8-GPU rank + its slot sum with all eight buffers local (scatter)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" and not args.no_flush else args.warmup
 

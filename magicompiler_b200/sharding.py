@@ -76,6 +76,14 @@ class ColumnParallelSwiGLU(torch.nn.Module):
         return fn(x, self.weight)
 
 
+def peer_slot_offset(dest_set: int, world: int, writer: int, rows: int, n_out: int) -> int:
+    """Element offset, inside a receive buffer ``[2 sets][world slots][rows][n_out]``, of the slot that rank ``writer``
+    fills in destination set ``dest_set`` (the same in every owner's buffer)."""
+    if not (0 <= dest_set < 2 and 0 <= writer < world):
+        raise ValueError(f"bad slot: set {dest_set}, writer {writer} of {world}")
+    return ((dest_set * world + writer) * rows) * n_out
+
+
 class PeerScatterReducer:
     """Reduce-scatter of a row-parallel GEMM whose data movement is the GEMM's own epilogue.
 
@@ -138,11 +146,11 @@ class PeerScatterReducer:
         from .ops import scatter_setup
 
         torch.cuda.current_stream(self.device).synchronize()  # no scattered GEMM may be running on the old sets
-        slot_bytes = self.rows * self.n_out * 2
         bases = [int(p) for p in self.handle.buffer_ptrs]
         for dest_set in (0, 1):
-            scatter_setup(dest_set, [bases[o] + (dest_set * self.world + self.rank) * slot_bytes for o in range(self.world)],
-                          self.rows, self.n_out, device=self.device.index)
+            mine = 2 * peer_slot_offset(dest_set, self.world, self.rank, self.rows, self.n_out)  # bytes (bf16)
+            scatter_setup(dest_set, [bases[o] + mine for o in range(self.world)], self.rows, self.n_out,
+                          device=self.device.index)
         PeerScatterReducer._active = self
 
     def linear_reduce_scatter(self, h: torch.Tensor, w_down: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:

@@ -139,6 +139,86 @@ def test_two_gloo_ranks_column_shards_and_row_parallel_allreduce(chunks):
         assert ok_cols and ok_mlp and shape == [40, 64]
 
 
+def _peer_protocol_rank(rank, world, port, bufs, q, leaver):
+    """The host side of the fused reduce-scatter on CPU: shared-memory tensors stand in for symmetric memory, plain
+    tensor writes for the epilogue's stores into the owners' slots, a gloo all-reduce of one element for the barrier.
+    Same slot arithmetic (``peer_slot_offset``), same order (write, barrier, sum own slots in rank order), same
+    alternation of the two destination sets, and ONE barrier per step; ranks are slowed down at different steps so
+    that a set being overwritten before its owner has summed it would show up as a wrong result."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import datetime
+    import time
+
+    from magicompiler_b200.sharding import peer_slot_offset
+
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=6))
+    try:
+        m, n_in, n_out = 96, 40, 64
+        rows = m // world
+        token = torch.zeros(1)
+        ok, outcome = True, "done"
+        for step in range(6):
+            if rank == leaver and step == 3:
+                outcome = "left"  # between steps: its writes of step 2 are complete, nothing of step 3 has started
+                break
+            g = torch.Generator().manual_seed(100 + step)
+            h = torch.randn(world, m, n_in, generator=g)          # every rank can rebuild every rank's operands
+            wd = torch.randn(world, n_out, n_in, generator=g)
+            partial = h[rank] @ wd[rank].t()
+            dest_set = step & 1
+            if (step + rank) % 3 == 0:
+                time.sleep(0.05)                                   # skew the ranks against each other
+            for o in range(world):                                 # "epilogue stores": row block o into owner o's slot
+                off = peer_slot_offset(dest_set, world, rank, rows, n_out)
+                bufs[o].view(-1)[off:off + rows * n_out] = partial[o * rows:(o + 1) * rows].reshape(-1)
+            try:
+                dist.all_reduce(token)                             # the one barrier of the step
+            except Exception as exc:
+                outcome = "error:" + type(exc).__name__
+                break
+            acc = torch.zeros(rows, n_out)
+            for r in range(world):                                 # own slots, rank order
+                off = peer_slot_offset(dest_set, world, r, rows, n_out)
+                acc += bufs[rank].view(-1)[off:off + rows * n_out].view(rows, n_out)
+            want = sum(h[r] @ wd[r].t() for r in range(world))[rank * rows:(rank + 1) * rows]
+            ok &= bool(torch.equal(acc, want))
+        q.put((rank, ok, outcome))
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+@pytest.mark.parametrize("world,leaver", [(2, -1), (3, -1), (2, 1)])
+def test_peer_scatter_host_protocol(world, leaver):
+    """Two destination sets and one barrier per step are enough (every step's sums are exact although the ranks run
+    skewed); and a rank that leaves between steps ends the survivors' next barrier with an error, not a hang."""
+    from magicompiler_b200.sharding import peer_slot_offset
+
+    with pytest.raises(ValueError):
+        peer_slot_offset(2, 2, 0, 8, 8)
+    m, n_out = 96, 64
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    bufs = [torch.zeros(2 * world * (m // world) * n_out).share_memory_() for _ in range(world)]
+    procs = [ctx.Process(target=_peer_protocol_rank, args=(r, world, port, bufs, q, leaver)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=180) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+    for rank, ok, outcome in res:
+        assert ok, res
+        if leaver < 0:
+            assert outcome == "done", res
+        elif rank == leaver:
+            assert outcome == "left", res
+        else:
+            assert outcome.startswith("error:"), res
+
+
 def _failing_rank(rank, world, port, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     import datetime

@@ -7,10 +7,12 @@ line carries, under "workloads", one sub-record for each of the other benchmark 
 three decode shapes, the full SwiGLU MLP block), each with its own timing, roofline and output check.  On N > 1 GPUs
 the packed weight is column-sharded along N (rank r owns N/P gate and N/P up rows), X is replicated and no collective
 is on the op's data path; the job's work is the whole problem, so scaling is "strong".  Only the MLP block has an
-exchange step: the reduction after the row-parallel down projection.  Its record times NCCL's all-reduce (row chunks
-overlapped with the next chunk's GEMMs) and carries three more timings of the same block: NCCL reduce-scatter, and
-the two forms in which the down projection's epilogue stores each row block straight into its owner GPU's memory
-("peer_scatter": reduce-scatter; "peer_all_reduce": the owners then store their sums into every GPU's result).
+exchange step: the reduction after the row-parallel down projection.  At N > 1 its record is the fused all-reduce
+("peer_all_reduce": the down projection's epilogue stores each row block straight into its owner GPU's memory, the
+owners sum and store their rows into every GPU's result; every rank ends with the whole result, as after the
+reference's row-parallel linear) and carries three more timings of the same block: NCCL's all-reduce with row chunks
+overlapped with the next chunk's GEMMs ("nccl_all_reduce"), NCCL's reduce-scatter, and the fused reduce-scatter
+("peer_scatter").  Without symmetric memory the record is NCCL's all-reduce and says why ("peer_unavailable").
 
 Timing: W warm-up steps, then exactly K steps, each bracketed by its own pair of CUDA events on the launch stream
 with an L2 flush (256 MiB written, then 256 MiB read, so no dirty lines remain) before it; a barrier and a device
@@ -849,20 +851,25 @@ def main():
             torch.cuda.synchronize(dev)
             time.sleep(SETTLE_S)
             if name == "mlp_block":
-                subs[name] = run_mlp_block(b, mb, sub_steps, sub_warmup, args.chunks if world > 1 else 1, args.reduce,
-                                           args.down)
-                if world > 1:  # the same block with each rank keeping only its rows of the sum (half the link bytes)
+                nccl = run_mlp_block(b, mb, sub_steps, sub_warmup, args.chunks if world > 1 else 1, args.reduce, args.down)
+                subs[name] = nccl
+                if world > 1:
+                    short = ("ms_per_step", "ms_median", "ms_min", "value", "unit", "chunks", "reduce", "parallelism", "parity")
+                    # the same block with each rank keeping only its rows of the sum (half the link bytes)
                     alt = run_mlp_block(b, mb, sub_steps, sub_warmup, 1, "reduce_scatter", args.down)
-                    subs[name]["reduce_scatter"] = {k: alt[k] for k in ("ms_per_step", "value", "unit", "chunks", "parity")}
-                    if not args.no_peer_scatter:  # ... and with the reduce-scatter's transfer fused into the down projection
+                    extra = {"reduce_scatter": {k: alt[k] for k in short}}
+                    if not args.no_peer_scatter:  # ... and with the reduction fused into the down projection's epilogue
                         try:
                             alt = run_mlp_block(b, mb, sub_steps, sub_warmup, 1, "peer_scatter", "own")
-                            subs[name]["peer_scatter"] = {k: alt[k] for k in ("ms_per_step", "value", "unit", "parallelism", "parity")}
-                            alt = run_mlp_block(b, mb, sub_steps, sub_warmup, 1, "peer_all_reduce", "own")
-                            subs[name]["peer_all_reduce"] = {k: alt[k] for k in ("ms_per_step", "value", "unit", "parallelism", "parity")}
+                            extra["peer_scatter"] = {k: alt[k] for k in short}
+                            fused = run_mlp_block(b, mb, sub_steps, sub_warmup, 1, "peer_all_reduce", "own")
+                            # The block's record is the fused all-reduce (every rank ends with the whole result, the
+                            # contract of the reference's row-parallel linear); NCCL's all-reduce is kept beside it.
+                            extra["nccl_all_reduce"] = {k: nccl[k] for k in short}
+                            subs[name] = fused
                         except (RuntimeError, ValueError, ImportError) as exc:  # e.g. no symmetric memory on this machine
-                            subs[name].setdefault("peer_scatter", {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"})
-                            subs[name].setdefault("peer_all_reduce", {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"})
+                            extra["peer_unavailable"] = f"{type(exc).__name__}: {str(exc)[:200]}"
+                    subs[name].update(extra)
                 continue
             sM, sK, sN, _, _ = WORKLOADS[name]
             xs, ws = make_inputs_cuda(sM, sK, sN, dev, seed=0)
@@ -870,9 +877,9 @@ def main():
                 ws = mb.shard_gate_up(ws, rank, world)
             subs[name] = time_op_workload(b, mb, name, xs, ws, sub_steps, sub_warmup)[0]
             del xs, ws
-    ok = head["parity"]["ok"] and all(r["parity"]["ok"] and r.get("reduce_scatter", {}).get("parity", {}).get("ok", True)
-                                      and r.get("peer_scatter", {}).get("parity", {}).get("ok", True)
-                                      and r.get("peer_all_reduce", {}).get("parity", {}).get("ok", True) for r in subs.values())
+    ok = head["parity"]["ok"] and all(
+        r["parity"]["ok"] and all(r.get(k, {}).get("parity", {}).get("ok", True)
+                                  for k in ("reduce_scatter", "peer_scatter", "nccl_all_reduce")) for r in subs.values())
 
     if rank != 0:
         if world > 1:

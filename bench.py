@@ -656,6 +656,28 @@ def run_single_kernel(b, mb, args):
     print(json.dumps(line), flush=True)
 
 
+def bind_to_gpu_numa_node(local_rank):
+    """N > 1: run this rank on the CPU cores next to its GPU (read from NVML, nothing is set on the GPU), so that the
+    pinned host buffers of the end-to-end leg are allocated on that NUMA node and the copies do not cross sockets.
+    Returns a short description for the JSON line."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(local_rank)
+        ncpu = os.cpu_count() or 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (ncpu + 63) // 64)
+        near = {i for i in range(ncpu) if (words[i // 64] >> (i % 64)) & 1}
+        allowed = os.sched_getaffinity(0)
+        cpus = sorted(near & allowed)
+        if not cpus or len(cpus) == len(allowed):
+            return f"not bound ({len(near)} cores next to the GPU, {len(allowed)} allowed)"
+        os.sched_setaffinity(0, cpus)
+        return f"bound to the {len(cpus)} cores next to the GPU ({cpus[0]}..{cpus[-1]})"
+    except Exception as exc:  # no NVML, no such call, not permitted: stay where we are
+        return f"not bound ({type(exc).__name__})"
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -678,6 +700,8 @@ def main():
     ap.add_argument("--train", action="store_true",
                     help="also time forward + backward of the op (both autograd forms) against the eager expression")
     ap.add_argument("--no-flush", action="store_true", help="profiling runs only: skip the L2 flush kernels")
+    ap.add_argument("--no-numa-bind", action="store_true",
+                    help="N > 1: leave the rank on whatever cores it was started on (default: the cores next to its GPU)")
     ap.add_argument("--no-peer-scatter", action="store_true",
                     help="N > 1: skip the MLP block variant whose down projection stores into the other GPUs' memory")
     ap.add_argument("--only", default=None, choices=["gemm_nt", "backward_dh", "decode_shard", "scatter"],
@@ -703,6 +727,7 @@ def main():
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    cpu_binding = bind_to_gpu_numa_node(local_rank) if world > 1 and not args.no_numa_bind else "not bound"
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
@@ -917,7 +942,8 @@ def main():
     if e2e is not None:
         ms, h2d, d2h, how, rates = e2e
         line["e2e"] = {"value": e2e_scale / (ms * 1e-3), "unit": unit, "h2d_bytes_per_step": h2d,
-                       "d2h_bytes_per_step": d2h, "ms_per_step": ms, "how": how, "copies_alone": rates}
+                       "d2h_bytes_per_step": d2h, "ms_per_step": ms, "how": how, "copies_alone": rates,
+                       "cpu_binding_rank0": cpu_binding}
     if subs:
         line["workloads"] = subs
     if incumbents is not None:

@@ -92,8 +92,9 @@ class PeerScatterReducer:
     epilogue's TMA stores aimed at slot ``rank`` of the buffer of whichever GPU owns the row block
     (``magi_swiglu_gemm_nt_bf16_scatter``), waits for all ranks on the stream (a one-element NCCL all-reduce: it
     starts after this rank's GEMM has completed and ends only when every rank has joined, and a rank that never joins
-    ends it with the process group's timeout error instead of an endless wait), and adds the ``world`` slots of its own buffer in rank order (``magi_swiglu_sum_slots_bf16``): deterministic, and the partial
-    products cross NVLink while the tensor cores are still busy with later tiles instead of in a collective afterwards.
+    ends it with the process group's timeout error instead of an endless wait), and adds the ``world`` slots of its
+    own buffer in rank order (``magi_swiglu_sum_slots_bf16``): deterministic, and the partial products cross NVLink
+    while the tensor cores are still busy with later tiles instead of in a collective afterwards.
     Consecutive calls alternate between the two sets, so one barrier per call is enough: a peer can only start
     overwriting set s two calls later, which needs the barrier of the call in between, which this rank enters after
     its sum over set s.  Collective: all ranks of ``group`` construct it and call it in the same order.

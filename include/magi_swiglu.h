@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define MAGI_SWIGLU_ABI_VERSION 7
+#define MAGI_SWIGLU_ABI_VERSION 8
 
 /* variant selector of magi_swiglu_forward_bf16 */
 #define MAGI_SWIGLU_VARIANT_AUTO   0  /* M <= 128 -> STREAM, else MMA2           */
@@ -226,6 +226,17 @@ int magi_swiglu_sum_slots_bf16_bcast(const void* src, void* const* dst, int n_ds
 int magi_swiglu_gemm_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,
                           int64_t lda, int64_t ldb, int64_t ldc, int a_layout, int b_layout,
                           int device, void* cuda_stream);
+
+/* The same GEMM with optional scratch (size from magi_swiglu_gemm_bf16_workspace_bytes; 0 = none wanted; caller-owned,
+ * 256-byte aligned, no initialisation needed): with it the last waves of the tile schedule are balanced stream-K
+ * fashion as in magi_swiglu_forward_bf16_ws where the last wave would be at most a quarter full (dW = dH^T · X of the
+ * Llama shape: 896 tiles on 74 CTA pairs).  Results differ from the scratch-less call by fp32 summation order in the
+ * tiles that were cut.
+ * Replaces: the same library GEMMs as magi_swiglu_gemm_bf16. */
+int magi_swiglu_gemm_bf16_ws(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,
+                             int64_t lda, int64_t ldb, int64_t ldc, int a_layout, int b_layout, int device,
+                             void* cuda_stream, void* workspace, int64_t workspace_bytes);
+int64_t magi_swiglu_gemm_bf16_workspace_bytes(int64_t M, int64_t N, int64_t K, int b_layout, int device);
 
 /* Backward of the activation.  h is [M, 2N] = [G | U], the pre-activations X·Wg^T and X·Wu^T (bf16, row stride ldh),
  * dy is [M, N]; writes dh = [dG | dU] ([M, 2N], row stride lddh) with dG = dY*U*s*(1 + G*(1-s)), dU = dY*G*s,

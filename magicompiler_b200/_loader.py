@@ -25,7 +25,7 @@ NVCC_FLAGS = [
     "-shared", "-Xcompiler", "-fPIC",
 ]
 
-ABI_VERSION = 7
+ABI_VERSION = 8
 VARIANT_AUTO, VARIANT_MMA, VARIANT_STREAM, VARIANT_SIMT, VARIANT_MMA2 = 0, 1, 2, 3, 4
 VARIANTS = {"auto": VARIANT_AUTO, "mma": VARIANT_MMA, "stream": VARIANT_STREAM, "simt": VARIANT_SIMT,
             "mma2": VARIANT_MMA2}
@@ -95,6 +95,10 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.magi_swiglu_backward_dh_bf16.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, i32, vp]
     lib.magi_swiglu_gemm_bf16.restype = i32
     lib.magi_swiglu_gemm_bf16.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, i32, vp]
+    lib.magi_swiglu_gemm_bf16_ws.restype = i32
+    lib.magi_swiglu_gemm_bf16_ws.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, i32, vp, vp, i64]
+    lib.magi_swiglu_gemm_bf16_workspace_bytes.restype = i64
+    lib.magi_swiglu_gemm_bf16_workspace_bytes.argtypes = [i64, i64, i64, i32, i32]
     lib.magi_swiglu_gemm_nt_bf16.restype = i32
     lib.magi_swiglu_gemm_nt_bf16.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, vp]
     lib.magi_swiglu_scatter_setup.restype = i32

@@ -675,8 +675,30 @@ int magi_swiglu_sum_slots_bf16_bcast(const void* src, void* const* dst, int n_ds
   return sum_slots_impl(src, dst, n_dst, slots, slot_stride, n, device, cuda_stream);
 }
 
-int magi_swiglu_gemm_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
-                          int64_t ldc, int a_layout, int b_layout, int device, void* cuda_stream) {
+// tile width an MN-major B tile allows (256 with two MMAs per step for pairs, 128, 64); 0 = let the planner choose
+static int gemm_bf16_block_n(int64_t M, int64_t N, int b_layout, int variant, int device) {
+  if (b_layout != 1) return 0;
+  const int64_t half = N / 2;
+  if (half < 128) return 64;
+  if (variant == MAGI_SWIGLU_VARIANT_MMA) return 128;
+  const magi::DeviceInfo* di = magi::device_info(device);
+  const int64_t units = di ? di->sm_count / 2 : 74;
+  const int64_t m_units = (M + 2 * magi::kBM - 1) / (2 * magi::kBM);
+  const int64_t c256 = ((m_units * ((half + 255) / 256) + units - 1) / units) * (256 + 146);
+  const int64_t c128 = ((m_units * ((half + 127) / 128) + units - 1) / units) * (128 + 146);
+  return (c256 <= c128) ? 256 : 128;
+}
+
+int64_t magi_swiglu_gemm_bf16_workspace_bytes(int64_t M, int64_t N, int64_t K, int b_layout, int device) {
+  magi::g_err[0] = 0;
+  if (N <= 0 || N % 16 != 0) return magi::fail(MAGI_SWIGLU_ERR_SHAPE, "N (%lld) must be a positive multiple of 16", (long long)N);
+  const int variant = (M <= 128) ? MAGI_SWIGLU_VARIANT_MMA : MAGI_SWIGLU_VARIANT_MMA2;
+  return magi_swiglu_workspace_bytes(M, N / 2, K, variant, gemm_bf16_block_n(M, N, b_layout, variant, device), 0, 0, 0, device, 0);
+}
+
+int magi_swiglu_gemm_bf16_ws(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                             int64_t ldc, int a_layout, int b_layout, int device, void* cuda_stream, void* workspace,
+                             int64_t workspace_bytes) {
   magi::g_err[0] = 0;
   if (N <= 0 || N % 16 != 0)
     return magi::fail(MAGI_SWIGLU_ERR_SHAPE, "magi_swiglu_gemm_bf16 needs N (%lld) to be a positive multiple of 16", (long long)N);
@@ -685,25 +707,14 @@ int magi_swiglu_gemm_bf16(const void* a, const void* b, void* c, int64_t M, int6
   if (a_layout == 1 && M % 8 != 0)
     return magi::fail(MAGI_SWIGLU_ERR_SHAPE, "an A operand stored [K, M] needs M (%lld) to be a multiple of 8", (long long)M);
   const int variant = (M <= 128) ? MAGI_SWIGLU_VARIANT_MMA : MAGI_SWIGLU_VARIANT_MMA2;
-  int block_n = 0;
-  if (b_layout == 1) {
-    // tile widths an MN-major B tile allows: 256 (two MMAs per step, pairs only), 128, 64
-    const int64_t half = N / 2;
-    if (half < 128) {
-      block_n = 64;
-    } else if (variant == MAGI_SWIGLU_VARIANT_MMA) {
-      block_n = 128;
-    } else {
-      const magi::DeviceInfo* di = magi::device_info(device);
-      const int64_t units = di ? di->sm_count / 2 : 74;
-      const int64_t m_units = (M + 2 * magi::kBM - 1) / (2 * magi::kBM);
-      const int64_t c256 = ((m_units * ((half + 255) / 256) + units - 1) / units) * (256 + 146);
-      const int64_t c128 = ((m_units * ((half + 127) / 128) + units - 1) / units) * (128 + 146);
-      block_n = (c256 <= c128) ? 256 : 128;
-    }
-  }
-  return magi::forward_impl(a, b, c, M, N / 2, K, lda, ldb, ldc, device, cuda_stream, variant, block_n, 0, 0, 0, nullptr, 0,
-                            1, nullptr, nullptr, nullptr, 0, nullptr, 0, nullptr, 0, 0, a_layout, b_layout);
+  return magi::forward_impl(a, b, c, M, N / 2, K, lda, ldb, ldc, device, cuda_stream, variant,
+                            gemm_bf16_block_n(M, N, b_layout, variant, device), 0, 0, 0, workspace, workspace_bytes, 1, nullptr,
+                            nullptr, nullptr, 0, nullptr, 0, nullptr, 0, 0, a_layout, b_layout);
+}
+
+int magi_swiglu_gemm_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                          int64_t ldc, int a_layout, int b_layout, int device, void* cuda_stream) {
+  return magi_swiglu_gemm_bf16_ws(a, b, c, M, N, K, lda, ldb, ldc, a_layout, b_layout, device, cuda_stream, nullptr, 0);
 }
 
 int magi_swiglu_backward_act_bf16(const void* h, const void* dy, void* dh, int64_t M, int64_t N, int64_t ldh,

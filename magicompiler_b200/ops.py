@@ -327,12 +327,18 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, a_is_km: bool, b_is_kn: bool) ->
     c = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
     if m > 0:
         dev = a.device.index if a.device.index is not None else torch.cuda.current_device()
-        rc = _loader.load_library().magi_swiglu_gemm_bf16(
+        lib = _loader.load_library()
+        key = ("gemm_bf16", m, n, k, bool(b_is_kn), dev, _loader.tuning_epoch())
+        need = _ws_need.get(key)
+        if need is None:  # scratch lets a nearly empty last wave be balanced by K ranges
+            need = _ws_need[key] = max(0, int(lib.magi_swiglu_gemm_bf16_workspace_bytes(m, n, k, 1 if b_is_kn else 0, dev)))
+        ws = _workspace(a.device, need) if need else None
+        rc = lib.magi_swiglu_gemm_bf16_ws(
             a2.data_ptr(), b2.data_ptr(), c.data_ptr(), m, n, k, a2.stride(0) if a2.shape[0] > 1 else a2.shape[1],
             b2.stride(0) if b2.shape[0] > 1 else b2.shape[1], n, 1 if a_is_km else 0, 1 if b_is_kn else 0, dev,
-            torch.cuda.current_stream(a.device).cuda_stream)
+            torch.cuda.current_stream(a.device).cuda_stream, ws.data_ptr() if ws is not None else None, need)
         if rc != 0:
-            msg = f"magi_swiglu_gemm_bf16 failed ({rc}): {_loader.last_error()}"
+            msg = f"magi_swiglu_gemm_bf16_ws failed ({rc}): {_loader.last_error()}"
             raise (ValueError(msg) if rc < 0 else RuntimeError(msg))
     return c
 

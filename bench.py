@@ -742,7 +742,12 @@ def main():
         run_single_kernel(b, mb, args)
         return
     if args.workload == "mlp_block":  # the MLP block alone, as the line's headline
-        rec = run_mlp_block(b, mb, args.steps, args.warmup, args.chunks, args.reduce, args.down)
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        rec = run_mlp_block(b, mb, args.steps, args.warmup,
+                            1 if args.reduce in ("peer_scatter", "peer_all_reduce") else args.chunks, args.reduce, args.down)
+        clocks = sampler.stop() if rank == 0 else None
         if rank == 0:
             M, K, N, _, desc = WORKLOADS["mlp_block"]
             print(json.dumps({
@@ -753,7 +758,7 @@ def main():
                 "config": {"workload": "mlp_block", "shape": desc, "chunks": args.chunks, "M": M, "K": K, "N": N,
                            "parallelism": rec["parallelism"], "l2": rec["l2"]},
                 "roofline": rec["roofline"], "gpu_launches": rec["gpu_launches"], "parity": rec["parity"],
-                "detail": rec}), flush=True)
+                "clocks": clocks, "detail": rec}), flush=True)
         if world > 1:
             dist.destroy_process_group()
         if not rec["parity"]["ok"]:
